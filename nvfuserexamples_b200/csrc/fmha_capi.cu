@@ -1,0 +1,263 @@
+// fmha_capi.cu — the extern "C" boundary of libfmha_sm100.so: argument validation, TMA
+// tensor-map construction and kernel launches.  Nothing here allocates device memory and
+// nothing throws; every failure is an int status (see include/fmha_sm100.h).
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cudaTypedefs.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/fmha_sm100.h"
+#include "fmha_kernel_args.h"
+#include "philox.cuh"
+
+namespace fmha {
+
+static thread_local int g_last_cuda_error = 0;
+
+static int cuda_fail(cudaError_t e) {
+  g_last_cuda_error = static_cast<int>(e);
+  return FMHA_ERR_LAUNCH;
+}
+
+// cuTensorMapEncodeTiled, fetched through the runtime so that the library does not link
+// against libcuda directly.
+static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres);
+    if (e == cudaSuccess && qres == cudaDriverEntryPointSuccess) fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+  });
+  return fn;
+}
+
+// Tensor map of a [B,H,S,D] view with a {64 x box_rows x 1 x 1} box and 128-byte swizzle.
+static int make_tmap(CUtensorMap* out, const fmha_tensor4& t, int dtype, int B, int H, int S, int D, int box_rows) {
+  auto enc = get_encode_fn();
+  if (enc == nullptr) return FMHA_ERR_LAUNCH;
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(H),
+                              static_cast<cuuint64_t>(B)};
+  const cuuint64_t strides[3] = {static_cast<cuuint64_t>(t.stride_s) * 2, static_cast<cuuint64_t>(t.stride_h) * 2,
+                                 static_cast<cuuint64_t>(t.stride_b) * 2};
+  const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUtensorMapDataType dt = (dtype == FMHA_DTYPE_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = enc(out, dt, 4, t.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_cuda_error = static_cast<int>(r);
+    return FMHA_ERR_LAUNCH;
+  }
+  return FMHA_OK;
+}
+
+static bool tensor_ok(const fmha_tensor4& t, int B, int H) {
+  if (t.ptr == nullptr) return false;
+  if (reinterpret_cast<uintptr_t>(t.ptr) & 15) return false;
+  if (t.stride_s <= 0 || (t.stride_s % 8) != 0) return false;
+  if (H > 1 && (t.stride_h <= 0 || (t.stride_h % 8) != 0)) return false;
+  if (B > 1 && (t.stride_b <= 0 || (t.stride_b % 8) != 0)) return false;
+  return true;
+}
+
+// Strides of size-1 axes are irrelevant to addressing but must still satisfy the encoder.
+static fmha_tensor4 sanitized(const fmha_tensor4& t, int B, int H, int S, int D) {
+  fmha_tensor4 r = t;
+  if (H <= 1 || r.stride_h <= 0) r.stride_h = static_cast<int64_t>(S) * r.stride_s;
+  if (B <= 1 || r.stride_b <= 0) r.stride_b = static_cast<int64_t>(H) * r.stride_h;
+  (void)D;
+  return r;
+}
+
+static int check_device() {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) { g_last_cuda_error = static_cast<int>(e); return FMHA_ERR_NO_DEVICE; }
+  int major = 0;
+  e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+  if (e != cudaSuccess) { g_last_cuda_error = static_cast<int>(e); return FMHA_ERR_NO_DEVICE; }
+  if (major != 10) return FMHA_ERR_NO_DEVICE;
+  return FMHA_OK;
+}
+
+static int validate_common(int struct_bytes, size_t expect, int dtype, int B, int H, int S_q, int S_k, int D, float scale) {
+  if (struct_bytes != static_cast<int>(expect)) return FMHA_ERR_BAD_ARG;
+  if (dtype != FMHA_DTYPE_F16 && dtype != FMHA_DTYPE_BF16) return FMHA_ERR_UNSUPPORTED;
+  if (D != 64 && D != 128) return FMHA_ERR_UNSUPPORTED;
+  if (B < 0 || H < 0 || S_q < 0 || S_k < 0) return FMHA_ERR_BAD_ARG;
+  if (B > 65535 || H > 65535) return FMHA_ERR_TOO_LARGE;
+  if (!(scale > 0.f) || !std::isfinite(scale)) return FMHA_ERR_BAD_ARG;
+  return FMHA_OK;
+}
+
+}  // namespace fmha
+
+using namespace fmha;
+
+extern "C" {
+
+int fmha_sm100_abi_version(void) { return 1; }
+
+int fmha_sm100_last_cuda_error(void) { return g_last_cuda_error; }
+
+const char* fmha_sm100_strerror(int code) {
+  switch (code) {
+    case FMHA_OK: return "ok";
+    case FMHA_ERR_BAD_ARG: return "bad argument (null/misaligned pointer, bad stride, size or struct_bytes)";
+    case FMHA_ERR_UNSUPPORTED: return "unsupported head dimension, dtype or mode";
+    case FMHA_ERR_LAUNCH: return "CUDA call failed (see fmha_sm100_last_cuda_error)";
+    case FMHA_ERR_DEVICE_TIMEOUT: return "a bounded wait inside the kernel ran out";
+    case FMHA_ERR_NO_DEVICE: return "current device is not an sm_100 GPU";
+    case FMHA_ERR_TOO_LARGE: return "size exceeds the documented maximum";
+    default: return "unknown status";
+  }
+}
+
+int32_t fmha_sm100_dropout_threshold(float p_drop) { return dropout_threshold(p_drop); }
+
+int fmha_sm100_fwd(const fmha_fwd_params* p, void* stream) {
+  if (p == nullptr) return FMHA_ERR_BAD_ARG;
+  int rc = validate_common(p->struct_bytes, sizeof(fmha_fwd_params), p->dtype, p->B, p->H, p->S_q, p->S_k, p->D, p->scale);
+  if (rc != FMHA_OK) return rc;
+  if (p->mask_kind < FMHA_MASK_NONE || p->mask_kind > FMHA_MASK_SEQLEN) return FMHA_ERR_UNSUPPORTED;
+  if (p->dropout_kind < FMHA_DROPOUT_NONE || p->dropout_kind > FMHA_DROPOUT_PHILOX) return FMHA_ERR_UNSUPPORTED;
+  if (p->mask_kind != FMHA_MASK_NONE && p->mask == nullptr) return FMHA_ERR_BAD_ARG;
+  if (p->dropout_kind == FMHA_DROPOUT_DENSE && p->dropout_mask == nullptr) return FMHA_ERR_BAD_ARG;
+  if (p->dropout_kind == FMHA_DROPOUT_PHILOX) {
+    if (!(p->p_drop >= 0.f && p->p_drop < 1.f)) return FMHA_ERR_BAD_ARG;
+    if (p->philox_offset >> 32) return FMHA_ERR_BAD_ARG;
+  }
+  if (p->B == 0 || p->H == 0 || p->S_q == 0) return FMHA_OK;  // nothing to write
+  if (p->S_k == 0) return FMHA_ERR_BAD_ARG;                    // softmax over no keys is undefined
+  if (!tensor_ok(p->q, p->B, p->H) || !tensor_ok(p->k, p->B, p->H) || !tensor_ok(p->v, p->B, p->H) ||
+      !tensor_ok(p->o, p->B, p->H))
+    return FMHA_ERR_BAD_ARG;
+  rc = check_device();
+  if (rc != FMHA_OK) return rc;
+
+  FwdArgs a;
+  std::memset(&a, 0, sizeof(a));
+  if ((rc = make_tmap(&a.tm_q, sanitized(p->q, p->B, p->H, p->S_q, p->D), p->dtype, p->B, p->H, p->S_q, p->D, kTileM))) return rc;
+  if ((rc = make_tmap(&a.tm_k, sanitized(p->k, p->B, p->H, p->S_k, p->D), p->dtype, p->B, p->H, p->S_k, p->D, kTileN))) return rc;
+  if ((rc = make_tmap(&a.tm_v, sanitized(p->v, p->B, p->H, p->S_k, p->D), p->dtype, p->B, p->H, p->S_k, p->D, kTileN))) return rc;
+  if ((rc = make_tmap(&a.tm_o, sanitized(p->o, p->B, p->H, p->S_q, p->D), p->dtype, p->B, p->H, p->S_q, p->D, kTileM))) return rc;
+  a.B = p->B; a.H = p->H; a.S_q = p->S_q; a.S_k = p->S_k;
+  a.scale_log2 = p->scale * 1.4426950408889634f;
+  a.lse = p->lse;
+  a.mask_kind = p->mask_kind;
+  a.mask = p->mask;
+  a.dropout_kind = p->dropout_kind;
+  a.dropout_mask = p->dropout_mask;
+  a.dropout_scale = 1.0f;
+  if (p->dropout_kind == FMHA_DROPOUT_DENSE) a.dropout_scale = p->dropout_scale;
+  if (p->dropout_kind == FMHA_DROPOUT_PHILOX) {
+    const int thr = dropout_threshold(p->p_drop);
+    a.philox_thr = static_cast<uint32_t>(thr);
+    a.dropout_scale = 128.0f / static_cast<float>(128 - thr);
+    if (thr == 0) a.dropout_kind = FMHA_DROPOUT_NONE;  // nothing is ever dropped
+  }
+  a.philox_seed = p->philox_seed;
+  a.philox_offset = static_cast<uint32_t>(p->philox_offset);
+  a.philox_bh_offset = p->philox_bh_offset;
+  a.save_softmax = p->save_softmax;
+  a.save_dropout = p->save_dropout;
+  a.keep_mask_out = p->keep_mask_out;
+  a.debug_scores = p->debug_scores;
+  a.status = p->status;
+
+  const bool p_via_smem = (p->flags & FMHA_FLAG_P_VIA_SMEM) != 0;
+  const bool legacy = p_via_smem || p->mask_kind == FMHA_MASK_DENSE_KEEP || p->mask_kind == FMHA_MASK_DENSE_ADDITIVE ||
+                      p->dropout_kind == FMHA_DROPOUT_DENSE || p->save_softmax || p->save_dropout ||
+                      p->keep_mask_out || p->debug_scores;
+  const int e = launch_fwd(a, p->D, p->dtype, legacy, p_via_smem, static_cast<cudaStream_t>(stream));
+  if (e != 0) return cuda_fail(static_cast<cudaError_t>(e));
+  return FMHA_OK;
+}
+
+int fmha_sm100_check_status(int32_t* status, void* stream, int32_t* host_copy) {
+  if (status == nullptr) return FMHA_ERR_BAD_ARG;
+  int32_t h[4] = {0, 0, 0, 0};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemcpyAsync(h, status, sizeof(h), cudaMemcpyDeviceToHost, s);
+  if (e != cudaSuccess) return cuda_fail(e);
+  e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (host_copy) std::memcpy(host_copy, h, sizeof(h));
+  if (h[0] != 0) {
+    e = cudaMemsetAsync(status, 0, sizeof(h), s);
+    if (e != cudaSuccess) return cuda_fail(e);
+    return FMHA_ERR_DEVICE_TIMEOUT;
+  }
+  return FMHA_OK;
+}
+
+int fmha_sm100_philox_mask_host(uint64_t seed, uint64_t offset, int32_t bh_offset, int32_t n_bh, int32_t S_q,
+                                int32_t S_k, float p_drop, uint8_t* out) {
+  if (out == nullptr || n_bh < 0 || S_q < 0 || S_k < 0) return FMHA_ERR_BAD_ARG;
+  if (!(p_drop >= 0.f && p_drop < 1.f) || (offset >> 32)) return FMHA_ERR_BAD_ARG;
+  const uint32_t thr = static_cast<uint32_t>(dropout_threshold(p_drop));
+  for (int bh = 0; bh < n_bh; ++bh)
+    for (int r = 0; r < S_q; ++r) {
+      uint8_t* row = out + (static_cast<size_t>(bh) * S_q + r) * S_k;
+      for (int kb = 0; kb * 16 < S_k; ++kb) {
+        const U4 d = dropout_draw(seed, static_cast<uint32_t>(offset), static_cast<uint32_t>(bh_offset + bh),
+                                  static_cast<uint32_t>(r), static_cast<uint32_t>(kb));
+        const uint32_t w[4] = {d.x, d.y, d.z, d.w};
+        for (int i = 0; i < 16 && kb * 16 + i < S_k; ++i) {
+          const uint32_t byte = (w[i / 4] >> (8 * (i % 4))) & 0xffu;
+          row[kb * 16 + i] = ((byte & 0x7fu) >= thr) ? 1 : 0;
+        }
+      }
+    }
+  return FMHA_OK;
+}
+
+}  // extern "C"
+
+namespace fmha {
+__global__ void philox_mask_kernel(uint64_t seed, uint32_t offset, int bh_offset, int n_bh, int S_q, int S_k,
+                                   uint32_t thr, uint8_t* out) {
+  const int n_kb = (S_k + 15) / 16;
+  const size_t total = static_cast<size_t>(n_bh) * S_q * n_kb;
+  for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const int kb = static_cast<int>(idx % n_kb);
+    const size_t rr = idx / n_kb;
+    const int r = static_cast<int>(rr % S_q);
+    const int bh = static_cast<int>(rr / S_q);
+    const U4 d = dropout_draw(seed, offset, static_cast<uint32_t>(bh_offset + bh), static_cast<uint32_t>(r),
+                              static_cast<uint32_t>(kb));
+    const uint32_t w[4] = {d.x, d.y, d.z, d.w};
+    uint8_t* row = out + (static_cast<size_t>(bh) * S_q + r) * S_k;
+    for (int k = 0; k < 4; ++k) {
+      const uint32_t keep = dropout_keep_bits(w[k], thr);
+      for (int e = 0; e < 4; ++e) {
+        const int col = kb * 16 + k * 4 + e;
+        if (col < S_k) row[col] = (keep >> (8 * e + 7)) & 1u;
+      }
+    }
+  }
+}
+}  // namespace fmha
+
+extern "C" int fmha_sm100_philox_mask_device(uint64_t seed, uint64_t offset, int32_t bh_offset, int32_t n_bh,
+                                              int32_t S_q, int32_t S_k, float p_drop, uint8_t* out, void* stream) {
+  if (out == nullptr || n_bh < 0 || S_q < 0 || S_k < 0) return FMHA_ERR_BAD_ARG;
+  if (!(p_drop >= 0.f && p_drop < 1.f) || (offset >> 32)) return FMHA_ERR_BAD_ARG;
+  const size_t total = static_cast<size_t>(n_bh) * S_q * ((S_k + 15) / 16);
+  if (total == 0) return FMHA_OK;
+  const uint32_t thr = static_cast<uint32_t>(dropout_threshold(p_drop));
+  const int threads = 256;
+  const int blocks = static_cast<int>(std::min<size_t>((total + threads - 1) / threads, 148 * 16));
+  fmha::philox_mask_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      seed, static_cast<uint32_t>(offset), bh_offset, n_bh, S_q, S_k, thr, out);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e);
+  return FMHA_OK;
+}

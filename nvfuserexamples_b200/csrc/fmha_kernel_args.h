@@ -1,0 +1,66 @@
+// fmha_kernel_args.h — parameter blocks passed (by value, __grid_constant__) to the kernels,
+// and the launch functions the C ABI layer calls.  Internal to the library.
+#pragma once
+#include <cuda.h>  // CUtensorMap (type only; the encode entry point is looked up at run time)
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fmha {
+
+constexpr int kTileM = 128;  // query rows per CTA tile
+constexpr int kTileN = 128;  // keys per step
+
+struct FwdArgs {
+  alignas(64) CUtensorMap tm_q;
+  alignas(64) CUtensorMap tm_k;
+  alignas(64) CUtensorMap tm_v;
+  alignas(64) CUtensorMap tm_o;
+  int B, H, S_q, S_k;
+  float scale_log2;  // softmax scale * log2(e)
+  float* lse;
+  int mask_kind;
+  const void* mask;
+  int dropout_kind;
+  const void* dropout_mask;
+  float dropout_scale;   // multiplier applied to kept probabilities
+  uint32_t philox_thr;   // 7-bit threshold
+  uint64_t philox_seed;
+  uint32_t philox_offset;
+  int philox_bh_offset;
+  void* save_softmax;
+  void* save_dropout;
+  uint8_t* keep_mask_out;
+  float* debug_scores;
+  int* status;
+};
+
+struct BwdArgs {
+  alignas(64) CUtensorMap tm_q;
+  alignas(64) CUtensorMap tm_k;
+  alignas(64) CUtensorMap tm_v;
+  alignas(64) CUtensorMap tm_do;
+  alignas(64) CUtensorMap tm_dk;
+  alignas(64) CUtensorMap tm_dv;
+  int B, H, S_q, S_k;
+  float scale;       // softmax scale
+  float scale_log2;  // softmax scale * log2(e)
+  const float* lse;  // [B*H, S_q] natural log
+  const float* delta;  // [B*H, S_q] rowsum(dO * O)
+  float* dq_accum;     // [B*H, S_q_pad, D] fp32, zero on entry
+  int S_q_pad;         // S_q rounded up to the tile
+  int mask_kind;
+  const void* mask;
+  int dropout_kind;
+  float dropout_scale;
+  uint32_t philox_thr;
+  uint64_t philox_seed;
+  uint32_t philox_offset;
+  int philox_bh_offset;
+  int* status;
+};
+
+// Launchers (defined in the .cu files).  Return a cudaError_t as int.
+int launch_fwd(const FwdArgs& a, int D, int dtype, bool legacy, bool p_via_smem, cudaStream_t stream);
+int launch_bwd(const BwdArgs& a, int D, int dtype, cudaStream_t stream);
+
+}  // namespace fmha

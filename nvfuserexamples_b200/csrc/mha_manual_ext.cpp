@@ -1,0 +1,400 @@
+// mha_manual_ext.cpp — the torch operator layer: `import mha_manual` registers
+// torch.ops.mha_manual.* and forwards every call to the C ABI of libfmha_sm100.so.
+//
+// The three legacy operators keep the names, arity and positional order of the reference's
+// (shmsong/NvFuserExamples fmha/fmha_manual.cpp:1218-1250), so its test.py, test_train_mha.py
+// and perf_measurement*.py run against this module unchanged:
+//     fmha_nvfuser(q, k, v, amask)                              -> ctx
+//     fmha_train_nvfuser(q, k, v, pad_mask, dropout_mask)       -> ctx
+//     fmha_train_saveim_nvfuser(q, k, v, pad_mask, dropout_mask)-> [ctx, softmax, dropout_out]
+// Unlike the reference they accept any [B*H, S, D] (D in {64,128}, fp16/bf16) and validate
+// their arguments.  The softmax scale is 1/sqrt(D) (the reference hard-wires 1/8 for D=64,
+// fmha_manual.cpp:68) and the dropout factor is the reference's 1/0.5 (fmha_manual.cpp:478-480).
+//
+// New operators (no reference counterpart): fmha_fwd / fmha_bwd / fmha (autograd) take a
+// compact padding mask or valid lengths and Philox (seed, offset) dropout, and
+// philox_dropout_mask regenerates the dense keep mask for checking.
+//
+// There is no CPU implementation: the operators are registered for the CUDA key only and
+// every failure of the kernel library surfaces as a RuntimeError.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <cmath>
+#include <cstdlib>
+#include <mutex>
+#include <vector>
+
+#include "fmha_sm100.h"
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+
+// One int32[4] status block per device, allocated on first use and kept for the process.
+at::Tensor& status_block(int device) {
+  static std::mutex mu;
+  static at::Tensor blocks[kMaxDevices];
+  std::lock_guard<std::mutex> g(mu);
+  TORCH_CHECK(device >= 0 && device < kMaxDevices, "mha_manual: device index out of range");
+  if (!blocks[device].defined())
+    blocks[device] = at::zeros({4}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device));
+  return blocks[device];
+}
+
+bool checked_mode() {
+  static const bool on = [] {
+    const char* e = std::getenv("MHA_MANUAL_CHECKED");
+    return e != nullptr && e[0] != '\0' && e[0] != '0';
+  }();
+  return on;
+}
+
+void raise_if(int rc, const char* what) {
+  TORCH_CHECK(rc == FMHA_OK, "mha_manual::", what, " failed: ", fmha_sm100_strerror(rc), " (status ", rc,
+              ", cuda error ", fmha_sm100_last_cuda_error(), ")");
+}
+
+void finish_call(int rc, const char* what, int device) {
+  raise_if(rc, what);
+  if (checked_mode()) {
+    int32_t words[4];
+    const int s = fmha_sm100_check_status(status_block(device).data_ptr<int32_t>(),
+                                          at::cuda::getCurrentCUDAStream(device).stream(), words);
+    TORCH_CHECK(s == FMHA_OK, "mha_manual::", what, ": ", fmha_sm100_strerror(s), " at wait site ", words[0],
+                " (CTA ", words[2], ",", words[3], ")");
+  }
+}
+
+struct View4 {
+  fmha_tensor4 t;
+  int64_t B, H, S, D;
+};
+
+// Accepts [B,H,S,D] or [B*H,S,D] (then B := B*H, H := 1) with a contiguous last axis.
+View4 view4(const at::Tensor& x, const char* name) {
+  TORCH_CHECK(x.is_cuda(), "mha_manual: ", name, " must be a CUDA tensor");
+  TORCH_CHECK(x.dim() == 3 || x.dim() == 4, "mha_manual: ", name, " must be [B,H,S,D] or [B*H,S,D]");
+  TORCH_CHECK(x.scalar_type() == at::kHalf || x.scalar_type() == at::kBFloat16, "mha_manual: ", name,
+              " must be float16 or bfloat16");
+  TORCH_CHECK(x.stride(-1) == 1, "mha_manual: ", name, " must be contiguous along the head dimension");
+  View4 v;
+  v.t.ptr = x.data_ptr();
+  if (x.dim() == 4) {
+    v.B = x.size(0); v.H = x.size(1); v.S = x.size(2); v.D = x.size(3);
+    v.t.stride_b = x.stride(0); v.t.stride_h = x.stride(1); v.t.stride_s = x.stride(2);
+  } else {
+    v.B = x.size(0); v.H = 1; v.S = x.size(1); v.D = x.size(2);
+    v.t.stride_b = x.stride(0); v.t.stride_h = x.stride(0); v.t.stride_s = x.stride(1);
+  }
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(v.t.ptr) & 15) == 0, "mha_manual: ", name, " must be 16-byte aligned");
+  TORCH_CHECK(v.t.stride_s % 8 == 0 && (v.H == 1 || v.t.stride_h % 8 == 0) && (v.B == 1 || v.t.stride_b % 8 == 0),
+              "mha_manual: strides of ", name, " must be multiples of 8 elements");
+  return v;
+}
+
+int dtype_code(const at::Tensor& x) { return x.scalar_type() == at::kBFloat16 ? FMHA_DTYPE_BF16 : FMHA_DTYPE_F16; }
+
+void check_same(const at::Tensor& ref, const at::Tensor& x, const char* name) {
+  TORCH_CHECK(x.device() == ref.device(), "mha_manual: ", name, " is on a different device");
+  TORCH_CHECK(x.scalar_type() == ref.scalar_type(), "mha_manual: ", name, " has a different dtype");
+}
+
+void check_qkv(const View4& q, const View4& k, const View4& v) {
+  TORCH_CHECK(q.D == 64 || q.D == 128, "mha_manual: head dimension must be 64 or 128, got ", q.D);
+  TORCH_CHECK(k.D == q.D && v.D == q.D, "mha_manual: q, k, v head dimensions differ");
+  TORCH_CHECK(k.B == q.B && v.B == q.B && k.H == q.H && v.H == q.H, "mha_manual: q, k, v batch/head sizes differ");
+  TORCH_CHECK(k.S == v.S, "mha_manual: k and v sequence lengths differ");
+  TORCH_CHECK(q.S == 0 || k.S > 0, "mha_manual: key length must be positive");
+}
+
+at::Tensor dense_3d(const at::Tensor& m, const at::Tensor& q, int64_t bh, int64_t sq, int64_t sk, const char* name) {
+  check_same(q, m, name);
+  TORCH_CHECK(m.numel() == bh * sq * sk, "mha_manual: ", name, " must have B*H*S_q*S_k elements");
+  return m.contiguous();
+}
+
+// ---------------------------------------------------------------------------------------
+// legacy operators
+// ---------------------------------------------------------------------------------------
+std::vector<at::Tensor> legacy_forward(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                                       const at::Tensor& mask, int mask_kind, const at::Tensor* dropout_mask,
+                                       bool save, const char* what) {
+  const View4 vq = view4(q, "q"), vk = view4(k, "k"), vv = view4(v, "v");
+  check_same(q, k, "k");
+  check_same(q, v, "v");
+  check_qkv(vq, vk, vv);
+  const c10::cuda::CUDAGuard guard(q.device());
+  const int dev = q.get_device();
+  const int64_t bh = vq.B * vq.H;
+  at::Tensor mask_c = dense_3d(mask, q, bh, vq.S, vk.S, "mask");
+  at::Tensor dm_c;
+  if (dropout_mask) dm_c = dense_3d(*dropout_mask, q, bh, vq.S, vk.S, "dropout_mask");
+  at::Tensor o = at::empty(q.sizes(), q.options());
+  const View4 vo = view4(o, "o");
+  std::vector<at::Tensor> outs{o};
+  fmha_fwd_params p{};
+  p.struct_bytes = sizeof(p);
+  p.dtype = dtype_code(q);
+  p.B = static_cast<int32_t>(vq.B); p.H = static_cast<int32_t>(vq.H);
+  p.S_q = static_cast<int32_t>(vq.S); p.S_k = static_cast<int32_t>(vk.S); p.D = static_cast<int32_t>(vq.D);
+  p.scale = 1.0f / std::sqrt(static_cast<float>(vq.D));
+  p.q = vq.t; p.k = vk.t; p.v = vv.t; p.o = vo.t;
+  p.mask_kind = mask_kind;
+  p.mask = mask_c.data_ptr();
+  if (dropout_mask) {
+    p.dropout_kind = FMHA_DROPOUT_DENSE;
+    p.dropout_mask = dm_c.data_ptr();
+    p.dropout_scale = 2.0f;  // 1 / dropout_prob with dropout_prob = 0.5, fmha_manual.cpp:421,478-479
+  }
+  if (save) {
+    at::Tensor sm = at::empty({bh, vq.S, vk.S}, q.options());
+    at::Tensor dr = at::empty({bh, vq.S, vk.S}, q.options());
+    p.save_softmax = sm.data_ptr();
+    p.save_dropout = dr.data_ptr();
+    outs.push_back(sm);
+    outs.push_back(dr);
+  }
+  p.status = status_block(dev).data_ptr<int32_t>();
+  finish_call(fmha_sm100_fwd(&p, at::cuda::getCurrentCUDAStream(dev).stream()), what, dev);
+  return outs;
+}
+
+at::Tensor fmha_nvfuser(const at::Tensor& input, const at::Tensor& qk, const at::Tensor& v, const at::Tensor& amask) {
+  return legacy_forward(input, qk, v, amask, FMHA_MASK_DENSE_KEEP, nullptr, false, "fmha_nvfuser")[0];
+}
+
+at::Tensor fmha_train_nvfuser(const at::Tensor& input, const at::Tensor& qk, const at::Tensor& v,
+                              const at::Tensor& pad_mask, const at::Tensor& dropout_mask) {
+  return legacy_forward(input, qk, v, pad_mask, FMHA_MASK_DENSE_ADDITIVE, &dropout_mask, false, "fmha_train_nvfuser")[0];
+}
+
+std::vector<at::Tensor> fmha_train_saveim_nvfuser(const at::Tensor& input, const at::Tensor& qk, const at::Tensor& v,
+                                                  const at::Tensor& pad_mask, const at::Tensor& dropout_mask) {
+  return legacy_forward(input, qk, v, pad_mask, FMHA_MASK_DENSE_ADDITIVE, &dropout_mask, true,
+                        "fmha_train_saveim_nvfuser");
+}
+
+// ---------------------------------------------------------------------------------------
+// new operators
+// ---------------------------------------------------------------------------------------
+struct MaskArg {
+  int kind = FMHA_MASK_NONE;
+  at::Tensor holder;
+  const void* ptr = nullptr;
+};
+
+MaskArg resolve_mask(const c10::optional<at::Tensor>& mask, const c10::optional<at::Tensor>& seqlens, int64_t B,
+                     int64_t S_k, const at::Tensor& q) {
+  MaskArg m;
+  TORCH_CHECK(!(mask.has_value() && seqlens.has_value()), "mha_manual: give either mask or seqlens, not both");
+  if (mask.has_value()) {
+    const at::Tensor& t = *mask;
+    TORCH_CHECK(t.device() == q.device(), "mha_manual: mask is on a different device");
+    TORCH_CHECK(t.numel() == B * S_k, "mha_manual: mask must be [B,S_k] (or [B,1,1,S_k]) additive");
+    m.holder = t.reshape({B, S_k}).to(at::kFloat).contiguous();
+    m.kind = FMHA_MASK_KEY_ADDITIVE;
+    m.ptr = m.holder.data_ptr();
+  } else if (seqlens.has_value()) {
+    const at::Tensor& t = *seqlens;
+    TORCH_CHECK(t.device() == q.device(), "mha_manual: seqlens is on a different device");
+    TORCH_CHECK(t.numel() == B, "mha_manual: seqlens must be [B]");
+    m.holder = t.reshape({B}).to(at::kInt).contiguous();
+    m.kind = FMHA_MASK_SEQLEN;
+    m.ptr = m.holder.data_ptr();
+  }
+  return m;
+}
+
+std::tuple<at::Tensor, at::Tensor> fmha_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                                            const c10::optional<at::Tensor>& mask,
+                                            const c10::optional<at::Tensor>& seqlens, double p_drop, int64_t seed,
+                                            int64_t offset, c10::optional<double> scale, int64_t bh_offset) {
+  const View4 vq = view4(q, "q"), vk = view4(k, "k"), vv = view4(v, "v");
+  check_same(q, k, "k");
+  check_same(q, v, "v");
+  check_qkv(vq, vk, vv);
+  const c10::cuda::CUDAGuard guard(q.device());
+  const int dev = q.get_device();
+  const MaskArg m = resolve_mask(mask, seqlens, vq.B, vk.S, q);
+  at::Tensor o = at::empty(q.sizes(), q.options());
+  std::vector<int64_t> lse_shape{vq.B, vq.S};
+  if (q.dim() == 4) lse_shape = {vq.B, vq.H, vq.S};
+  at::Tensor lse = at::empty(lse_shape, q.options().dtype(at::kFloat));
+  const View4 vo = view4(o, "o");
+  fmha_fwd_params p{};
+  p.struct_bytes = sizeof(p);
+  p.dtype = dtype_code(q);
+  p.B = static_cast<int32_t>(vq.B); p.H = static_cast<int32_t>(vq.H);
+  p.S_q = static_cast<int32_t>(vq.S); p.S_k = static_cast<int32_t>(vk.S); p.D = static_cast<int32_t>(vq.D);
+  p.scale = scale.has_value() ? static_cast<float>(*scale) : 1.0f / std::sqrt(static_cast<float>(vq.D));
+  p.q = vq.t; p.k = vk.t; p.v = vv.t; p.o = vo.t;
+  p.lse = lse.data_ptr<float>();
+  p.mask_kind = m.kind;
+  p.mask = m.ptr;
+  if (p_drop > 0.0) {
+    p.dropout_kind = FMHA_DROPOUT_PHILOX;
+    p.p_drop = static_cast<float>(p_drop);
+    p.philox_seed = static_cast<uint64_t>(seed);
+    p.philox_offset = static_cast<uint64_t>(offset);
+  }
+  p.philox_bh_offset = static_cast<int32_t>(bh_offset);
+  p.status = status_block(dev).data_ptr<int32_t>();
+  finish_call(fmha_sm100_fwd(&p, at::cuda::getCurrentCUDAStream(dev).stream()), "fmha_fwd", dev);
+  return {o, lse};
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_bwd(const at::Tensor& d_o, const at::Tensor& q, const at::Tensor& k,
+                                                        const at::Tensor& v, const at::Tensor& o, const at::Tensor& lse,
+                                                        const c10::optional<at::Tensor>& mask,
+                                                        const c10::optional<at::Tensor>& seqlens, double p_drop,
+                                                        int64_t seed, int64_t offset, c10::optional<double> scale,
+                                                        int64_t bh_offset) {
+  const View4 vq = view4(q, "q"), vk = view4(k, "k"), vv = view4(v, "v"), vo = view4(o, "o");
+  at::Tensor d_o_c = d_o.stride(-1) == 1 ? d_o : d_o.contiguous();
+  const View4 vdo = view4(d_o_c, "d_o");
+  check_same(q, k, "k"); check_same(q, v, "v"); check_same(q, o, "o"); check_same(q, d_o_c, "d_o");
+  check_qkv(vq, vk, vv);
+  TORCH_CHECK(vo.B == vq.B && vo.H == vq.H && vo.S == vq.S && vo.D == vq.D, "mha_manual: o must have the shape of q");
+  TORCH_CHECK(vdo.B == vq.B && vdo.H == vq.H && vdo.S == vq.S && vdo.D == vq.D, "mha_manual: d_o must have the shape of q");
+  TORCH_CHECK(lse.device() == q.device() && lse.scalar_type() == at::kFloat && lse.numel() == vq.B * vq.H * vq.S,
+              "mha_manual: lse must be float32 [B,H,S_q] on the device of q");
+  const c10::cuda::CUDAGuard guard(q.device());
+  const int dev = q.get_device();
+  const MaskArg m = resolve_mask(mask, seqlens, vq.B, vk.S, q);
+  at::Tensor lse_c = lse.contiguous();
+  at::Tensor dq = at::empty(q.sizes(), q.options());
+  at::Tensor dk = at::empty(k.sizes(), k.options());
+  at::Tensor dv = at::empty(v.sizes(), v.options());
+  const View4 vdq = view4(dq, "dq"), vdk = view4(dk, "dk"), vdv = view4(dv, "dv");
+  fmha_bwd_params p{};
+  p.struct_bytes = sizeof(p);
+  p.dtype = dtype_code(q);
+  p.B = static_cast<int32_t>(vq.B); p.H = static_cast<int32_t>(vq.H);
+  p.S_q = static_cast<int32_t>(vq.S); p.S_k = static_cast<int32_t>(vk.S); p.D = static_cast<int32_t>(vq.D);
+  p.scale = scale.has_value() ? static_cast<float>(*scale) : 1.0f / std::sqrt(static_cast<float>(vq.D));
+  p.q = vq.t; p.k = vk.t; p.v = vv.t; p.o = vo.t; p.d_o = vdo.t;
+  p.lse = lse_c.data_ptr<float>();
+  p.dq = vdq.t; p.dk = vdk.t; p.dv = vdv.t;
+  p.mask_kind = m.kind;
+  p.mask = m.ptr;
+  if (p_drop > 0.0) {
+    p.dropout_kind = FMHA_DROPOUT_PHILOX;
+    p.p_drop = static_cast<float>(p_drop);
+    p.philox_seed = static_cast<uint64_t>(seed);
+    p.philox_offset = static_cast<uint64_t>(offset);
+  }
+  p.philox_bh_offset = static_cast<int32_t>(bh_offset);
+  size_t ws = 0;
+  raise_if(fmha_sm100_bwd_workspace_bytes(&p, &ws), "fmha_bwd_workspace_bytes");
+  at::Tensor workspace = at::empty({static_cast<int64_t>(ws)}, q.options().dtype(at::kByte));
+  p.workspace = workspace.data_ptr();
+  p.workspace_bytes = ws;
+  p.status = status_block(dev).data_ptr<int32_t>();
+  finish_call(fmha_sm100_bwd(&p, at::cuda::getCurrentCUDAStream(dev).stream()), "fmha_bwd", dev);
+  return {dq, dk, dv};
+}
+
+at::Tensor philox_dropout_mask(int64_t B, int64_t H, int64_t S_q, int64_t S_k, double p, int64_t seed, int64_t offset,
+                               int64_t bh_offset, bool on_device) {
+  TORCH_CHECK(B >= 0 && H >= 0 && S_q >= 0 && S_k >= 0, "mha_manual: negative size");
+  if (on_device) {
+    at::Tensor out = at::empty({B, H, S_q, S_k}, at::TensorOptions().dtype(at::kByte).device(at::kCUDA));
+    raise_if(fmha_sm100_philox_mask_device(static_cast<uint64_t>(seed), static_cast<uint64_t>(offset),
+                                           static_cast<int32_t>(bh_offset), static_cast<int32_t>(B * H),
+                                           static_cast<int32_t>(S_q), static_cast<int32_t>(S_k), static_cast<float>(p),
+                                           out.data_ptr<uint8_t>(), at::cuda::getCurrentCUDAStream().stream()),
+             "philox_dropout_mask");
+    return out;
+  }
+  at::Tensor out = at::empty({B, H, S_q, S_k}, at::TensorOptions().dtype(at::kByte));
+  raise_if(fmha_sm100_philox_mask_host(static_cast<uint64_t>(seed), static_cast<uint64_t>(offset),
+                                       static_cast<int32_t>(bh_offset), static_cast<int32_t>(B * H),
+                                       static_cast<int32_t>(S_q), static_cast<int32_t>(S_k), static_cast<float>(p),
+                                       out.data_ptr<uint8_t>()),
+           "philox_dropout_mask");
+  return out;
+}
+
+void check_status() {
+  const int dev = at::cuda::current_device();
+  int32_t words[4];
+  const int s = fmha_sm100_check_status(status_block(dev).data_ptr<int32_t>(),
+                                        at::cuda::getCurrentCUDAStream(dev).stream(), words);
+  TORCH_CHECK(s == FMHA_OK, "mha_manual: ", fmha_sm100_strerror(s), " at wait site ", words[0], " (CTA ", words[2], ",",
+              words[3], ")");
+}
+
+// ---------------------------------------------------------------------------------------
+// autograd: fmha = fmha_fwd + fmha_bwd
+// ---------------------------------------------------------------------------------------
+class FmhaFunction : public torch::autograd::Function<FmhaFunction> {
+ public:
+  static at::Tensor forward(torch::autograd::AutogradContext* ctx, const at::Tensor& q, const at::Tensor& k,
+                            const at::Tensor& v, const c10::optional<at::Tensor>& mask,
+                            const c10::optional<at::Tensor>& seqlens, double p_drop, int64_t seed, int64_t offset,
+                            c10::optional<double> scale) {
+    at::AutoDispatchBelowADInplaceOrView guard;
+    auto [o, lse] = fmha_fwd(q, k, v, mask, seqlens, p_drop, seed, offset, scale, 0);
+    ctx->save_for_backward({q, k, v, o, lse, mask.has_value() ? *mask : at::Tensor(),
+                            seqlens.has_value() ? *seqlens : at::Tensor()});
+    ctx->saved_data["p_drop"] = p_drop;
+    ctx->saved_data["seed"] = seed;
+    ctx->saved_data["offset"] = offset;
+    ctx->saved_data["has_scale"] = scale.has_value();
+    ctx->saved_data["scale"] = scale.has_value() ? *scale : 0.0;
+    return o;
+  }
+  static torch::autograd::variable_list backward(torch::autograd::AutogradContext* ctx,
+                                                 torch::autograd::variable_list grads) {
+    const auto saved = ctx->get_saved_variables();
+    c10::optional<at::Tensor> mask, seqlens;
+    if (saved[5].defined()) mask = saved[5];
+    if (saved[6].defined()) seqlens = saved[6];
+    c10::optional<double> scale;
+    if (ctx->saved_data["has_scale"].toBool()) scale = ctx->saved_data["scale"].toDouble();
+    auto [dq, dk, dv] = fmha_bwd(grads[0], saved[0], saved[1], saved[2], saved[3], saved[4], mask, seqlens,
+                                 ctx->saved_data["p_drop"].toDouble(), ctx->saved_data["seed"].toInt(),
+                                 ctx->saved_data["offset"].toInt(), scale, 0);
+    return {dq, dk, dv, at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor()};
+  }
+};
+
+at::Tensor fmha_autograd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                         const c10::optional<at::Tensor>& mask, const c10::optional<at::Tensor>& seqlens, double p_drop,
+                         int64_t seed, int64_t offset, c10::optional<double> scale) {
+  return FmhaFunction::apply(q, k, v, mask, seqlens, p_drop, seed, offset, scale);
+}
+
+}  // namespace
+
+TORCH_LIBRARY(mha_manual, m) {
+  m.def("fmha_nvfuser(Tensor input, Tensor qk, Tensor v, Tensor amask) -> Tensor");
+  m.def("fmha_train_nvfuser(Tensor input, Tensor qk, Tensor v, Tensor pad_mask, Tensor dropout_mask) -> Tensor");
+  m.def("fmha_train_saveim_nvfuser(Tensor input, Tensor qk, Tensor v, Tensor pad_mask, Tensor dropout_mask) -> Tensor[]");
+  m.def("fmha_fwd(Tensor q, Tensor k, Tensor v, Tensor? mask=None, Tensor? seqlens=None, float p_drop=0.0, "
+        "int seed=0, int offset=0, float? scale=None, int bh_offset=0) -> (Tensor, Tensor)");
+  m.def("fmha_bwd(Tensor d_o, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, Tensor? mask=None, "
+        "Tensor? seqlens=None, float p_drop=0.0, int seed=0, int offset=0, float? scale=None, int bh_offset=0) "
+        "-> (Tensor, Tensor, Tensor)");
+  m.def("fmha(Tensor q, Tensor k, Tensor v, Tensor? mask=None, Tensor? seqlens=None, float p_drop=0.0, int seed=0, "
+        "int offset=0, float? scale=None) -> Tensor");
+  m.def("philox_dropout_mask(int B, int H, int S_q, int S_k, float p, int seed, int offset, int bh_offset=0, "
+        "bool on_device=False) -> Tensor", philox_dropout_mask);
+  m.def("check_status() -> ()", check_status);
+}
+
+TORCH_LIBRARY_IMPL(mha_manual, CUDA, m) {
+  m.impl("fmha_nvfuser", fmha_nvfuser);
+  m.impl("fmha_train_nvfuser", fmha_train_nvfuser);
+  m.impl("fmha_train_saveim_nvfuser", fmha_train_saveim_nvfuser);
+  m.impl("fmha_fwd", fmha_fwd);
+  m.impl("fmha_bwd", fmha_bwd);
+}
+
+TORCH_LIBRARY_IMPL(mha_manual, Autograd, m) { m.impl("fmha", fmha_autograd); }
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.doc() = "B200 fused multi-head attention operators (torch.ops.mha_manual.*)";
+}
