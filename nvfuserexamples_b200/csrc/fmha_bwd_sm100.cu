@@ -1,6 +1,561 @@
-// placeholder, replaced below
+// fmha_bwd_sm100.cu — fused multi-head-attention backward for B200 (sm_100a).
+//
+// The reference project has no backward pass (shmsong/NvFuserExamples README.md:1); its
+// provision for one is the pair of S x S tensors saved by FMHATrainKernelSaveIntermediate
+// (fmha/fmha_manual.cpp:891-897).  This backward needs neither: it recomputes the
+// probabilities from Q, K and the per-row logsumexp the forward kernel wrote.
+//
+// Three kernels per call:
+//   1. bwd_prepare : delta[row] = sum_d dO[row,d] * O[row,d]  and zero the fp32 dQ accumulator
+//   2. bwd_main    : one CTA per (128-key tile, head, batch) loops over the 128-row query tiles
+//                      S  = Q K^T            dP = dO V^T              (tcgen05.mma, fp32 in TMEM)
+//                      P  = exp2(S*scale*log2e + mask - lse*log2e)   (8 warps, thread = row, half the columns)
+//                      dS = P * (keep*c*dP - delta)                   c = 1/(1-p_drop)
+//                      dV += (keep*P)^T dO     dK += dS^T Q     dQ_tile = dS K
+//                    P and dS go through shared memory (16-bit, 128-byte swizzle) and are read
+//                    by the tensor core both as K-major (dQ) and as MN-major (dV, dK) operands;
+//                    dQ tiles are added to the fp32 accumulator with vector red.global.add;
+//                    dK and dV leave through shared memory and TMA stores.
+//   3. bwd_finish  : dQ = (scale * accumulator) rounded to the 16-bit dtype
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cstring>
+
 #include "../../include/fmha_sm100.h"
+#include "fmha_device_utils.cuh"
 #include "fmha_kernel_args.h"
-namespace fmha { int launch_bwd(const BwdArgs&, int, int, cudaStream_t) { return 1; } }
-extern "C" int fmha_sm100_bwd(const fmha_bwd_params*, void*) { return FMHA_ERR_UNSUPPORTED; }
-extern "C" int fmha_sm100_bwd_workspace_bytes(const fmha_bwd_params*, size_t*) { return FMHA_ERR_UNSUPPORTED; }
+#include "philox.cuh"
+#include "sm100_ptx.cuh"
+
+namespace fmha {
+
+namespace {
+
+constexpr int kBwdThreads = 320;  // producer warp, MMA warp, 8 compute warps
+constexpr float kLog2eB = 1.4426950408889634f;
+
+enum BwdWaitSite {
+  kSiteKvFull = 201, kSiteQdoFull = 202, kSiteQdoEmpty = 203, kSiteSdpFull = 204, kSitePdsFull = 205,
+  kSiteDqFull = 206, kSiteDqFree = 207, kSiteAccFull = 208
+};
+
+template <int D>
+struct BwdSmem {
+  static constexpr int kStages = (D == 64) ? 2 : 1;
+  static constexpr int kTileBytes = kTileM * D * 2;
+  static constexpr int kOffK = 0;
+  static constexpr int kOffV = kOffK + kTileBytes;
+  static constexpr int kOffQ = kOffV + kTileBytes;
+  static constexpr int kOffdO = kOffQ + kStages * kTileBytes;
+  static constexpr int kOffP = kOffdO + kStages * kTileBytes;
+  static constexpr int kOffdS = kOffP + kTileM * kTileN * 2;
+  static constexpr int kOffMask = kOffdS + kTileM * kTileN * 2;  // 128 floats
+  static constexpr int kOffBar = kOffMask + kTileN * 4;
+  static constexpr int kNumBars = 6 + 2 * kStages;
+  static constexpr int kOffMisc = kOffBar + kNumBars * 8;
+  static constexpr int kBytes = kOffMisc + 16;
+  static constexpr int kDynBytes = kBytes + 1024;
+};
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------
+// 1. delta and accumulator clearing
+// ---------------------------------------------------------------------------------------
+struct PrepArgs {
+  const void* o;
+  const void* d_o;
+  int64_t o_sb, o_sh, o_ss, do_sb, do_sh, do_ss;
+  int B, H, S_q, S_q_pad, D;
+  float* delta;     // [B*H, S_q]
+  float* dq_accum;  // [B*H, S_q_pad, D]
+};
+
+template <bool BF16>
+__global__ void __launch_bounds__(256) bwd_prepare_kernel(const PrepArgs a) {
+  // 8 threads per row (D = 64: 8 elements each; D = 128: 16 elements each)
+  const int per = a.D / 8;
+  const int64_t row_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 3;
+  const int part = threadIdx.x & 7;
+  const int64_t n_rows = static_cast<int64_t>(a.B) * a.H * a.S_q_pad;
+  const bool in_range = row_global < n_rows;  // no early exit: the shuffles below need every lane
+  const int r = in_range ? static_cast<int>(row_global % a.S_q_pad) : a.S_q_pad;
+  const int64_t bh = row_global / a.S_q_pad;
+  const int h = static_cast<int>(bh % a.H);
+  const int b = static_cast<int>(bh / a.H);
+  if (in_range) {
+    float4* acc = reinterpret_cast<float4*>(a.dq_accum + row_global * a.D + part * per);
+    for (int i = 0; i < per / 4; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float sum = 0.f;
+  if (r < a.S_q) {
+    const unsigned short* po = reinterpret_cast<const unsigned short*>(a.o) + b * a.o_sb + h * a.o_sh + r * a.o_ss + part * per;
+    const unsigned short* pd = reinterpret_cast<const unsigned short*>(a.d_o) + b * a.do_sb + h * a.do_sh + r * a.do_ss + part * per;
+    for (int i = 0; i < per / 8; ++i) {
+      const uint4 wo = __ldg(reinterpret_cast<const uint4*>(po) + i);
+      const uint4 wd = __ldg(reinterpret_cast<const uint4*>(pd) + i);
+      const uint32_t xo[4] = {wo.x, wo.y, wo.z, wo.w};
+      const uint32_t xd[4] = {wd.x, wd.y, wd.z, wd.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        sum = fmaf(unpack_lo<BF16>(xo[k]), unpack_lo<BF16>(xd[k]), sum);
+        sum = fmaf(unpack_hi<BF16>(xo[k]), unpack_hi<BF16>(xd[k]), sum);
+      }
+    }
+  }
+  sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+  sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+  sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+  if (part == 0 && r < a.S_q) a.delta[bh * a.S_q + r] = sum;
+}
+
+// ---------------------------------------------------------------------------------------
+// 3. dQ = scale * accumulator
+// ---------------------------------------------------------------------------------------
+struct FinishArgs {
+  const float* dq_accum;
+  void* dq;
+  int64_t sb, sh, ss;
+  int B, H, S_q, S_q_pad, D;
+  float scale;
+};
+
+template <bool BF16>
+__global__ void __launch_bounds__(256) bwd_finish_kernel(const FinishArgs a) {
+  // one thread converts 8 consecutive elements
+  const int per_row = a.D / 8;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t total = static_cast<int64_t>(a.B) * a.H * a.S_q * per_row;
+  if (idx >= total) return;
+  const int part = static_cast<int>(idx % per_row);
+  const int64_t row = idx / per_row;
+  const int r = static_cast<int>(row % a.S_q);
+  const int64_t bh = row / a.S_q;
+  const int h = static_cast<int>(bh % a.H);
+  const int b = static_cast<int>(bh / a.H);
+  const float4* src = reinterpret_cast<const float4*>(a.dq_accum + (bh * a.S_q_pad + r) * a.D + part * 8);
+  const float4 x = src[0], y = src[1];
+  uint4 w;
+  w.x = pack2<BF16>(x.x * a.scale, x.y * a.scale);
+  w.y = pack2<BF16>(x.z * a.scale, x.w * a.scale);
+  w.z = pack2<BF16>(y.x * a.scale, y.y * a.scale);
+  w.w = pack2<BF16>(y.z * a.scale, y.w * a.scale);
+  unsigned short* dst = reinterpret_cast<unsigned short*>(a.dq) + b * a.sb + h * a.sh + r * a.ss + part * 8;
+  *reinterpret_cast<uint4*>(dst) = w;
+}
+
+// ---------------------------------------------------------------------------------------
+// 2. main kernel
+// ---------------------------------------------------------------------------------------
+template <int D, bool BF16>
+__global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_constant__ BwdArgs a) {
+  using L = BwdSmem<D>;
+  constexpr int ST = L::kStages;
+  constexpr int kTmemCols = 512;
+  // tensor-memory columns
+  constexpr uint32_t kColS = 0, kColdP = 128, kColdV = 256, kColdK = 256 + D;
+  constexpr uint32_t kColdQ = (D == 64) ? 384 : kColdP;  // D = 128: dQ reuses the dP columns
+  constexpr int kFmt = BF16 ? 1 : 0;
+  constexpr uint32_t kIdescS = make_idesc_f16(128, 128, kFmt, false, false);
+  constexpr uint32_t kIdescT = make_idesc_f16(128, D, kFmt, true, true);    // dV, dK: A and B MN-major
+  constexpr uint32_t kIdescQ = make_idesc_f16(128, D, kFmt, false, true);   // dQ: A K-major, B MN-major
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem + L::kOffK;
+  uint8_t* sV = smem + L::kOffV;
+  uint8_t* sQ = smem + L::kOffQ;
+  uint8_t* sdO = smem + L::kOffdO;
+  uint8_t* sP = smem + L::kOffP;
+  uint8_t* sdS = smem + L::kOffdS;
+  float* sMask = reinterpret_cast<float*>(smem + L::kOffMask);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
+  uint64_t* kv_full = bars + 0;
+  uint64_t* sdp_full = bars + 1;   // S and dP are in tensor memory
+  uint64_t* pds_full = bars + 2;   // P and dS are in shared memory (256 arrivals)
+  uint64_t* dq_full = bars + 3;    // dQ tile is in tensor memory
+  uint64_t* dq_free = bars + 4;    // dQ tile has been read out (256 arrivals)
+  uint64_t* acc_full = bars + 5;   // dK / dV accumulation finished
+  uint64_t* qdo_full = bars + 6;
+  uint64_t* qdo_empty = qdo_full + ST;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(smem + L::kOffMisc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kOffMisc + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int kv_tile = blockIdx.x;
+  const int h = blockIdx.y;
+  const int b = blockIdx.z;
+  const int k0 = kv_tile * kTileN;
+  const int bh = b * a.H + h;
+
+  int k_limit = a.S_k;
+  if (a.mask_kind == FMHA_MASK_SEQLEN) {
+    const int len = reinterpret_cast<const int*>(a.mask)[b];
+    if (len > 0 && len < a.S_k) k_limit = len;
+  }
+  const int n_cols = min(kTileN, k_limit - k0);  // <= 0: this key tile is masked out entirely
+  const int n_q = (n_cols > 0) ? (a.S_q + kTileM - 1) / kTileM : 0;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(kv_full, 1);
+    mbar_init(sdp_full, 1);
+    mbar_init(pds_full, 256);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_free, 256);
+    mbar_init(acc_full, 1);
+    for (int s = 0; s < ST; ++s) {
+      mbar_init(qdo_full + s, 1);
+      mbar_init(qdo_empty + s, 1);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&a.tm_q);
+    tma_prefetch_desc(&a.tm_k);
+    tma_prefetch_desc(&a.tm_v);
+    tma_prefetch_desc(&a.tm_do);
+    tma_prefetch_desc(&a.tm_dk);
+    tma_prefetch_desc(&a.tm_dv);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_base_slot;
+  const WaitCtx wctx{abort_flag, a.status};
+
+  if (warp == 0) {
+    // ============================ TMA producer ======================================
+    if (lane == 0 && n_q > 0) {
+      mbar_arrive_expect_tx(kv_full, 2 * L::kTileBytes);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        tma_load_4d(sK + c * 16384, &a.tm_k, kv_full, c * 64, k0, h, b);
+        tma_load_4d(sV + c * 16384, &a.tm_v, kv_full, c * 64, k0, h, b);
+      }
+      for (int i = 0; i < n_q; ++i) {
+        const int s = i % ST;
+        if (i >= ST) mbar_wait(qdo_empty + s, ((i / ST) - 1) & 1, wctx, kSiteQdoEmpty);
+        mbar_arrive_expect_tx(qdo_full + s, 2 * L::kTileBytes);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          tma_load_4d(sQ + s * L::kTileBytes + c * 16384, &a.tm_q, qdo_full + s, c * 64, i * kTileM, h, b);
+          tma_load_4d(sdO + s * L::kTileBytes + c * 16384, &a.tm_do, qdo_full + s, c * 64, i * kTileM, h, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ============================ MMA issuer ========================================
+    if (lane == 0 && n_q > 0) {
+      const uint32_t tS = tmem_base + kColS, tdP = tmem_base + kColdP, tdV = tmem_base + kColdV,
+                     tdK = tmem_base + kColdK, tdQ = tmem_base + kColdQ;
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP), adS = smem_u32(sdS);
+      auto issue_s = [&](int i) {
+        const uint32_t aQ = smem_u32(sQ + (i % ST) * L::kTileBytes);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
+          umma_ss(tS, make_smem_desc_sw128(aQ + off, 16, 1024), make_smem_desc_sw128(aK + off, 16, 1024), kIdescS,
+                  kk > 0 ? 1u : 0u);
+        }
+      };
+      auto issue_dp = [&](int i) {
+        const uint32_t adO = smem_u32(sdO + (i % ST) * L::kTileBytes);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
+          umma_ss(tdP, make_smem_desc_sw128(adO + off, 16, 1024), make_smem_desc_sw128(aV + off, 16, 1024), kIdescS,
+                  kk > 0 ? 1u : 0u);
+        }
+      };
+      mbar_wait(kv_full, 0, wctx, kSiteKvFull);
+      mbar_wait(qdo_full + 0, 0, wctx, kSiteQdoFull);
+      tc_fence_after_sync();
+      issue_s(0);
+      issue_dp(0);
+      umma_commit(sdp_full);
+      for (int i = 0; i < n_q; ++i) {
+        const int s = i % ST;
+        const uint32_t aQ = smem_u32(sQ + s * L::kTileBytes);
+        const uint32_t adO = smem_u32(sdO + s * L::kTileBytes);
+        mbar_wait(pds_full, i & 1, wctx, kSitePdsFull);
+        tc_fence_after_sync();
+        // dV += P^T dO ; dK += dS^T Q : A is the [q x keys] tile read MN-major (keys contiguous),
+        // 16 query rows (2048 B) per k-step, the two 64-key halves 16 KB apart.
+#pragma unroll
+        for (int kk = 0; kk < kTileM / 16; ++kk) {
+          const uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
+          umma_ss(tdV, make_smem_desc_sw128(aP + kk * 2048, 16384, 1024),
+                  make_smem_desc_sw128(adO + kk * 2048, 16384, 1024), kIdescT, acc);
+        }
+#pragma unroll
+        for (int kk = 0; kk < kTileM / 16; ++kk) {
+          const uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
+          umma_ss(tdK, make_smem_desc_sw128(adS + kk * 2048, 16384, 1024),
+                  make_smem_desc_sw128(aQ + kk * 2048, 16384, 1024), kIdescT, acc);
+        }
+        umma_commit(qdo_empty + s);  // Q and dO of this stage are not read again (dQ needs dS and K only)
+        if (i > 0) {
+          mbar_wait(dq_free, (i - 1) & 1, wctx, kSiteDqFree);
+          tc_fence_after_sync();
+        }
+        // dQ tile = dS K : A K-major (keys along the row), B = K tile read MN-major
+#pragma unroll
+        for (int kk = 0; kk < kTileN / 16; ++kk) {
+          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
+          umma_ss(tdQ, make_smem_desc_sw128(adS + off, 16, 1024), make_smem_desc_sw128(aK + kk * 2048, 16384, 1024),
+                  kIdescQ, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(dq_full);
+        if (i + 1 < n_q) {
+          mbar_wait(qdo_full + ((i + 1) % ST), ((i + 1) / ST) & 1, wctx, kSiteQdoFull);
+          tc_fence_after_sync();
+          issue_s(i + 1);
+          if constexpr (D == 128) {
+            mbar_wait(dq_free, i & 1, wctx, kSiteDqFree);
+            tc_fence_after_sync();
+          }
+          issue_dp(i + 1);
+          umma_commit(sdp_full);
+        }
+      }
+      umma_commit(acc_full);
+    }
+  } else {
+    // ============================ compute warps =====================================
+    const int cw = warp - 2;             // 0..7
+    const int quad = warp & 3;           // tensor-memory lane quarter of this warp
+    const int half = cw >> 2;            // which 64 columns of the tile
+    const int row = quad * 32 + lane;
+    const int tid = threadIdx.x - 64;    // 0..255
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const float sl2 = a.scale_log2;
+    const uint32_t gbh = static_cast<uint32_t>(a.philox_bh_offset + bh);
+    const bool philox = a.dropout_kind == FMHA_DROPOUT_PHILOX;
+    const float dscale = philox ? a.dropout_scale : 1.0f;
+
+    if (n_q > 0 && a.mask_kind == FMHA_MASK_KEY_ADDITIVE && tid < kTileN) {
+      const int c = k0 + tid;
+      sMask[tid] = (c < a.S_k) ? reinterpret_cast<const float*>(a.mask)[static_cast<size_t>(b) * a.S_k + c] * kLog2eB : 0.f;
+    }
+    named_bar_sync(1, 256);
+
+    for (int i = 0; i < n_q; ++i) {
+      const int q_row = i * kTileM + row;
+      const bool row_ok = q_row < a.S_q;
+      // lse in the log2 domain; +inf for rows past the end makes their probabilities zero
+      const float lse2 = row_ok ? a.lse[static_cast<size_t>(bh) * a.S_q + q_row] * kLog2eB : INFINITY;
+      const float delta = row_ok ? a.delta[static_cast<size_t>(bh) * a.S_q + q_row] : 0.f;
+
+      mbar_wait(sdp_full, i & 1, wctx, kSiteSdpFull);
+      tc_fence_after_sync();
+#pragma unroll 1
+      for (int c2 = 0; c2 < 2; ++c2) {
+        const int cc = half * 2 + c2;   // 32-column chunk of the tile
+        const int cbase = cc * 32;
+        uint32_t rs[32], rp[32];
+        tmem_ld32(tmem_base + lane_addr + kColS + cbase, rs);
+        tmem_ld32(tmem_base + lane_addr + kColdP + cbase, rp);
+        tmem_wait_ld();
+        float p[32];
+        if (a.mask_kind == FMHA_MASK_KEY_ADDITIVE) {
+#pragma unroll
+          for (int k = 0; k < 32; ++k) p[k] = fast_exp2(fmaf(__uint_as_float(rs[k]), sl2, sMask[cbase + k] - lse2));
+        } else {
+#pragma unroll
+          for (int k = 0; k < 32; ++k) p[k] = fast_exp2(fmaf(__uint_as_float(rs[k]), sl2, -lse2));
+        }
+        if (cbase + 32 > n_cols) {
+#pragma unroll
+          for (int k = 0; k < 32; ++k)
+            if (cbase + k >= n_cols) p[k] = 0.f;
+        }
+        uint32_t keep01[8], keep23[8];  // 16-bit lane masks, two elements each
+        if (philox) {
+#pragma unroll
+          for (int d = 0; d < 2; ++d) {
+            const U4 draw = dropout_draw(a.philox_seed, a.philox_offset, gbh, static_cast<uint32_t>(q_row),
+                                         static_cast<uint32_t>((k0 + cbase) / 16 + d));
+            const uint32_t w[4] = {draw.x, draw.y, draw.z, draw.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const uint32_t keep = dropout_keep_bits(w[k], a.philox_thr);
+              keep01[d * 4 + k] = prmt(keep, 0u, 0x9988u);
+              keep23[d * 4 + k] = prmt(keep, 0u, 0xBBAAu);
+            }
+          }
+        }
+        // dS = P * (keep*c*dP - delta), computed in fp32; the keep decision of element e is bit
+        // (16*(e&1)) of its pair mask.
+        uint32_t pk_p[16], pk_ds[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+          float dp0 = __uint_as_float(rp[2 * k]), dp1 = __uint_as_float(rp[2 * k + 1]);
+          uint32_t pm = 0xffffffffu;
+          if (philox) {
+            pm = (k & 1) ? keep23[k >> 1] : keep01[k >> 1];
+            dp0 = (pm & 0x0000ffffu) ? dp0 * dscale : 0.f;
+            dp1 = (pm & 0xffff0000u) ? dp1 * dscale : 0.f;
+          }
+          const float ds0 = p[2 * k] * (dp0 - delta);
+          const float ds1 = p[2 * k + 1] * (dp1 - delta);
+          pk_p[k] = pack2<BF16>(p[2 * k], p[2 * k + 1]) & pm;
+          pk_ds[k] = pack2<BF16>(ds0, ds1);
+        }
+        uint8_t* tileP = sP + (cc / 2) * 16384;
+        uint8_t* tileS = sdS + (cc / 2) * 16384;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t off = sw128_offset(row, (cc % 2) * 4 + q);
+          *reinterpret_cast<uint4*>(tileP + off) = make_uint4(pk_p[q * 4], pk_p[q * 4 + 1], pk_p[q * 4 + 2], pk_p[q * 4 + 3]);
+          *reinterpret_cast<uint4*>(tileS + off) = make_uint4(pk_ds[q * 4], pk_ds[q * 4 + 1], pk_ds[q * 4 + 2], pk_ds[q * 4 + 3]);
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(pds_full);
+
+      // ---- dQ tile -> global accumulator --------------------------------------------
+      mbar_wait(dq_full, i & 1, wctx, kSiteDqFull);
+      tc_fence_after_sync();
+      {
+        float* dst = a.dq_accum + (static_cast<size_t>(bh) * a.S_q_pad + i * kTileM + row) * D + half * (D / 2);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tmem_base + lane_addr + kColdQ + half * (D / 2) + c * 32, r);
+          tmem_wait_ld();
+          if (*abort_flag == 0) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              red_add_v4(dst + c * 32 + q * 4, __uint_as_float(r[q * 4]), __uint_as_float(r[q * 4 + 1]),
+                         __uint_as_float(r[q * 4 + 2]), __uint_as_float(r[q * 4 + 3]));
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(dq_free);
+    }
+
+    // ---- epilogue: dK, dV -> 16-bit -> shared memory -> TMA store ----------------------
+    if (n_q > 0) {
+      mbar_wait(acc_full, 0, wctx, kSiteAccFull);
+      tc_fence_after_sync();
+    }
+    // sP / sdS are free (every MMA that read them has completed); dV goes to sP, dK to sdS.
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+      const uint32_t col = (which == 0 ? kColdV : kColdK) + half * (D / 2);
+      const float mul = (which == 0) ? dscale : a.scale;
+      uint8_t* stage = (which == 0) ? sP : sdS;
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        uint32_t r[32];
+        if (n_q > 0) {
+          tmem_ld32(tmem_base + lane_addr + col + c * 32, r);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int k = 0; k < 32; ++k) r[k] = 0u;
+        }
+        const int cc = (half * (D / 2) + c * 32) / 32;  // 32-element chunk within the D axis
+        uint8_t* tile = stage + (cc / 2) * 16384;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint4 w;
+          w.x = pack2<BF16>(__uint_as_float(r[q * 8 + 0]) * mul, __uint_as_float(r[q * 8 + 1]) * mul);
+          w.y = pack2<BF16>(__uint_as_float(r[q * 8 + 2]) * mul, __uint_as_float(r[q * 8 + 3]) * mul);
+          w.z = pack2<BF16>(__uint_as_float(r[q * 8 + 4]) * mul, __uint_as_float(r[q * 8 + 5]) * mul);
+          w.w = pack2<BF16>(__uint_as_float(r[q * 8 + 6]) * mul, __uint_as_float(r[q * 8 + 7]) * mul);
+          *reinterpret_cast<uint4*>(tile + sw128_offset(row, (cc % 2) * 4 + q)) = w;
+        }
+      }
+    }
+    fence_proxy_async_smem();
+    named_bar_sync(1, 256);
+    if (tid == 0) {
+      if (*abort_flag == 0) {
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          tma_store_4d(&a.tm_dv, sP + c * 16384, c * 64, k0, h, b);
+          tma_store_4d(&a.tm_dk, sdS + c * 16384, c * 64, k0, h, b);
+        }
+        tma_store_commit();
+      }
+      tma_store_wait_all();
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int k = 0; k < 20; ++k) __nanosleep(1000000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// launchers
+// ---------------------------------------------------------------------------------------
+template <int D, bool BF16>
+static int launch_bwd_impl(const BwdArgs& a, cudaStream_t stream) {
+  using L = BwdSmem<D>;
+  auto kfn = fmha_bwd_kernel<D, BF16>;
+  cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynBytes);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  dim3 grid((a.S_k + kTileN - 1) / kTileN, a.H, a.B);
+  kfn<<<grid, kBwdThreads, L::kDynBytes, stream>>>(a);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int launch_bwd(const BwdArgs& a, int D, int dtype, cudaStream_t stream) {
+  const bool bf = dtype == FMHA_DTYPE_BF16;
+  if (D == 64) return bf ? launch_bwd_impl<64, true>(a, stream) : launch_bwd_impl<64, false>(a, stream);
+  if (D == 128) return bf ? launch_bwd_impl<128, true>(a, stream) : launch_bwd_impl<128, false>(a, stream);
+  return static_cast<int>(cudaErrorInvalidValue);
+}
+
+int launch_bwd_prepare(const void* o, const fmha_tensor4& ot, const fmha_tensor4& dot, int B, int H, int S_q, int S_q_pad,
+                       int D, int dtype, float* delta, float* dq_accum, cudaStream_t stream) {
+  PrepArgs p;
+  p.o = ot.ptr; p.d_o = dot.ptr;
+  (void)o;
+  p.o_sb = ot.stride_b; p.o_sh = ot.stride_h; p.o_ss = ot.stride_s;
+  p.do_sb = dot.stride_b; p.do_sh = dot.stride_h; p.do_ss = dot.stride_s;
+  p.B = B; p.H = H; p.S_q = S_q; p.S_q_pad = S_q_pad; p.D = D;
+  p.delta = delta; p.dq_accum = dq_accum;
+  const int64_t threads = static_cast<int64_t>(B) * H * S_q_pad * 8;
+  const int block = 256;
+  const int64_t blocks = (threads + block - 1) / block;
+  if (dtype == FMHA_DTYPE_BF16) bwd_prepare_kernel<true><<<static_cast<unsigned>(blocks), block, 0, stream>>>(p);
+  else bwd_prepare_kernel<false><<<static_cast<unsigned>(blocks), block, 0, stream>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int launch_bwd_finish(const float* dq_accum, const fmha_tensor4& dq, int B, int H, int S_q, int S_q_pad, int D, int dtype,
+                      float scale, cudaStream_t stream) {
+  FinishArgs f;
+  f.dq_accum = dq_accum; f.dq = dq.ptr;
+  f.sb = dq.stride_b; f.sh = dq.stride_h; f.ss = dq.stride_s;
+  f.B = B; f.H = H; f.S_q = S_q; f.S_q_pad = S_q_pad; f.D = D; f.scale = scale;
+  const int64_t threads = static_cast<int64_t>(B) * H * S_q * (D / 8);
+  const int block = 256;
+  const int64_t blocks = (threads + block - 1) / block;
+  if (dtype == FMHA_DTYPE_BF16) bwd_finish_kernel<true><<<static_cast<unsigned>(blocks), block, 0, stream>>>(f);
+  else bwd_finish_kernel<false><<<static_cast<unsigned>(blocks), block, 0, stream>>>(f);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace fmha

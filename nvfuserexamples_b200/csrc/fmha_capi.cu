@@ -180,6 +180,94 @@ int fmha_sm100_fwd(const fmha_fwd_params* p, void* stream) {
   return FMHA_OK;
 }
 
+static size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
+
+int fmha_sm100_bwd_workspace_bytes(const fmha_bwd_params* p, size_t* bytes) {
+  if (p == nullptr || bytes == nullptr) return FMHA_ERR_BAD_ARG;
+  int rc = validate_common(p->struct_bytes, sizeof(fmha_bwd_params), p->dtype, p->B, p->H, p->S_q, p->S_k, p->D, p->scale);
+  if (rc != FMHA_OK) return rc;
+  const size_t bh = static_cast<size_t>(p->B) * p->H;
+  const size_t s_q_pad = (static_cast<size_t>(p->S_q) + kTileM - 1) / kTileM * kTileM;
+  *bytes = align256(bh * s_q_pad * p->D * sizeof(float)) + align256(bh * p->S_q * sizeof(float));
+  return FMHA_OK;
+}
+
+int fmha_sm100_bwd(const fmha_bwd_params* p, void* stream_) {
+  if (p == nullptr) return FMHA_ERR_BAD_ARG;
+  int rc = validate_common(p->struct_bytes, sizeof(fmha_bwd_params), p->dtype, p->B, p->H, p->S_q, p->S_k, p->D, p->scale);
+  if (rc != FMHA_OK) return rc;
+  if (p->mask_kind != FMHA_MASK_NONE && p->mask_kind != FMHA_MASK_KEY_ADDITIVE && p->mask_kind != FMHA_MASK_SEQLEN)
+    return FMHA_ERR_UNSUPPORTED;
+  if (p->dropout_kind != FMHA_DROPOUT_NONE && p->dropout_kind != FMHA_DROPOUT_PHILOX) return FMHA_ERR_UNSUPPORTED;
+  if (p->mask_kind != FMHA_MASK_NONE && p->mask == nullptr) return FMHA_ERR_BAD_ARG;
+  if (p->dropout_kind == FMHA_DROPOUT_PHILOX) {
+    if (!(p->p_drop >= 0.f && p->p_drop < 1.f)) return FMHA_ERR_BAD_ARG;
+    if (p->philox_offset >> 32) return FMHA_ERR_BAD_ARG;
+  }
+  if (p->B == 0 || p->H == 0) return FMHA_OK;
+  if (p->S_q == 0 && p->S_k == 0) return FMHA_OK;
+  if (p->S_k == 0 || p->S_q == 0) return FMHA_ERR_BAD_ARG;
+  if (!tensor_ok(p->q, p->B, p->H) || !tensor_ok(p->k, p->B, p->H) || !tensor_ok(p->v, p->B, p->H) ||
+      !tensor_ok(p->o, p->B, p->H) || !tensor_ok(p->d_o, p->B, p->H) || !tensor_ok(p->dq, p->B, p->H) ||
+      !tensor_ok(p->dk, p->B, p->H) || !tensor_ok(p->dv, p->B, p->H) || p->lse == nullptr)
+    return FMHA_ERR_BAD_ARG;
+  size_t need = 0;
+  rc = fmha_sm100_bwd_workspace_bytes(p, &need);
+  if (rc != FMHA_OK) return rc;
+  if (p->workspace == nullptr || p->workspace_bytes < need || (reinterpret_cast<uintptr_t>(p->workspace) & 255))
+    return FMHA_ERR_BAD_ARG;
+  rc = check_device();
+  if (rc != FMHA_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+
+  const int s_q_pad = (p->S_q + kTileM - 1) / kTileM * kTileM;
+  const size_t bh = static_cast<size_t>(p->B) * p->H;
+  float* dq_accum = reinterpret_cast<float*>(p->workspace);
+  float* delta = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p->workspace) + align256(bh * s_q_pad * p->D * sizeof(float)));
+
+  BwdArgs a;
+  std::memset(&a, 0, sizeof(a));
+  const fmha_tensor4 tq = sanitized(p->q, p->B, p->H, p->S_q, p->D), tk = sanitized(p->k, p->B, p->H, p->S_k, p->D),
+                     tv = sanitized(p->v, p->B, p->H, p->S_k, p->D), to = sanitized(p->o, p->B, p->H, p->S_q, p->D),
+                     tdo = sanitized(p->d_o, p->B, p->H, p->S_q, p->D), tdq = sanitized(p->dq, p->B, p->H, p->S_q, p->D),
+                     tdk = sanitized(p->dk, p->B, p->H, p->S_k, p->D), tdv = sanitized(p->dv, p->B, p->H, p->S_k, p->D);
+  if ((rc = make_tmap(&a.tm_q, tq, p->dtype, p->B, p->H, p->S_q, p->D, kTileM))) return rc;
+  if ((rc = make_tmap(&a.tm_k, tk, p->dtype, p->B, p->H, p->S_k, p->D, kTileN))) return rc;
+  if ((rc = make_tmap(&a.tm_v, tv, p->dtype, p->B, p->H, p->S_k, p->D, kTileN))) return rc;
+  if ((rc = make_tmap(&a.tm_do, tdo, p->dtype, p->B, p->H, p->S_q, p->D, kTileM))) return rc;
+  if ((rc = make_tmap(&a.tm_dk, tdk, p->dtype, p->B, p->H, p->S_k, p->D, kTileN))) return rc;
+  if ((rc = make_tmap(&a.tm_dv, tdv, p->dtype, p->B, p->H, p->S_k, p->D, kTileN))) return rc;
+  a.B = p->B; a.H = p->H; a.S_q = p->S_q; a.S_k = p->S_k;
+  a.scale = p->scale;
+  a.scale_log2 = p->scale * 1.4426950408889634f;
+  a.lse = p->lse;
+  a.delta = delta;
+  a.dq_accum = dq_accum;
+  a.S_q_pad = s_q_pad;
+  a.mask_kind = p->mask_kind;
+  a.mask = p->mask;
+  a.dropout_kind = p->dropout_kind;
+  a.dropout_scale = 1.0f;
+  if (p->dropout_kind == FMHA_DROPOUT_PHILOX) {
+    const int thr = dropout_threshold(p->p_drop);
+    a.philox_thr = static_cast<uint32_t>(thr);
+    a.dropout_scale = 128.0f / static_cast<float>(128 - thr);
+    if (thr == 0) a.dropout_kind = FMHA_DROPOUT_NONE;
+  }
+  a.philox_seed = p->philox_seed;
+  a.philox_offset = static_cast<uint32_t>(p->philox_offset);
+  a.philox_bh_offset = p->philox_bh_offset;
+  a.status = p->status;
+
+  int e = launch_bwd_prepare(nullptr, to, tdo, p->B, p->H, p->S_q, s_q_pad, p->D, p->dtype, delta, dq_accum, stream);
+  if (e != 0) return cuda_fail(static_cast<cudaError_t>(e));
+  e = launch_bwd(a, p->D, p->dtype, stream);
+  if (e != 0) return cuda_fail(static_cast<cudaError_t>(e));
+  e = launch_bwd_finish(dq_accum, tdq, p->B, p->H, p->S_q, s_q_pad, p->D, p->dtype, p->scale, stream);
+  if (e != 0) return cuda_fail(static_cast<cudaError_t>(e));
+  return FMHA_OK;
+}
+
 int fmha_sm100_check_status(int32_t* status, void* stream, int32_t* host_copy) {
   if (status == nullptr) return FMHA_ERR_BAD_ARG;
   int32_t h[4] = {0, 0, 0, 0};

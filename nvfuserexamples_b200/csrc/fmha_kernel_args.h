@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "../../include/fmha_sm100.h"
+
 namespace fmha {
 
 constexpr int kTileM = 128;  // query rows per CTA tile
@@ -62,5 +64,9 @@ struct BwdArgs {
 // Launchers (defined in the .cu files).  Return a cudaError_t as int.
 int launch_fwd(const FwdArgs& a, int D, int dtype, bool legacy, bool p_via_smem, cudaStream_t stream);
 int launch_bwd(const BwdArgs& a, int D, int dtype, cudaStream_t stream);
+int launch_bwd_prepare(const void* o, const fmha_tensor4& ot, const fmha_tensor4& dot, int B, int H, int S_q, int S_q_pad,
+                       int D, int dtype, float* delta, float* dq_accum, cudaStream_t stream);
+int launch_bwd_finish(const float* dq_accum, const fmha_tensor4& dq, int B, int H, int S_q, int S_q_pad, int D, int dtype,
+                      float scale, cudaStream_t stream);
 
 }  // namespace fmha
