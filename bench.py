@@ -1,0 +1,388 @@
+#!/usr/bin/env python
+"""Benchmark of the fused multi-head-attention training step (forward + backward) at the
+BERT-large shape, on N GPUs of one node.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--scaling weak|strong]
+
+One "step" is one forward and one backward pass of the hot path over one batch of synthetic
+input (B=32, H=16, S=512, D=64, fp16, valid lengths uniform in [256,512], Philox dropout 0.1).
+With N > 1 (launched under torchrun, one rank per GPU) every rank works on its own shard of the
+batch x heads axis; there is no collective on the data path, only a barrier and a MAX of the
+per-rank device times.  Rank 0 prints ONE JSON line.
+
+What is counted: `value` is EXECUTED TFLOP/s — 14*H*S_q*S_k_tiles*D per batch element, where
+S_k_tiles is the key length rounded up to the 128-key tiles the kernels actually visit (key
+tiles that lie wholly in the padding are skipped, which is exact).  The dense-equivalent figure
+(14*B*H*S^2*D over the same time) is reported beside it.
+
+`--impl reference` times the reference's own CPU path for the same step: the eager composite of
+its test scripts (matmul, scale, mask, softmax, dropout, matmul) plus autograd, on the host
+cores, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOAD = "bert_large_train"
+B0, H, S, D = 32, 16, 512, 64
+LEN_RANGE = (256, 512)
+P_DROP = 0.1
+METRIC = "fused MHA fwd+bwd TFLOP/s at BERT-large shape (executed flops)"
+# ncu capture of fmha_bwd_kernel<64,fp16> at this workload (profiles/bwd_kernel_bert_large_train.md):
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, bytes.  None until captured.
+BWD_KERNEL_DRAM_TRAFFIC = None
+
+
+def executed_flops(lens, h, s_q, d, mult):
+    """mult * h * s_q * (key length rounded up to 128) * d summed over the batch."""
+    return float(sum(mult * h * s_q * (math.ceil(int(n) / 128) * 128) * d for n in lens))
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(tflops=float(p["bf16_tflops"]), tflops_sustained=float(p.get("bf16_tflops_sustained", 0.0)),
+                    hbm_gbs=float(p["hbm_gbs"]), source="measured")
+    return dict(tflops=1590.0, tflops_sustained=1400.0, hbm_gbs=6650.0, source="fallback")
+
+
+class ClockSampler(threading.Thread):
+    """Polls SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop_evt = threading.Event()
+
+    def run(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            names = {
+                getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+                getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+                getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+                getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+                getattr(nv, "nvmlClocksEventReasonHwPowerBrakeSlowdown", 0x80): "hw_power_brake_slowdown",
+            }
+            get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+            while not self._stop_evt.is_set():
+                self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                r = get_reasons(h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+                time.sleep(0.002)
+        except Exception as e:  # NVML missing: report that instead of numbers
+            self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
+
+    def stop(self):
+        self._stop_evt.set()
+        self.join(2.0)
+        med = statistics.median(self.samples) if self.samples else None
+        return dict(sm_mhz=med, sm_max_mhz=self.max_mhz, reasons=sorted(self.reasons), samples=len(self.samples))
+
+
+# ------------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the eager composite + autograd on the host cores
+# ------------------------------------------------------------------------------------------
+def cpu_composite_step(sample_b: int, seed: int):
+    """Builds a closure running one fwd+bwd of the composite on `sample_b` batch elements of the
+    workload on the CPU, and the dense flops of that sample."""
+    import torch
+    from oracle import composite, philox
+    x = composite.make_inputs(sample_b, H, S, D, torch.float16, LEN_RANGE, seed, with_do=True)
+    add = composite.padding_add_mask(x["lens"], S)
+    keep = torch.from_numpy(philox.dropout_keep_mask(1, 0, 0, sample_b * H, S, S, P_DROP)).reshape(sample_b, H, S, S).float()
+    ks = philox.keep_scale(P_DROP)
+
+    def step():
+        return composite.attention_grads_fp32(x["q"], x["k"], x["v"], x["d_o"], add_mask=add, keep=keep, keep_scale=ks)
+
+    return step, 14.0 * sample_b * H * S * S * D
+
+
+def time_cpu(step, flops, warmup, steps):
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    return flops / dt / 1e12, dt
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    import torch
+    sample_b = 2
+    step, flops = cpu_composite_step(sample_b, 1004)
+    steps = max(1, min(args.steps, 20))
+    warm = max(1, min(args.warmup, 3))
+    tf, dt = time_cpu(step, flops, warm, steps)
+    cores = torch.get_num_threads()
+    sample = f"{sample_b} of {B0} batch elements (x{H} heads, S={S}, D={D}), fp32 composite + autograd, {steps} timed steps"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": steps,
+        "warmup": warm, "ms_per_step": dt * 1e3 * (B0 / sample_b), "higher_is_better": True, "scaling": args.scaling,
+        "vs_baseline": None, "dtype": "fp16 inputs, fp32 math", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "B": B0, "H": H, "S": S, "D": D, "p_drop": P_DROP,
+                   "flops_counted": "dense 14*B*H*S^2*D of the sample; ms_per_step scaled to the full batch"},
+        "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }), flush=True)
+
+
+# ------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------
+def run_ours(args, rank, world, local_rank):
+    import ctypes as C
+
+    import torch
+    import torch.distributed as dist
+
+    from nvfuserexamples_b200 import capi, sharding
+    from oracle import composite  # input recipe only (shapes, seeds); never on the timed path
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device (the kernels have no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    # ---- this rank's shard ---------------------------------------------------------------
+    if args.scaling == "weak":
+        b_global = B0 * world          # per-GPU work fixed: every rank owns B0 batch elements
+    else:
+        b_global = B0                  # total work fixed
+    shard = sharding.make_shard(b_global, H, world, rank)
+    if not shard.whole_batches or shard.bh_count == 0:
+        raise SystemExit("bench.py: the batch does not split into whole batch elements per rank")
+    b_loc = shard.bh_count // H
+    n_sets = 2
+    sets = []
+    for i in range(n_sets):
+        x = composite.make_inputs(b_loc, H, S, D, torch.float16, LEN_RANGE, 1004 + 17 * rank + i, with_do=True)
+        sets.append({k: v.to(dev) for k, v in x.items()})
+    lens_host = [s["lens"].cpu().tolist() for s in sets]
+    lib = capi.load()
+    stream = torch.cuda.current_stream(dev)
+    sp = stream.cuda_stream
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+
+    # persistent outputs and parameter blocks (no allocation inside the timed region)
+    plans = []
+    for i, x in enumerate(sets):
+        o = torch.empty_like(x["q"])
+        lse = torch.empty(b_loc, H, S, dtype=torch.float32, device=dev)
+        dq, dk, dv = (torch.empty_like(x["q"]) for _ in range(3))
+        fp = capi.FwdParams()
+        fp.struct_bytes = C.sizeof(capi.FwdParams)
+        fp.dtype = capi.DTYPE_F16
+        fp.B, fp.H, fp.S_q, fp.S_k, fp.D = b_loc, H, S, S, D
+        fp.scale = 1.0 / math.sqrt(D)
+        fp.q, fp.k, fp.v, fp.o = (capi._t4(t) for t in (x["q"], x["k"], x["v"], o))
+        fp.lse = lse.data_ptr()
+        fp.mask_kind, fp.mask = capi.MASK_SEQLEN, x["lens"].data_ptr()
+        fp.dropout_kind, fp.p_drop = capi.DROPOUT_PHILOX, P_DROP
+        fp.philox_seed, fp.philox_offset, fp.philox_bh_offset = 0x5EED0004, i, shard.bh_offset
+        fp.status = status.data_ptr()
+        bp = capi.bwd_params(x["d_o"], x["q"], x["k"], x["v"], o, lse, dq, dk, dv, mask_kind=capi.MASK_SEQLEN,
+                             mask=x["lens"], p_drop=P_DROP, seed=0x5EED0004, offset=i, bh_offset=shard.bh_offset,
+                             status=status)
+        ws = torch.empty(capi.bwd_workspace_bytes(bp), dtype=torch.uint8, device=dev)
+        bp.workspace, bp.workspace_bytes = ws.data_ptr(), ws.numel()
+        plans.append(dict(fp=fp, bp=bp, keep=(o, lse, dq, dk, dv, ws)))
+
+    def step(i):
+        pl = plans[i % n_sets]
+        rc = lib.fmha_sm100_fwd(C.byref(pl["fp"]), sp)
+        rc |= lib.fmha_sm100_bwd(C.byref(pl["bp"]), sp)
+        if rc != 0:
+            raise RuntimeError(f"kernel library call failed: {rc} {capi.strerror(rc)}")
+
+    def sync_all():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+
+    for i in range(args.warmup):
+        step(i)
+    capi.check_status(status)
+
+    # ---- timed region: exactly K steps --------------------------------------------------------
+    sampler = ClockSampler(local_rank)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    sampler.start()
+    e0.record(stream)
+    for i in range(args.steps):
+        step(i)
+    e1.record(stream)
+    sync_all()
+    clocks = sampler.stop()
+    ms_total = e0.elapsed_time(e1)
+    t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = t.item() / args.steps
+    capi.check_status(status)
+
+    exe_step = [executed_flops(l, H, S, D, 14.0) for l in lens_host]           # per input set, this rank
+    exe_mean = sum(exe_step[i % n_sets] for i in range(args.steps)) / args.steps
+    exe_all = torch.tensor([exe_mean], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(exe_all, op=dist.ReduceOp.SUM)
+    value = exe_all.item() / (ms_step * 1e-3) / 1e12
+    dense_all = 14.0 * b_loc * world * H * S * S * D
+    dense_value = dense_all / (ms_step * 1e-3) / 1e12
+
+    # ---- kernel-level numbers (rank 0 only needs them, but every rank runs the same code) ------
+    def time_calls(fn, n):
+        for i in range(3):
+            fn(i)
+        torch.cuda.synchronize(dev)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for i in range(n):
+            fn(i)
+        b.record(stream)
+        torch.cuda.synchronize(dev)
+        return a.elapsed_time(b) / n
+
+    kn = max(20, min(args.steps, 200))
+    fwd_ms = time_calls(lambda i: lib.fmha_sm100_fwd(C.byref(plans[i % n_sets]["fp"]), sp), kn)
+    for pl in plans:  # main backward kernel alone: skip the delta/clear and the dQ conversion kernels
+        pl["bp_main"] = capi.BwdParams.from_buffer_copy(pl["bp"])
+        pl["bp_main"].flags = capi.FLAG_BWD_SKIP_PREPARE | capi.FLAG_BWD_SKIP_FINISH
+    bwd_main_ms = time_calls(lambda i: lib.fmha_sm100_bwd(C.byref(plans[i % n_sets]["bp_main"]), sp), kn)
+    bwd_all_ms = time_calls(lambda i: lib.fmha_sm100_bwd(C.byref(plans[i % n_sets]["bp"]), sp), kn)
+    pk = peaks()
+    exe_bwd = sum(executed_flops(l, H, S, D, 10.0) for l in lens_host) / n_sets
+    exe_fwd = sum(executed_flops(l, H, S, D, 4.0) for l in lens_host) / n_sets
+    ach = exe_bwd / (bwd_main_ms * 1e-3) / 1e12
+    roofline = {"kernel": "fmha_bwd_kernel<64,fp16>", "bound": "tensor", "achieved": ach, "peak": pk["tflops"],
+                "unit": "TFLOP/s", "frac": ach / pk["tflops"], "traffic": BWD_KERNEL_DRAM_TRAFFIC,
+                "peak_source": f"{pk['source']} bf16 burst", "ms_per_launch": bwd_main_ms,
+                "algorithmic_flops_per_launch": exe_bwd}
+    ach_f = exe_fwd / (fwd_ms * 1e-3) / 1e12
+    roofline_fwd = {"kernel": "fmha_fwd_kernel<64,fp16>", "bound": "tensor", "achieved": ach_f, "peak": pk["tflops"],
+                    "unit": "TFLOP/s", "frac": ach_f / pk["tflops"], "ms_per_launch": fwd_ms}
+
+    # ---- end to end through the operator layer, host buffers in and out --------------------------
+    import mha_manual  # noqa: F401
+    ops = torch.ops.mha_manual
+    host = {k: sets[0][k].cpu().pin_memory() for k in ("q", "k", "v", "d_o")}
+    host_lens = sets[0]["lens"].cpu().pin_memory()
+    host_out = [torch.empty_like(host["q"]).pin_memory() for _ in range(4)]
+    h2d = sum(t.numel() * t.element_size() for t in host.values()) + host_lens.numel() * 4
+    d2h = sum(t.numel() * t.element_size() for t in host_out)
+
+    def e2e_step():
+        q, k, v, d_o = (host[n].to(dev, non_blocking=True) for n in ("q", "k", "v", "d_o"))
+        lens = host_lens.to(dev, non_blocking=True)
+        o, lse = ops.fmha_fwd(q, k, v, None, lens, P_DROP, 0x5EED0004, 0, None, shard.bh_offset)
+        dq, dk, dv = ops.fmha_bwd(d_o, q, k, v, o, lse, None, lens, P_DROP, 0x5EED0004, 0, None, shard.bh_offset)
+        for dst, src in zip(host_out, (o, dq, dk, dv)):
+            dst.copy_(src, non_blocking=True)
+
+    e2e_n = max(3, min(args.steps, 20))
+    for _ in range(2):
+        e2e_step()
+    sync_all()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    for _ in range(e2e_n):
+        e2e_step()
+    b.record(stream)
+    sync_all()
+    te = torch.tensor([a.elapsed_time(b) / e2e_n], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_exe = torch.tensor([exe_step[0]], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(e2e_exe, op=dist.ReduceOp.SUM)
+    e2e_value = e2e_exe.item() / (te.item() * 1e-3) / 1e12
+
+    # ---- CPU baseline (N = 1 only, bounded sample) ---------------------------------------------------
+    cpu = None
+    if rank == 0 and world == 1:
+        cstep, cflops = cpu_composite_step(2, 1004)
+        n = 0
+        cstep()
+        t0 = time.perf_counter()
+        while True:
+            cstep()
+            n += 1
+            if time.perf_counter() - t0 > 10.0 or n >= 40:
+                break
+        cdt = (time.perf_counter() - t0) / n
+        cpu = {"value": cflops / cdt / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+               "sample": f"2 of {B0} batch elements (x{H} heads, S={S}, D={D}): fp32 eager composite + autograd, "
+                         f"{n} iterations, {cdt * 1e3:.1f} ms each; dense flops"}
+
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling,
+            "vs_baseline": None, "dtype": "fp16 operands, fp32 accumulate", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "B_per_gpu": b_loc, "global_batch": b_loc * world, "H": H, "S": S, "D": D,
+                       "p_drop": P_DROP, "valid_len": list(LEN_RANGE), "parallelism": f"bh-shard x{world}, no collective",
+                       "l2": "335 MB touched per step (> 126 MB L2), 2 rotating input sets",
+                       "flops_counted": "executed: 14*H*S*ceil128(len_b)*D per batch element"},
+            "dense_equiv_tflops": dense_value,
+            "pct_of_measured_bf16_peak": 100.0 * value / (pk["tflops"] * world),
+            "roofline": roofline, "roofline_fwd": roofline_fwd,
+            "kernel_ms": {"fwd": fwd_ms, "bwd_main": bwd_main_ms, "bwd_all_three": bwd_all_ms},
+            "cpu_baseline": cpu,
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": te.item(), "api": "torch.ops.mha_manual.fmha_fwd + fmha_bwd on pinned host buffers"},
+            "gpu_launches": 4 * args.steps,
+            "clocks": clocks,
+        }), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        raise SystemExit("bench.py: --gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+    if args.impl == "reference":
+        run_reference(args, rank)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

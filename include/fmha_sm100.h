@@ -112,8 +112,13 @@ typedef struct {
 } fmha_fwd_params;
 
 enum {
-  FMHA_FLAG_P_VIA_SMEM = 1 /* stage the probability tile through shared memory instead of
-                              tensor memory for the second GEMM (slower; diagnostic) */
+  FMHA_FLAG_P_VIA_SMEM = 1, /* forward: stage the probability tile through shared memory instead
+                               of tensor memory for the second GEMM (slower; diagnostic) */
+  /* backward, measurement aids: launch only part of the three-kernel sequence so that the main
+     kernel can be timed alone.  The workspace must have been prepared by an earlier full call;
+     results of such partial calls are not meaningful. */
+  FMHA_FLAG_BWD_SKIP_PREPARE = 2,
+  FMHA_FLAG_BWD_SKIP_FINISH = 4
 };
 
 typedef struct {
@@ -166,6 +171,12 @@ int fmha_sm100_philox_mask_device(uint64_t seed, uint64_t offset, int32_t bh_off
 /* Synchronises `stream`, reads the 4-word device status block and clears it.
    Returns FMHA_OK or FMHA_ERR_DEVICE_TIMEOUT; host_copy (optional int32[4]) receives the words. */
 int fmha_sm100_check_status(int32_t* status, void* stream, int32_t* host_copy);
+
+/* Failure-detection self test (no counterpart in the reference): launches one CTA that waits
+   on a barrier nothing ever signals, so the bounded wait every kernel uses runs out (about
+   0.4 s), records wait site 900 in `status` and returns normally; the context stays usable.
+   Follow with fmha_sm100_check_status, which then reports FMHA_ERR_DEVICE_TIMEOUT. */
+int fmha_sm100_selftest_wait_timeout(int32_t* status, void* stream);
 
 /* Text for a status code. Never NULL. */
 const char* fmha_sm100_strerror(int code);

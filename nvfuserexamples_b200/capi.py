@@ -26,11 +26,14 @@ DTYPE_F16, DTYPE_BF16 = 0, 1
 MASK_NONE, MASK_DENSE_KEEP, MASK_DENSE_ADDITIVE, MASK_KEY_ADDITIVE, MASK_SEQLEN = 0, 1, 2, 3, 4
 DROPOUT_NONE, DROPOUT_DENSE, DROPOUT_PHILOX = 0, 1, 2
 FLAG_P_VIA_SMEM = 1
+FLAG_BWD_SKIP_PREPARE = 2
+FLAG_BWD_SKIP_FINISH = 4
 
 EXPORTS = [
     "fmha_sm100_fwd", "fmha_sm100_bwd", "fmha_sm100_bwd_workspace_bytes", "fmha_sm100_dropout_threshold",
     "fmha_sm100_philox_mask_host", "fmha_sm100_philox_mask_device", "fmha_sm100_check_status",
     "fmha_sm100_strerror", "fmha_sm100_last_cuda_error", "fmha_sm100_abi_version",
+    "fmha_sm100_selftest_wait_timeout",
 ]
 
 
@@ -106,6 +109,8 @@ def load() -> C.CDLL:
     lib.fmha_sm100_philox_mask_device.restype = C.c_int
     lib.fmha_sm100_check_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]
     lib.fmha_sm100_check_status.restype = C.c_int
+    lib.fmha_sm100_selftest_wait_timeout.argtypes = [C.c_void_p, C.c_void_p]
+    lib.fmha_sm100_selftest_wait_timeout.restype = C.c_int
     lib.fmha_sm100_strerror.argtypes = [C.c_int]
     lib.fmha_sm100_strerror.restype = C.c_char_p
     lib.fmha_sm100_last_cuda_error.restype = C.c_int
@@ -205,7 +210,7 @@ def fwd(q, k, v, *, mask_kind=MASK_NONE, mask=None, dropout_kind=DROPOUT_NONE, d
 
 
 def bwd_params(d_o, q, k, v, o, lse, dq, dk, dv, *, mask_kind=MASK_NONE, mask=None, p_drop=0.0, seed=0, offset=0,
-               bh_offset=0, scale=None, status=None) -> BwdParams:
+               bh_offset=0, scale=None, status=None, flags=0) -> BwdParams:
     B, H, S_q, D = _dims(q)
     S_k = _dims(k)[2]
     p = BwdParams()
@@ -222,6 +227,7 @@ def bwd_params(d_o, q, k, v, o, lse, dq, dk, dv, *, mask_kind=MASK_NONE, mask=No
     p.p_drop = p_drop
     p.philox_seed, p.philox_offset, p.philox_bh_offset = seed, offset, bh_offset
     p.status = _ptr(status)
+    p.flags = flags
     return p
 
 
@@ -273,3 +279,9 @@ def check_status(status) -> list:
     if code != FMHA_OK:
         raise FmhaError(code, "fmha_sm100_check_status", f"{strerror(code)}; words {list(words)}")
     return list(words)
+
+
+def selftest_wait_timeout(status) -> None:
+    """Launches the library's bounded-wait self test on the current stream (see the header)."""
+    _check(load().fmha_sm100_selftest_wait_timeout(status.data_ptr(), _stream_ptr(status.device)),
+           "fmha_sm100_selftest_wait_timeout")

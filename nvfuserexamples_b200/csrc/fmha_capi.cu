@@ -13,6 +13,7 @@
 #include "../../include/fmha_sm100.h"
 #include "fmha_kernel_args.h"
 #include "philox.cuh"
+#include "sm100_ptx.cuh"
 
 namespace fmha {
 
@@ -259,12 +260,17 @@ int fmha_sm100_bwd(const fmha_bwd_params* p, void* stream_) {
   a.philox_bh_offset = p->philox_bh_offset;
   a.status = p->status;
 
-  int e = launch_bwd_prepare(nullptr, to, tdo, p->B, p->H, p->S_q, s_q_pad, p->D, p->dtype, delta, dq_accum, stream);
-  if (e != 0) return cuda_fail(static_cast<cudaError_t>(e));
+  int e = 0;
+  if (!(p->flags & FMHA_FLAG_BWD_SKIP_PREPARE)) {
+    e = launch_bwd_prepare(nullptr, to, tdo, p->B, p->H, p->S_q, s_q_pad, p->D, p->dtype, delta, dq_accum, stream);
+    if (e != 0) return cuda_fail(static_cast<cudaError_t>(e));
+  }
   e = launch_bwd(a, p->D, p->dtype, stream);
   if (e != 0) return cuda_fail(static_cast<cudaError_t>(e));
-  e = launch_bwd_finish(dq_accum, tdq, p->B, p->H, p->S_q, s_q_pad, p->D, p->dtype, p->scale, stream);
-  if (e != 0) return cuda_fail(static_cast<cudaError_t>(e));
+  if (!(p->flags & FMHA_FLAG_BWD_SKIP_FINISH)) {
+    e = launch_bwd_finish(dq_accum, tdq, p->B, p->H, p->S_q, s_q_pad, p->D, p->dtype, p->scale, stream);
+    if (e != 0) return cuda_fail(static_cast<cudaError_t>(e));
+  }
   return FMHA_OK;
 }
 
@@ -345,6 +351,29 @@ extern "C" int fmha_sm100_philox_mask_device(uint64_t seed, uint64_t offset, int
   const int blocks = static_cast<int>(std::min<size_t>((total + threads - 1) / threads, 148 * 16));
   fmha::philox_mask_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
       seed, static_cast<uint32_t>(offset), bh_offset, n_bh, S_q, S_k, thr, out);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e);
+  return FMHA_OK;
+}
+
+namespace fmha {
+// One thread waits on an mbarrier that has no other participant: exercises the bounded wait.
+__global__ void selftest_wait_kernel(int* status) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  abort_flag = 0;
+  mbar_init(&bar, 1);
+  mbar_fence_init();
+  const WaitCtx ctx{&abort_flag, status};
+  mbar_wait(&bar, 0, ctx, 900);
+}
+}  // namespace fmha
+
+extern "C" int fmha_sm100_selftest_wait_timeout(int32_t* status, void* stream) {
+  if (status == nullptr) return FMHA_ERR_BAD_ARG;
+  const int rc = check_device();
+  if (rc != FMHA_OK) return rc;
+  fmha::selftest_wait_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e);
   return FMHA_OK;

@@ -1,0 +1,105 @@
+"""Backward parity on the GPU against autograd through the fp32 composite (the reference has
+no backward pass), through the C ABI."""
+import pytest
+import torch
+
+from nvfuserexamples_b200 import api, capi, sharding
+from oracle import composite
+from tests import helpers
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [
+    (2, 2, 128, 128, 64, torch.float16),
+    (1, 2, 384, 256, 64, torch.float16),
+    (2, 2, 512, 512, 64, torch.float16),     # BERT-large training sequence length
+    (2, 2, 200, 333, 64, torch.float16),
+    (1, 2, 256, 256, 128, torch.float16),
+    (1, 2, 77, 300, 128, torch.bfloat16),
+    (2, 2, 384, 384, 64, torch.bfloat16),
+]
+
+
+def _run(dev, B, H, S_q, S_k, D, dtype, mask, p_drop, seed=1):
+    q, k, v, d_o, lens = helpers.randn_like_config(B, H, S_q, S_k, D, dtype, seed=seed, device=dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    kw, okw = {}, {}
+    if mask == "seqlen":
+        kw["seqlens"], okw["lens"] = lens, lens
+    elif mask == "key":
+        add = composite.padding_add_mask(lens.cpu(), S_k).reshape(B, S_k).to(dev)
+        kw["mask"], okw["add_mask"] = add, add
+    o, lse = api.fmha_forward(q, k, v, p_drop=p_drop, seed=77, offset=2, status=status, **kw)
+    dq, dk, dv = api.fmha_backward(d_o, q, k, v, o, lse, p_drop=p_drop, seed=77, offset=2, status=status, **kw)
+    assert capi.check_status(status) == [0, 0, 0, 0]
+    ref, add, keep, ks = helpers.oracle_forward(q, k, v, p_drop=p_drop, seed=77, offset=2, **okw)
+    rdq, rdk, rdv = helpers.oracle_backward(q, k, v, d_o, add=add, keep=keep, ks=ks)
+    helpers.assert_close(o, ref["o"], "o", dtype)
+    helpers.assert_close(dq, rdq, "dq", dtype)
+    helpers.assert_close(dk, rdk, "dk", dtype)
+    helpers.assert_close(dv, rdv, "dv", dtype)
+
+
+@pytest.mark.parametrize("B,H,S_q,S_k,D,dtype", SHAPES)
+@pytest.mark.parametrize("mask", ["none", "seqlen", "key"])
+def test_backward_matches_autograd_oracle(cuda_device, B, H, S_q, S_k, D, dtype, mask):
+    _run(cuda_device, B, H, S_q, S_k, D, dtype, mask, 0.0)
+
+
+@pytest.mark.parametrize("D,dtype,p", [(64, torch.float16, 0.1), (128, torch.bfloat16, 0.25), (64, torch.float16, 0.5)])
+def test_backward_with_philox_dropout(cuda_device, D, dtype, p):
+    _run(cuda_device, 2, 2, 384, 384, D, dtype, "seqlen", p)
+
+
+def test_masked_out_key_tiles_get_zero_gradients(cuda_device):
+    B, H, S, D = 2, 2, 384, 64
+    q, k, v, d_o, _ = helpers.randn_like_config(B, H, S, S, D, torch.float16, seed=3, device=cuda_device)
+    lens = torch.tensor([100, 384], dtype=torch.int32, device=cuda_device)
+    o, lse = api.fmha_forward(q, k, v, seqlens=lens)
+    dq, dk, dv = api.fmha_backward(d_o, q, k, v, o, lse, seqlens=lens)
+    assert (dk[0, :, 100:] == 0).all() and (dv[0, :, 100:] == 0).all()
+    assert dk[1].abs().sum() > 0 and dv[0, :, :100].abs().sum() > 0
+
+
+def test_sharded_backward_equals_unsharded(cuda_device):
+    B, H, S, D, p = 4, 2, 256, 64, 0.1
+    q, k, v, d_o, lens = helpers.randn_like_config(B, H, S, S, D, torch.float16, seed=4, device=cuda_device)
+    o, lse = api.fmha_forward(q, k, v, seqlens=lens, p_drop=p, seed=5, offset=0)
+    full = api.fmha_backward(d_o, q, k, v, o, lse, seqlens=lens, p_drop=p, seed=5, offset=0)
+    parts = [[], [], []]
+    for r in range(4):
+        sh = sharding.make_shard(B, H, 4, r)
+        f = lambda t: sharding.shard_tensor(t, sh).contiguous()
+        ls = sharding.shard_per_batch(lens, sh)
+        got = api.fmha_backward(f(d_o), f(q), f(k), f(v), f(o), lse.reshape(B * H, S)[sh.bh_start:sh.bh_start + sh.bh_count].contiguous(),
+                                seqlens=ls, p_drop=p, seed=5, offset=0, bh_offset=sh.bh_offset)
+        for acc, t in zip(parts, got):
+            acc.append(t.reshape(sh.bh_count, S, D))
+    # dK and dV have a fixed summation order; dQ is summed by atomics over key tiles
+    assert torch.equal(torch.cat(parts[1]), full[1].reshape(B * H, S, D))
+    assert torch.equal(torch.cat(parts[2]), full[2].reshape(B * H, S, D))
+    assert (torch.cat(parts[0]).float() - full[0].reshape(B * H, S, D).float()).abs().max().item() <= 2e-3
+
+
+def test_full_size_linearity_in_d_o(cuda_device):
+    """BERT-large training shape: gradients are linear in dO, and doubling is exact in fp16, so
+    bwd(2 dO) == 2 bwd(dO) for dK, dV (fixed order) and to rounding for dQ (atomic order).
+    One (batch, head) slice is also checked against the oracle."""
+    name = "bert_large_train"
+    B, H, S, D, dtype, lr, p, _ = composite.CONFIGS[name]
+    x = composite.make_inputs(B, H, S, D, dtype, lr, composite.CONFIG_SEEDS[name], with_do=True)
+    q, k, v, d_o, lens = (x[n].to(cuda_device) for n in ("q", "k", "v", "d_o", "lens"))
+    seed = composite.PHILOX_SEEDS[name]
+    o, lse = api.fmha_forward(q, k, v, seqlens=lens, p_drop=p, seed=seed, offset=0)
+    g1 = api.fmha_backward(d_o, q, k, v, o, lse, seqlens=lens, p_drop=p, seed=seed, offset=0)
+    g2 = api.fmha_backward(d_o * 2, q, k, v, o, lse, seqlens=lens, p_drop=p, seed=seed, offset=0)
+    assert torch.equal(g2[1], g1[1] * 2) and torch.equal(g2[2], g1[2] * 2)
+    assert (g2[0].float() - 2 * g1[0].float()).abs().max().item() <= 4e-3
+    b, h = 3, 5
+    sl = lambda t: t[b:b + 1, h:h + 1]
+    ref, add, keep, ks = helpers.oracle_forward(sl(q), sl(k), sl(v), lens=lens[b:b + 1], p_drop=p, seed=seed, offset=0,
+                                                bh_offset=b * H + h)
+    rdq, rdk, rdv = helpers.oracle_backward(sl(q), sl(k), sl(v), sl(d_o), add=add, keep=keep, ks=ks)
+    helpers.assert_close(sl(g1[0]), rdq, "dq slice")
+    helpers.assert_close(sl(g1[1]), rdk, "dk slice")
+    helpers.assert_close(sl(g1[2]), rdv, "dv slice")

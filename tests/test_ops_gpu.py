@@ -1,0 +1,114 @@
+"""The torch operator layer on the GPU: the reference's own checks (test.py:20-29 and
+test_train_mha.py:23-41 of shmsong/NvFuserExamples) restated with seeds, the golden outputs of
+the reference composites, and the autograd operator."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import composite
+from tests import helpers
+from tests.golden import make_golden
+
+pytestmark = pytest.mark.gpu
+GOLD = Path(__file__).resolve().parent / "golden"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    import mha_manual  # noqa: F401  (registers torch.ops.mha_manual)
+    return torch.ops.mha_manual
+
+
+def test_reference_inference_check(ops, cuda_device):
+    """test.py with its sizes (B*H = 512, S = 128, D = 64) and its tolerance (atol 1e-2), plus ours."""
+    torch.manual_seed(0)
+    bh, s, d = 32 * 16, 128, 64
+    q, k, v = (torch.randn(bh, s, d, dtype=torch.half, device=cuda_device) for _ in range(3))
+    amask = torch.empty(bh, s, s, device=cuda_device).random_(2).to(torch.half)
+    fused = ops.fmha_nvfuser(q, k, v, amask)
+    ctx = composite.reference_mha_inference(q, k, v, amask)  # the composite itself, on the GPU as in test.py
+    assert torch.allclose(ctx, fused, atol=1e-2)
+    ref = composite.attention_fp32(q, k, v, add_mask=(1.0 - amask.float()) * -10000.0, scale=1 / 8)["o"]
+    helpers.assert_close(fused, ref, "ctx")
+    ops.check_status()
+
+
+def test_reference_train_check(ops, cuda_device):
+    torch.manual_seed(1)
+    bh, s, d = 32 * 16, 128, 64
+    q, k, v = (torch.randn(bh, s, d, dtype=torch.half, device=cuda_device) for _ in range(3))
+    pad = torch.empty(bh, s, s, device=cuda_device).random_(2).to(torch.half) * (-1000)
+    dm = torch.empty(bh, s, s, device=cuda_device).random_(2).to(torch.half)
+    sm, dr, ctx = composite.reference_mha_train(q, k, v, pad, dm)
+    ctx_fused = ops.fmha_train_nvfuser(q, k, v, pad, dm)
+    saved = ops.fmha_train_saveim_nvfuser(q, k, v, pad, dm)
+    assert torch.allclose(ctx_fused, ctx, atol=1e-2)            # test_train_mha.py:36
+    assert torch.allclose(saved[0], ctx, atol=1e-2)             # test_train_mha.py:41
+    r = composite.attention_fp32(q, k, v, add_mask=pad.float(), keep=dm.float(), keep_scale=2.0, scale=1 / 8)
+    helpers.assert_close(ctx_fused, r["o"], "ctx", atol=2e-3)
+    helpers.assert_close(saved[0], r["o"], "saved ctx", atol=4e-3)  # P is rounded to fp16 after normalising here
+    helpers.assert_close(saved[1], r["softmax"], "softmax")
+    helpers.assert_close(saved[2], r["dropout_out"], "dropout_out")
+    ops.check_status()
+
+
+def test_against_golden_outputs_of_the_reference_composites(ops, cuda_device):
+    g = np.load(GOLD / "ref_inference.npz")
+    bh, s, d = (int(x) for x in g["shape"])
+    q, k, v, amask = (t.to(cuda_device) for t in make_golden.inference_inputs(int(g["seed"]), bh, s, d))
+    fused = ops.fmha_nvfuser(q, k, v, amask)
+    assert torch.allclose(torch.from_numpy(g["ctx"]).float(), fused.cpu().float(), atol=2e-3)
+    g = np.load(GOLD / "ref_train.npz")
+    bh, s, d = (int(x) for x in g["shape"])
+    q, k, v, pad, dm = (t.to(cuda_device) for t in make_golden.train_inputs(int(g["seed"]), bh, s, d))
+    out = ops.fmha_train_saveim_nvfuser(q, k, v, pad, dm)
+    # the golden train composite ran natively in fp16 (its own error is ~1e-3, hence the reference's 1e-2)
+    assert torch.allclose(torch.from_numpy(g["ctx"]).float(), out[0].cpu().float(), atol=1e-2)
+    assert torch.allclose(torch.from_numpy(g["softmax"]).float(), out[1].cpu().float(), atol=2e-3)
+    assert torch.allclose(torch.from_numpy(g["dropout_out"]).float(), out[2].cpu().float(), atol=4e-3)
+
+
+def test_legacy_ops_accept_other_shapes(ops, cuda_device):
+    torch.manual_seed(2)
+    for bh, sq, sk, d, dt in ((3, 200, 136, 64, torch.half), (2, 128, 384, 128, torch.bfloat16), (2, 77, 51, 64, torch.half)):
+        q = torch.randn(bh, sq, d, device=cuda_device).to(dt)
+        k = torch.randn(bh, sk, d, device=cuda_device).to(dt)
+        v = torch.randn(bh, sk, d, device=cuda_device).to(dt)
+        amask = torch.empty(bh, sq, sk, device=cuda_device).random_(2).to(dt)
+        dm = torch.empty(bh, sq, sk, device=cuda_device).random_(2).to(dt)
+        pad = (1 - amask) * -1000
+        ref = composite.attention_fp32(q, k, v, add_mask=(1.0 - amask.float()) * -10000.0)
+        helpers.assert_close(ops.fmha_nvfuser(q, k, v, amask), ref["o"], f"ctx {bh,sq,sk,d}", dt)
+        r2 = composite.attention_fp32(q, k, v, add_mask=pad.float(), keep=dm.float(), keep_scale=2.0)
+        out = ops.fmha_train_saveim_nvfuser(q, k, v, pad, dm)
+        helpers.assert_close(out[0], r2["o"], "saved ctx", dt, atol=6e-3)
+        helpers.assert_close(out[1], r2["softmax"], "softmax", dt)
+        helpers.assert_close(out[2], r2["dropout_out"], "dropout", dt)
+        helpers.assert_close(ops.fmha_train_nvfuser(q, k, v, pad, dm), r2["o"], "train ctx", dt, atol=3e-3)
+
+
+def test_autograd_operator(ops, cuda_device):
+    B, H, S, D = 2, 2, 256, 64
+    q, k, v, d_o, lens = helpers.randn_like_config(B, H, S, S, D, torch.float16, seed=6, device=cuda_device)
+    q.requires_grad_(True); k.requires_grad_(True); v.requires_grad_(True)
+    o = ops.fmha(q, k, v, None, lens, 0.1, 42, 1, None)
+    o.backward(d_o)
+    ref, add, keep, ks = helpers.oracle_forward(q.detach(), k.detach(), v.detach(), lens=lens, p_drop=0.1, seed=42, offset=1)
+    rdq, rdk, rdv = helpers.oracle_backward(q.detach(), k.detach(), v.detach(), d_o, add=add, keep=keep, ks=ks)
+    helpers.assert_close(o, ref["o"], "o")
+    helpers.assert_close(q.grad, rdq, "dq")
+    helpers.assert_close(k.grad, rdk, "dk")
+    helpers.assert_close(v.grad, rdv, "dv")
+
+
+def test_operator_errors(ops, cuda_device):
+    x = torch.zeros(2, 128, 64, dtype=torch.half, device=cuda_device)
+    with pytest.raises(RuntimeError):
+        ops.fmha_nvfuser(x, x, x, torch.zeros(2, 128, 64, dtype=torch.half, device=cuda_device))   # wrong mask size
+    with pytest.raises(RuntimeError):
+        ops.fmha_nvfuser(x.float(), x.float(), x.float(), torch.zeros(2, 128, 128, device=cuda_device))  # fp32 unsupported
+    y = torch.zeros(2, 128, 96, dtype=torch.half, device=cuda_device)
+    with pytest.raises(RuntimeError):
+        ops.fmha_nvfuser(y, y, y, torch.zeros(2, 128, 128, dtype=torch.half, device=cuda_device))  # head dim 96
