@@ -80,6 +80,10 @@ static int check_device() {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) { g_last_cuda_error = static_cast<int>(e); return FMHA_ERR_NO_DEVICE; }
+  // Bind the device's primary context to this thread: a thread that has made no CUDA call yet
+  // (an autograd worker, a fresh FFI thread) has no current context, and launches from it fail.
+  e = cudaSetDevice(dev);
+  if (e != cudaSuccess) { g_last_cuda_error = static_cast<int>(e); return FMHA_ERR_NO_DEVICE; }
   int major = 0;
   e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
   if (e != cudaSuccess) { g_last_cuda_error = static_cast<int>(e); return FMHA_ERR_NO_DEVICE; }

