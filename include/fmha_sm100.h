@@ -154,6 +154,27 @@ int fmha_sm100_bwd(const fmha_bwd_params* p, void* stream);
    the row term delta = rowsum(dO * O)). */
 int fmha_sm100_bwd_workspace_bytes(const fmha_bwd_params* p, size_t* bytes);
 
+/* Backward for callers that cannot hand over a workspace (this entry point has no counterpart
+   in the reference, which has no backward pass and lets its JIT runner allocate).
+   Some hosts of this library cannot allocate device memory at call time: a serving process that
+   gave every free byte to its own pool at start-up, a foreign runtime whose calling thread may
+   not enter the CUDA allocator, a latency-critical loop for which the implicit device
+   synchronisation of cudaMalloc/cudaFree is unacceptable.  For them this variant of
+   fmha_sm100_bwd takes its scratch (fp32 dQ accumulator + delta) from an array that is part of
+   the library image instead of p->workspace, which is ignored.  It calls no cudaMalloc, cudaFree
+   or other allocating routine.
+     - The array is FMHA_STATIC_SCRATCH_BYTES large on EVERY GPU that loads the library, from load
+       to process exit.  Sizes whose fmha_sm100_bwd_workspace_bytes() exceeds it are refused with
+       FMHA_ERR_TOO_LARGE and nothing is launched.
+     - The first call on each device looks up the array's device address (once per device, with
+       that device current); make that first call before any stream capture begins.
+     - All calls share the one array and it keeps what the previous call left; the kernels clear
+       the part that must start at zero themselves.  Two calls that overlap on the same GPU
+       (different streams, or several host threads) race on it: serialise them.
+   Inputs, outputs, status codes and numerics are those of fmha_sm100_bwd. */
+#define FMHA_STATIC_SCRATCH_BYTES (32u << 20)
+int fmha_sm100_bwd_static_scratch(const fmha_bwd_params* p, void* stream);
+
 /* 7-bit dropout threshold T for a drop probability: T = round(128 p) clamped to [0,127]. */
 int32_t fmha_sm100_dropout_threshold(float p_drop);
 

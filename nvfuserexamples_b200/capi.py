@@ -28,12 +28,13 @@ DROPOUT_NONE, DROPOUT_DENSE, DROPOUT_PHILOX = 0, 1, 2
 FLAG_P_VIA_SMEM = 1
 FLAG_BWD_SKIP_PREPARE = 2
 FLAG_BWD_SKIP_FINISH = 4
+STATIC_SCRATCH_BYTES = 32 << 20
 
 EXPORTS = [
     "fmha_sm100_fwd", "fmha_sm100_bwd", "fmha_sm100_bwd_workspace_bytes", "fmha_sm100_dropout_threshold",
     "fmha_sm100_philox_mask_host", "fmha_sm100_philox_mask_device", "fmha_sm100_check_status",
     "fmha_sm100_strerror", "fmha_sm100_last_cuda_error", "fmha_sm100_abi_version",
-    "fmha_sm100_selftest_wait_timeout",
+    "fmha_sm100_selftest_wait_timeout", "fmha_sm100_bwd_static_scratch",
 ]
 
 
@@ -97,6 +98,8 @@ def load() -> C.CDLL:
     lib.fmha_sm100_fwd.restype = C.c_int
     lib.fmha_sm100_bwd.argtypes = [C.POINTER(BwdParams), C.c_void_p]
     lib.fmha_sm100_bwd.restype = C.c_int
+    lib.fmha_sm100_bwd_static_scratch.argtypes = [C.POINTER(BwdParams), C.c_void_p]
+    lib.fmha_sm100_bwd_static_scratch.restype = C.c_int
     lib.fmha_sm100_bwd_workspace_bytes.argtypes = [C.POINTER(BwdParams), C.POINTER(C.c_size_t)]
     lib.fmha_sm100_bwd_workspace_bytes.restype = C.c_int
     lib.fmha_sm100_dropout_threshold.argtypes = [C.c_float]
@@ -285,3 +288,15 @@ def selftest_wait_timeout(status) -> None:
     """Launches the library's bounded-wait self test on the current stream (see the header)."""
     _check(load().fmha_sm100_selftest_wait_timeout(status.data_ptr(), _stream_ptr(status.device)),
            "fmha_sm100_selftest_wait_timeout")
+
+
+def bwd_static_scratch(d_o, q, k, v, o, lse, **kw):
+    """fmha_sm100_bwd_static_scratch on the current stream: the backward pass with the scratch
+    taken from the library's built-in array (no workspace argument, nothing allocated by the
+    library).  Raises FmhaError(FMHA_ERR_TOO_LARGE) when the sizes need more than
+    STATIC_SCRATCH_BYTES.  Returns (dq, dk, dv); the outputs themselves are the caller's tensors."""
+    import torch
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    p = bwd_params(d_o, q, k, v, o, lse, dq, dk, dv, **kw)
+    _check(load().fmha_sm100_bwd_static_scratch(C.byref(p), _stream_ptr(q.device)), "fmha_sm100_bwd_static_scratch")
+    return dq, dk, dv

@@ -382,3 +382,52 @@ extern "C" int fmha_sm100_selftest_wait_timeout(int32_t* status, void* stream) {
   if (e != cudaSuccess) return cuda_fail(e);
   return FMHA_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Backward without a caller workspace: scratch lives in the library image.
+// ---------------------------------------------------------------------------------------------
+// In host code `g_bwd_static_scratch` is only a handle for the runtime's symbol table, never a
+// device address; the address each device gave the array is fetched below with
+// cudaGetSymbolAddress and that pointer is what the kernels receive.
+static __device__ __align__(256) unsigned char g_bwd_static_scratch[FMHA_STATIC_SCRATCH_BYTES];
+
+namespace fmha {
+constexpr int kMaxScratchDevices = 64;
+static std::mutex g_scratch_mu;
+static void* g_scratch_addr[kMaxScratchDevices] = {};
+
+// Device address of the static scratch on the CURRENT device (looked up once per device).
+static int static_scratch_address(void** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) { g_last_cuda_error = static_cast<int>(e); return FMHA_ERR_NO_DEVICE; }
+  if (dev < 0 || dev >= kMaxScratchDevices) return FMHA_ERR_TOO_LARGE;
+  std::lock_guard<std::mutex> lock(g_scratch_mu);
+  if (g_scratch_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_bwd_static_scratch);  // needs `dev` current: it is
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (ptr == nullptr || (reinterpret_cast<uintptr_t>(ptr) & 255)) return FMHA_ERR_LAUNCH;
+    g_scratch_addr[dev] = ptr;
+  }
+  *out = g_scratch_addr[dev];
+  return FMHA_OK;
+}
+}  // namespace fmha
+
+extern "C" int fmha_sm100_bwd_static_scratch(const fmha_bwd_params* p, void* stream) {
+  if (p == nullptr) return FMHA_ERR_BAD_ARG;
+  size_t need = 0;
+  int rc = fmha_sm100_bwd_workspace_bytes(p, &need);  // also validates struct size, dtype, D, sizes
+  if (rc != FMHA_OK) return rc;
+  if (need > FMHA_STATIC_SCRATCH_BYTES) return FMHA_ERR_TOO_LARGE;
+  rc = check_device();
+  if (rc != FMHA_OK) return rc;
+  void* scratch = nullptr;
+  rc = static_scratch_address(&scratch);
+  if (rc != FMHA_OK) return rc;
+  fmha_bwd_params q = *p;            // same call, scratch pointer swapped in; the caller's struct is untouched
+  q.workspace = scratch;
+  q.workspace_bytes = FMHA_STATIC_SCRATCH_BYTES;
+  return fmha_sm100_bwd(&q, stream);
+}
