@@ -10,9 +10,10 @@ With N > 1 (launched under torchrun, one rank per GPU) every rank works on its o
 batch x heads axis; there is no collective on the data path, only a barrier and a MAX of the
 per-rank device times.  Rank 0 prints ONE JSON line.
 
-What is counted: `value` is EXECUTED TFLOP/s — 14*H*S_q*S_k_tiles*D per batch element, where
-S_k_tiles is the key length rounded up to the 128-key tiles the kernels actually visit (key
-tiles that lie wholly in the padding are skipped, which is exact).  The dense-equivalent figure
+What is counted: `value` is EXECUTED TFLOP/s — (4*ceil64(len) + 10*ceil128(len))*H*S_q*D per batch
+element: the key length rounded up to the key steps the kernels actually visit (64 keys in the
+forward kernel, 128 in the backward kernel; steps that lie wholly in the padding are skipped,
+which is exact).  The dense-equivalent figure
 (14*B*H*S^2*D over the same time) is reported beside it.
 
 `--impl reference` times the reference's own CPU path for the same step: the eager composite of
@@ -44,9 +45,10 @@ METRIC = "fused MHA fwd+bwd TFLOP/s at BERT-large shape (executed flops)"
 BWD_KERNEL_DRAM_TRAFFIC = None
 
 
-def executed_flops(lens, h, s_q, d, mult):
-    """mult * h * s_q * (key length rounded up to 128) * d summed over the batch."""
-    return float(sum(mult * h * s_q * (math.ceil(int(n) / 128) * 128) * d for n in lens))
+def executed_flops(lens, h, s_q, d, mult, granule=128):
+    """mult * h * s_q * (key length rounded up to the kernel's key step) * d summed over the batch.
+    The forward kernel walks the keys in 64-key steps at D=64, the backward kernel in 128-key tiles."""
+    return float(sum(mult * h * s_q * (math.ceil(int(n) / granule) * granule) * d for n in lens))
 
 
 def peaks():
@@ -262,7 +264,7 @@ def run_ours(args, rank, world, local_rank):
     ms_step = t.item() / args.steps
     capi.check_status(status)
 
-    exe_step = [executed_flops(l, H, S, D, 14.0) for l in lens_host]           # per input set, this rank
+    exe_step = [executed_flops(l, H, S, D, 4.0, 64) + executed_flops(l, H, S, D, 10.0, 128) for l in lens_host]  # per input set
     exe_mean = sum(exe_step[i % n_sets] for i in range(args.steps)) / args.steps
     exe_all = torch.tensor([exe_mean], dtype=torch.float64, device=dev)
     if world > 1:
@@ -293,7 +295,7 @@ def run_ours(args, rank, world, local_rank):
     bwd_all_ms = time_calls(lambda i: lib.fmha_sm100_bwd(C.byref(plans[i % n_sets]["bp"]), sp), kn)
     pk = peaks()
     exe_bwd = sum(executed_flops(l, H, S, D, 10.0) for l in lens_host) / n_sets
-    exe_fwd = sum(executed_flops(l, H, S, D, 4.0) for l in lens_host) / n_sets
+    exe_fwd = sum(executed_flops(l, H, S, D, 4.0, 64) for l in lens_host) / n_sets
     ach = exe_bwd / (bwd_main_ms * 1e-3) / 1e12
     roofline = {"kernel": "fmha_bwd_kernel<64,fp16>", "bound": "tensor", "achieved": ach, "peak": pk["tflops"],
                 "unit": "TFLOP/s", "frac": ach / pk["tflops"], "traffic": BWD_KERNEL_DRAM_TRAFFIC,
@@ -363,7 +365,7 @@ def run_ours(args, rank, world, local_rank):
             "config": {"workload": WORKLOAD, "B_per_gpu": b_loc, "global_batch": b_loc * world, "H": H, "S": S, "D": D,
                        "p_drop": P_DROP, "valid_len": list(LEN_RANGE), "parallelism": f"bh-shard x{world}, no collective",
                        "l2": "335 MB touched per step (> 126 MB L2), 2 rotating input sets",
-                       "flops_counted": "executed: 14*H*S*ceil128(len_b)*D per batch element"},
+                       "flops_counted": "executed: (4*ceil64(len_b) + 10*ceil128(len_b))*H*S*D per batch element"},
             "dense_equiv_tflops": dense_value,
             "pct_of_measured_bf16_peak": 100.0 * value / (pk["tflops"] * world),
             "roofline": roofline, "roofline_fwd": roofline_fwd,

@@ -148,9 +148,14 @@ int fmha_sm100_fwd(const fmha_fwd_params* p, void* stream) {
 
   FwdArgs a;
   std::memset(&a, 0, sizeof(a));
+  const bool p_via_smem = (p->flags & FMHA_FLAG_P_VIA_SMEM) != 0;
+  const bool legacy = p_via_smem || p->mask_kind == FMHA_MASK_DENSE_KEEP || p->mask_kind == FMHA_MASK_DENSE_ADDITIVE ||
+                      p->dropout_kind == FMHA_DROPOUT_DENSE || p->save_softmax || p->save_dropout ||
+                      p->keep_mask_out || p->debug_scores;
   if ((rc = make_tmap(&a.tm_q, sanitized(p->q, p->B, p->H, p->S_q, p->D), p->dtype, p->B, p->H, p->S_q, p->D, kTileM))) return rc;
-  if ((rc = make_tmap(&a.tm_k, sanitized(p->k, p->B, p->H, p->S_k, p->D), p->dtype, p->B, p->H, p->S_k, p->D, kTileN))) return rc;
-  if ((rc = make_tmap(&a.tm_v, sanitized(p->v, p->B, p->H, p->S_k, p->D), p->dtype, p->B, p->H, p->S_k, p->D, kTileN))) return rc;
+  const int kv_rows = fwd_key_tile(p->D, legacy);
+  if ((rc = make_tmap(&a.tm_k, sanitized(p->k, p->B, p->H, p->S_k, p->D), p->dtype, p->B, p->H, p->S_k, p->D, kv_rows))) return rc;
+  if ((rc = make_tmap(&a.tm_v, sanitized(p->v, p->B, p->H, p->S_k, p->D), p->dtype, p->B, p->H, p->S_k, p->D, kv_rows))) return rc;
   if ((rc = make_tmap(&a.tm_o, sanitized(p->o, p->B, p->H, p->S_q, p->D), p->dtype, p->B, p->H, p->S_q, p->D, kTileM))) return rc;
   a.B = p->B; a.H = p->H; a.S_q = p->S_q; a.S_k = p->S_k;
   a.scale_log2 = p->scale * 1.4426950408889634f;
@@ -176,10 +181,7 @@ int fmha_sm100_fwd(const fmha_fwd_params* p, void* stream) {
   a.debug_scores = p->debug_scores;
   a.status = p->status;
 
-  const bool p_via_smem = (p->flags & FMHA_FLAG_P_VIA_SMEM) != 0;
-  const bool legacy = p_via_smem || p->mask_kind == FMHA_MASK_DENSE_KEEP || p->mask_kind == FMHA_MASK_DENSE_ADDITIVE ||
-                      p->dropout_kind == FMHA_DROPOUT_DENSE || p->save_softmax || p->save_dropout ||
-                      p->keep_mask_out || p->debug_scores;
+
   const int e = launch_fwd(a, p->D, p->dtype, legacy, p_via_smem, static_cast<cudaStream_t>(stream));
   if (e != 0) return cuda_fail(static_cast<cudaError_t>(e));
   return FMHA_OK;

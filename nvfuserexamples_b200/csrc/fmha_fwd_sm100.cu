@@ -507,13 +507,10 @@ static int launch_fwd_impl(const FwdArgs& a, cudaStream_t stream) {
 }
 
 int launch_fwd(const FwdArgs& a, int D, int dtype, bool legacy, bool p_via_smem, cudaStream_t stream) {
+  if (!legacy) return launch_fwd_fast(a, D, dtype, stream);  // compact masks, Philox dropout: the production kernel
 #define FMHA_FWD_CASE(DD, BF, LG, PS) \
   if (D == DD && (dtype == FMHA_DTYPE_BF16) == BF && legacy == LG && p_via_smem == PS) \
     return launch_fwd_impl<DD, BF, LG, PS>(a, stream);
-  FMHA_FWD_CASE(64, false, false, false)
-  FMHA_FWD_CASE(64, true, false, false)
-  FMHA_FWD_CASE(128, false, false, false)
-  FMHA_FWD_CASE(128, true, false, false)
   FMHA_FWD_CASE(64, false, true, false)
   FMHA_FWD_CASE(64, true, true, false)
   FMHA_FWD_CASE(128, false, true, false)

@@ -10,7 +10,10 @@
 namespace fmha {
 
 constexpr int kTileM = 128;  // query rows per CTA tile
-constexpr int kTileN = 128;  // keys per step
+constexpr int kTileN = 128;  // keys per step (general forward kernel, backward kernel)
+// Keys per step of the forward kernel that will run: the production kernel walks the keys in
+// 64-key steps at head dimension 64 (see fmha_fwd_fast_sm100.cu); the TMA box of K and V follows.
+constexpr int fwd_key_tile(int D, bool legacy) { return (!legacy && D == 64) ? 64 : 128; }
 
 struct FwdArgs {
   alignas(64) CUtensorMap tm_q;
@@ -63,6 +66,7 @@ struct BwdArgs {
 
 // Launchers (defined in the .cu files).  Return a cudaError_t as int.
 int launch_fwd(const FwdArgs& a, int D, int dtype, bool legacy, bool p_via_smem, cudaStream_t stream);
+int launch_fwd_fast(const FwdArgs& a, int D, int dtype, cudaStream_t stream);
 int launch_bwd(const BwdArgs& a, int D, int dtype, cudaStream_t stream);
 int launch_bwd_prepare(const void* o, const fmha_tensor4& ot, const fmha_tensor4& dot, int B, int H, int S_q, int S_q_pad,
                        int D, int dtype, float* delta, float* dq_accum, cudaStream_t stream);

@@ -25,8 +25,9 @@ struct U4 {
 
 FMHA_HD void mulhilo32(uint32_t a, uint32_t b, uint32_t& hi, uint32_t& lo) {
 #if defined(__CUDA_ARCH__)
-  lo = a * b;
-  hi = __umulhi(a, b);
+  const unsigned long long p = static_cast<unsigned long long>(a) * static_cast<unsigned long long>(b);  // one wide multiply
+  lo = static_cast<uint32_t>(p);
+  hi = static_cast<uint32_t>(p >> 32);
 #else
   const uint64_t p = static_cast<uint64_t>(a) * static_cast<uint64_t>(b);
   lo = static_cast<uint32_t>(p);

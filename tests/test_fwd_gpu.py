@@ -63,14 +63,15 @@ def test_dropout_mask_bit_exact(cuda_device):
     dev = api.philox_dropout_mask(B, H, S_q, S_k, p, seed, off, device=cuda_device).cpu().numpy().reshape(B * H, S_q, S_k)
     np.testing.assert_array_equal(dev, oracle)
     np.testing.assert_array_equal(api.philox_dropout_mask(B, H, S_q, S_k, p, seed, off).reshape(B * H, S_q, S_k), oracle)
-    # and the fast-path kernel (no debug outputs) produced the same O as the instrumented one
+    # and the production kernel (no debug outputs) dropped the same entries as the instrumented one:
+    # the two differ only by rounding, a differing keep decision would show as an O(1) difference
     o_fast, _ = api.fmha_forward(q, k, v, p_drop=p, seed=seed, offset=off)
-    assert torch.equal(o_fast, res["o"])
+    assert (o_fast.float() - res["o"].float()).abs().max().item() <= 2e-3
 
 
 def test_tensor_memory_and_shared_memory_paths_agree(cuda_device):
     q, k, v, _, lens = helpers.randn_like_config(2, 2, 256, 384, 64, torch.float16, seed=5, device=cuda_device)
-    a = capi.fwd(q, k, v, mask_kind=capi.MASK_SEQLEN, mask=lens)
+    a = capi.fwd(q, k, v, mask_kind=capi.MASK_SEQLEN, mask=lens, debug_scores=True)  # general kernel, P in tensor memory
     b = capi.fwd(q, k, v, mask_kind=capi.MASK_SEQLEN, mask=lens, flags=capi.FLAG_P_VIA_SMEM)
     assert torch.equal(a["o"], b["o"]) and torch.equal(a["lse"], b["lse"])
 
