@@ -9,7 +9,7 @@
 //   1. bwd_prepare : delta[row] = sum_d dO[row,d] * O[row,d]  and zero the fp32 dQ accumulator
 //   2. bwd_main    : one CTA per (128-key tile, head, batch) loops over the 128-row query tiles
 //                      S  = Q K^T            dP = dO V^T              (tcgen05.mma, fp32 in TMEM)
-//                      P  = exp2(S*scale*log2e + mask - lse*log2e)   (8 warps, thread = row, half the columns)
+//                      P  = exp2(S*scale*log2e + mask - lse*log2e)   (16 warps, thread = row, a quarter of the columns)
 //                      dS = P * (keep*c*dP - delta)                   c = 1/(1-p_drop)
 //                      dV += (keep*P)^T dO     dK += dS^T Q     dQ_tile = dS K
 //                    P and dS go through shared memory (16-bit, 128-byte swizzle) and are read
@@ -21,6 +21,7 @@
 #include <cuda_fp16.h>
 
 #include <cstring>
+#include <type_traits>
 
 #include "../../include/fmha_sm100.h"
 #include "fmha_device_utils.cuh"
@@ -32,30 +33,33 @@ namespace fmha {
 
 namespace {
 
-constexpr int kBwdThreads = 320;  // producer warp, MMA warp, 8 compute warps
+constexpr int kComputeThreads = 512;               // 16 compute warps
+constexpr int kBwdThreads = 64 + kComputeThreads;   // + producer warp + MMA warp
 constexpr float kLog2eB = 1.4426950408889634f;
 
 enum BwdWaitSite {
   kSiteKvFull = 201, kSiteQdoFull = 202, kSiteQdoEmpty = 203, kSiteSdpFull = 204, kSitePdsFull = 205,
-  kSiteDqFull = 206, kSiteDqFree = 207, kSiteAccFull = 208
+  kSiteDqFull = 206, kSiteDqFree = 207, kSiteAccFull = 208, kSiteSdpFree = 209
 };
 
 template <int D>
 struct BwdSmem {
-  static constexpr int kStages = (D == 64) ? 2 : 1;
+  static constexpr int kStages = (D == 64) ? 2 : 1;   // Q / dO stages
+  static constexpr int kPdsBufs = (D == 64) ? 2 : 1;  // P / dS buffers
   static constexpr int kTileBytes = kTileM * D * 2;
   static constexpr int kOffK = 0;
   static constexpr int kOffV = kOffK + kTileBytes;
   static constexpr int kOffQ = kOffV + kTileBytes;
   static constexpr int kOffdO = kOffQ + kStages * kTileBytes;
   static constexpr int kOffP = kOffdO + kStages * kTileBytes;
-  static constexpr int kOffdS = kOffP + kTileM * kTileN * 2;
-  static constexpr int kOffMask = kOffdS + kTileM * kTileN * 2;  // 128 floats
+  static constexpr int kOffdS = kOffP + kPdsBufs * kTileM * kTileN * 2;
+  static constexpr int kOffMask = kOffdS + kPdsBufs * kTileM * kTileN * 2;  // 128 floats
   static constexpr int kOffBar = kOffMask + kTileN * 4;
-  static constexpr int kNumBars = 6 + 2 * kStages;
+  static constexpr int kNumBars = 7 + 2 * kStages;
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;
   static constexpr int kBytes = kOffMisc + 16;
   static constexpr int kDynBytes = kBytes + 1024;
+  static_assert(kDynBytes <= 232448, "shared memory budget of one CTA exceeded");
 };
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
@@ -152,18 +156,27 @@ __global__ void __launch_bounds__(256) bwd_finish_kernel(const FinishArgs a) {
 // ---------------------------------------------------------------------------------------
 // 2. main kernel
 // ---------------------------------------------------------------------------------------
-template <int D, bool BF16>
+// Schedule.  The eight compute warps copy S and dP of query tile i into registers as soon as the
+// tensor core has produced them and release the tensor-memory columns at once (sdp_free), so the
+// MMA warp can already issue S and dP of tile i+1 while tile i is still being turned into P and
+// dS.  At D = 64 P and dS are double-buffered in shared memory, so dV/dK/dQ of tile i run on the
+// tensor core while the compute warps work on tile i+1, and the dQ tile of i is read out one
+// iteration later.  At D = 128 (shared memory and tensor memory are full) P/dS are single
+// buffered and dQ shares the dP columns, so only the S/dP copy-out overlaps.
+template <int D, bool BF16, bool KEYADD, bool DROP>
 __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_constant__ BwdArgs a) {
   using L = BwdSmem<D>;
   constexpr int ST = L::kStages;
+  constexpr int NB = L::kPdsBufs;
+  constexpr bool EARLY = (D == 64);  // S/dP of the next tile are issued before dV/dK/dQ of this one
   constexpr int kTmemCols = 512;
-  // tensor-memory columns
   constexpr uint32_t kColS = 0, kColdP = 128, kColdV = 256, kColdK = 256 + D;
-  constexpr uint32_t kColdQ = (D == 64) ? 384 : kColdP;  // D = 128: dQ reuses the dP columns
+  constexpr uint32_t kColdQ = (D == 64) ? 384 : kColdP;
   constexpr int kFmt = BF16 ? 1 : 0;
   constexpr uint32_t kIdescS = make_idesc_f16(128, 128, kFmt, false, false);
   constexpr uint32_t kIdescT = make_idesc_f16(128, D, kFmt, true, true);    // dV, dK: A and B MN-major
   constexpr uint32_t kIdescQ = make_idesc_f16(128, D, kFmt, false, true);   // dQ: A K-major, B MN-major
+  constexpr int kPdsBytes = kTileM * kTileN * 2;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -176,12 +189,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
   float* sMask = reinterpret_cast<float*>(smem + L::kOffMask);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
   uint64_t* kv_full = bars + 0;
-  uint64_t* sdp_full = bars + 1;   // S and dP are in tensor memory
-  uint64_t* pds_full = bars + 2;   // P and dS are in shared memory (256 arrivals)
-  uint64_t* dq_full = bars + 3;    // dQ tile is in tensor memory
-  uint64_t* dq_free = bars + 4;    // dQ tile has been read out (256 arrivals)
-  uint64_t* acc_full = bars + 5;   // dK / dV accumulation finished
-  uint64_t* qdo_full = bars + 6;
+  uint64_t* sdp_full = bars + 1;   // S and dP of a tile are in tensor memory
+  uint64_t* sdp_free = bars + 2;   // ... and have been copied to registers (all compute threads arrive)
+  uint64_t* pds_full = bars + 3;   // P and dS are in shared memory (all compute threads arrive)
+  uint64_t* dq_full = bars + 4;    // dQ tile is in tensor memory; dV/dK/dQ of that tile are complete
+  uint64_t* dq_free = bars + 5;    // dQ tile has been read out (all compute threads arrive)
+  uint64_t* acc_full = bars + 6;   // dK / dV accumulation finished
+  uint64_t* qdo_full = bars + 7;
   uint64_t* qdo_empty = qdo_full + ST;
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(smem + L::kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kOffMisc + 4);
@@ -206,9 +220,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
     *abort_flag = 0;
     mbar_init(kv_full, 1);
     mbar_init(sdp_full, 1);
-    mbar_init(pds_full, 256);
+    mbar_init(sdp_free, kComputeThreads);
+    mbar_init(pds_full, kComputeThreads);
     mbar_init(dq_full, 1);
-    mbar_init(dq_free, 256);
+    mbar_init(dq_free, kComputeThreads);
     mbar_init(acc_full, 1);
     for (int s = 0; s < ST; ++s) {
       mbar_init(qdo_full + s, 1);
@@ -231,6 +246,16 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_slot;
   const WaitCtx wctx{abort_flag, a.status};
+#ifdef FMHA_TIMELINE
+  // Development aid (not compiled into the library): one CTA records clock64() stamps after its
+  // status words; TL(slot) is issued by the MMA thread and by the first compute thread.
+  long long* tl_buf = reinterpret_cast<long long*>(a.status + 16);
+  const bool tl_cta = (blockIdx.x == 0 && blockIdx.y == 1 && blockIdx.z == gridDim.z / 2);
+#define TL(slot) do { if (tl_cta) tl_buf[slot] = clock64(); } while (0)
+#else
+#define TL(slot) do { } while (0)
+#endif
+  if (threadIdx.x == 0) TL(205);
 
   if (warp == 0) {
     // ============================ TMA producer ======================================
@@ -257,230 +282,289 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
     if (lane == 0 && n_q > 0) {
       const uint32_t tS = tmem_base + kColS, tdP = tmem_base + kColdP, tdV = tmem_base + kColdV,
                      tdK = tmem_base + kColdK, tdQ = tmem_base + kColdQ;
-      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP), adS = smem_u32(sdS);
+      const DescWords dK_k = desc_words(make_smem_desc_sw128(smem_u32(sK), 16, 1024));       // K as K-major B (S)
+      const DescWords dV_k = desc_words(make_smem_desc_sw128(smem_u32(sV), 16, 1024));       // V as K-major B (dP)
+      const DescWords dK_m = desc_words(make_smem_desc_sw128(smem_u32(sK), 16384, 1024));    // K as MN-major B (dQ)
       auto issue_s = [&](int i) {
-        const uint32_t aQ = smem_u32(sQ + (i % ST) * L::kTileBytes);
+        const DescWords dq = desc_words(make_smem_desc_sw128(smem_u32(sQ + (i % ST) * L::kTileBytes), 16, 1024));
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
-          umma_ss(tS, make_smem_desc_sw128(aQ + off, 16, 1024), make_smem_desc_sw128(aK + off, 16, 1024), kIdescS,
-                  kk > 0 ? 1u : 0u);
-        }
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_ss_w(tS, dq.lo + kmajor_step(kk, 16384), dq.hi, dK_k.lo + kmajor_step(kk, 16384), dK_k.hi, kIdescS,
+                    kk > 0 ? 1u : 0u);
       };
       auto issue_dp = [&](int i) {
-        const uint32_t adO = smem_u32(sdO + (i % ST) * L::kTileBytes);
+        const DescWords dd = desc_words(make_smem_desc_sw128(smem_u32(sdO + (i % ST) * L::kTileBytes), 16, 1024));
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
-          umma_ss(tdP, make_smem_desc_sw128(adO + off, 16, 1024), make_smem_desc_sw128(aV + off, 16, 1024), kIdescS,
-                  kk > 0 ? 1u : 0u);
-        }
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_ss_w(tdP, dd.lo + kmajor_step(kk, 16384), dd.hi, dV_k.lo + kmajor_step(kk, 16384), dV_k.hi, kIdescS,
+                    kk > 0 ? 1u : 0u);
       };
+      TL(200);
       mbar_wait(kv_full, 0, wctx, kSiteKvFull);
       mbar_wait(qdo_full + 0, 0, wctx, kSiteQdoFull);
+      TL(201);
       tc_fence_after_sync();
       issue_s(0);
       issue_dp(0);
       umma_commit(sdp_full);
       for (int i = 0; i < n_q; ++i) {
+        TL(i * 16 + 0);
         const int s = i % ST;
-        const uint32_t aQ = smem_u32(sQ + s * L::kTileBytes);
-        const uint32_t adO = smem_u32(sdO + s * L::kTileBytes);
+        // MN-major views of this tile's operands (16 rows = 2048 B per k-step, 64-wide halves 16 KB apart)
+        const DescWords dQ_m = desc_words(make_smem_desc_sw128(smem_u32(sQ + s * L::kTileBytes), 16384, 1024));
+        const DescWords ddO_m = desc_words(make_smem_desc_sw128(smem_u32(sdO + s * L::kTileBytes), 16384, 1024));
+        const DescWords dP_m = desc_words(make_smem_desc_sw128(smem_u32(sP + (i % NB) * kPdsBytes), 16384, 1024));
+        const DescWords ddS_m = desc_words(make_smem_desc_sw128(smem_u32(sdS + (i % NB) * kPdsBytes), 16384, 1024));
+        const DescWords ddS_k = desc_words(make_smem_desc_sw128(smem_u32(sdS + (i % NB) * kPdsBytes), 16, 1024));
+        if constexpr (EARLY) {
+          if (i + 1 < n_q) {
+            mbar_wait(sdp_free, i & 1, wctx, kSiteSdpFree);
+            mbar_wait(qdo_full + ((i + 1) % ST), ((i + 1) / ST) & 1, wctx, kSiteQdoFull);
+            tc_fence_after_sync();
+            TL(i * 16 + 1);
+            issue_s(i + 1);
+            issue_dp(i + 1);
+            umma_commit(sdp_full);
+          }
+        }
+        TL(i * 16 + 2);
         mbar_wait(pds_full, i & 1, wctx, kSitePdsFull);
+        TL(i * 16 + 3);
         tc_fence_after_sync();
         // dV += P^T dO ; dK += dS^T Q : A is the [q x keys] tile read MN-major (keys contiguous),
         // 16 query rows (2048 B) per k-step, the two 64-key halves 16 KB apart.
 #pragma unroll
-        for (int kk = 0; kk < kTileM / 16; ++kk) {
-          const uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
-          umma_ss(tdV, make_smem_desc_sw128(aP + kk * 2048, 16384, 1024),
-                  make_smem_desc_sw128(adO + kk * 2048, 16384, 1024), kIdescT, acc);
-        }
+        for (int kk = 0; kk < kTileM / 16; ++kk)
+          umma_ss_w(tdV, dP_m.lo + mnmajor_step(kk), dP_m.hi, ddO_m.lo + mnmajor_step(kk), ddO_m.hi, kIdescT,
+                    (i > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
-        for (int kk = 0; kk < kTileM / 16; ++kk) {
-          const uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
-          umma_ss(tdK, make_smem_desc_sw128(adS + kk * 2048, 16384, 1024),
-                  make_smem_desc_sw128(aQ + kk * 2048, 16384, 1024), kIdescT, acc);
-        }
+        for (int kk = 0; kk < kTileM / 16; ++kk)
+          umma_ss_w(tdK, ddS_m.lo + mnmajor_step(kk), ddS_m.hi, dQ_m.lo + mnmajor_step(kk), dQ_m.hi, kIdescT,
+                    (i > 0 || kk > 0) ? 1u : 0u);
         umma_commit(qdo_empty + s);  // Q and dO of this stage are not read again (dQ needs dS and K only)
+        TL(i * 16 + 4);
         if (i > 0) {
           mbar_wait(dq_free, (i - 1) & 1, wctx, kSiteDqFree);
           tc_fence_after_sync();
         }
+        TL(i * 16 + 5);
         // dQ tile = dS K : A K-major (keys along the row), B = K tile read MN-major
 #pragma unroll
-        for (int kk = 0; kk < kTileN / 16; ++kk) {
-          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
-          umma_ss(tdQ, make_smem_desc_sw128(adS + off, 16, 1024), make_smem_desc_sw128(aK + kk * 2048, 16384, 1024),
-                  kIdescQ, kk > 0 ? 1u : 0u);
-        }
+        for (int kk = 0; kk < kTileN / 16; ++kk)
+          umma_ss_w(tdQ, ddS_k.lo + kmajor_step(kk, 16384), ddS_k.hi, dK_m.lo + mnmajor_step(kk), dK_m.hi, kIdescQ,
+                    kk > 0 ? 1u : 0u);
         umma_commit(dq_full);
-        if (i + 1 < n_q) {
-          mbar_wait(qdo_full + ((i + 1) % ST), ((i + 1) / ST) & 1, wctx, kSiteQdoFull);
-          tc_fence_after_sync();
-          issue_s(i + 1);
-          if constexpr (D == 128) {
-            mbar_wait(dq_free, i & 1, wctx, kSiteDqFree);
+        TL(i * 16 + 6);
+        if constexpr (!EARLY) {
+          if (i + 1 < n_q) {
+            mbar_wait(qdo_full + ((i + 1) % ST), ((i + 1) / ST) & 1, wctx, kSiteQdoFull);
             tc_fence_after_sync();
+            issue_s(i + 1);                                      // S columns were released before pds_full(i)
+            mbar_wait(dq_free, i & 1, wctx, kSiteDqFree);       // dQ shares the dP columns
+            tc_fence_after_sync();
+            issue_dp(i + 1);
+            umma_commit(sdp_full);
           }
-          issue_dp(i + 1);
-          umma_commit(sdp_full);
         }
       }
       umma_commit(acc_full);
     }
   } else {
     // ============================ compute warps =====================================
-    const int cw = warp - 2;             // 0..7
+    // 16 warps: warp (quad, cq) owns rows [32*quad, +32) (its tensor-memory lane quarter) and the
+    // 32 columns [32*cq, +32) of every 128 x 128 tile.
+    const int cw = warp - 2;             // 0..15
     const int quad = warp & 3;           // tensor-memory lane quarter of this warp
-    const int half = cw >> 2;            // which 64 columns of the tile
+    const int cq = cw >> 2;              // which 32 columns of the tile
     const int row = quad * 32 + lane;
-    const int tid = threadIdx.x - 64;    // 0..255
+    const int tid = threadIdx.x - 64;    // 0..511
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const float sl2 = a.scale_log2;
     const uint32_t gbh = static_cast<uint32_t>(a.philox_bh_offset + bh);
-    const bool philox = a.dropout_kind == FMHA_DROPOUT_PHILOX;
-    const float dscale = philox ? a.dropout_scale : 1.0f;
+    // With dropout dS is formed as keep*P*dP - P*delta/c and the factor c = 1/(1-p) moves into the
+    // final scaling of dQ and dK (and of dV, whose P operand is unscaled as well).
+    const float inv_c = DROP ? 1.0f / a.dropout_scale : 1.0f;
+    const int cbase = cq * 32;           // first column of this thread within the tile
+    constexpr int DQ = D / 4;            // columns of a [128 x D] accumulator handled by one thread
 
-    if (n_q > 0 && a.mask_kind == FMHA_MASK_KEY_ADDITIVE && tid < kTileN) {
-      const int c = k0 + tid;
-      sMask[tid] = (c < a.S_k) ? reinterpret_cast<const float*>(a.mask)[static_cast<size_t>(b) * a.S_k + c] * kLog2eB : 0.f;
-    }
-    named_bar_sync(1, 256);
-
-    for (int i = 0; i < n_q; ++i) {
-      const int q_row = i * kTileM + row;
-      const bool row_ok = q_row < a.S_q;
-      // lse in the log2 domain; +inf for rows past the end makes their probabilities zero
-      const float lse2 = row_ok ? a.lse[static_cast<size_t>(bh) * a.S_q + q_row] * kLog2eB : INFINITY;
-      const float delta = row_ok ? a.delta[static_cast<size_t>(bh) * a.S_q + q_row] : 0.f;
-
-      mbar_wait(sdp_full, i & 1, wctx, kSiteSdpFull);
-      tc_fence_after_sync();
-#pragma unroll 1
-      for (int c2 = 0; c2 < 2; ++c2) {
-        const int cc = half * 2 + c2;   // 32-column chunk of the tile
-        const int cbase = cc * 32;
-        uint32_t rs[32], rp[32];
-        tmem_ld32(tmem_base + lane_addr + kColS + cbase, rs);
-        tmem_ld32(tmem_base + lane_addr + kColdP + cbase, rp);
-        tmem_wait_ld();
-        float p[32];
-        if (a.mask_kind == FMHA_MASK_KEY_ADDITIVE) {
-#pragma unroll
-          for (int k = 0; k < 32; ++k) p[k] = fast_exp2(fmaf(__uint_as_float(rs[k]), sl2, sMask[cbase + k] - lse2));
-        } else {
-#pragma unroll
-          for (int k = 0; k < 32; ++k) p[k] = fast_exp2(fmaf(__uint_as_float(rs[k]), sl2, -lse2));
-        }
-        if (cbase + 32 > n_cols) {
-#pragma unroll
-          for (int k = 0; k < 32; ++k)
-            if (cbase + k >= n_cols) p[k] = 0.f;
-        }
-        uint32_t keep01[8], keep23[8];  // 16-bit lane masks, two elements each
-        if (philox) {
-#pragma unroll
-          for (int d = 0; d < 2; ++d) {
-            const U4 draw = dropout_draw(a.philox_seed, a.philox_offset, gbh, static_cast<uint32_t>(q_row),
-                                         static_cast<uint32_t>((k0 + cbase) / 16 + d));
-            const uint32_t w[4] = {draw.x, draw.y, draw.z, draw.w};
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const uint32_t keep = dropout_keep_bits(w[k], a.philox_thr);
-              keep01[d * 4 + k] = prmt(keep, 0u, 0x9988u);
-              keep23[d * 4 + k] = prmt(keep, 0u, 0xBBAAu);
-            }
-          }
-        }
-        // dS = P * (keep*c*dP - delta), computed in fp32; the keep decision of element e is bit
-        // (16*(e&1)) of its pair mask.
-        uint32_t pk_p[16], pk_ds[16];
-#pragma unroll
-        for (int k = 0; k < 16; ++k) {
-          float dp0 = __uint_as_float(rp[2 * k]), dp1 = __uint_as_float(rp[2 * k + 1]);
-          uint32_t pm = 0xffffffffu;
-          if (philox) {
-            pm = (k & 1) ? keep23[k >> 1] : keep01[k >> 1];
-            dp0 = (pm & 0x0000ffffu) ? dp0 * dscale : 0.f;
-            dp1 = (pm & 0xffff0000u) ? dp1 * dscale : 0.f;
-          }
-          const float ds0 = p[2 * k] * (dp0 - delta);
-          const float ds1 = p[2 * k + 1] * (dp1 - delta);
-          pk_p[k] = pack2<BF16>(p[2 * k], p[2 * k + 1]) & pm;
-          pk_ds[k] = pack2<BF16>(ds0, ds1);
-        }
-        uint8_t* tileP = sP + (cc / 2) * 16384;
-        uint8_t* tileS = sdS + (cc / 2) * 16384;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const uint32_t off = sw128_offset(row, (cc % 2) * 4 + q);
-          *reinterpret_cast<uint4*>(tileP + off) = make_uint4(pk_p[q * 4], pk_p[q * 4 + 1], pk_p[q * 4 + 2], pk_p[q * 4 + 3]);
-          *reinterpret_cast<uint4*>(tileS + off) = make_uint4(pk_ds[q * 4], pk_ds[q * 4 + 1], pk_ds[q * 4 + 2], pk_ds[q * 4 + 3]);
-        }
+    if constexpr (KEYADD) {
+      if (n_q > 0 && tid < kTileN) {
+        const int c = k0 + tid;
+        sMask[tid] = (c < a.S_k) ? reinterpret_cast<const float*>(a.mask)[static_cast<size_t>(b) * a.S_k + c] * kLog2eB : 0.f;
       }
-      fence_proxy_async_smem();
-      tc_fence_before_sync();
-      mbar_arrive(pds_full);
+    }
+    named_bar_sync(1, kComputeThreads);
 
-      // ---- dQ tile -> global accumulator --------------------------------------------
-      mbar_wait(dq_full, i & 1, wctx, kSiteDqFull);
+    // dQ tile of query tile `it` -> global fp32 accumulator
+    auto dq_readout = [&](int it) {
+      mbar_wait(dq_full, it & 1, wctx, kSiteDqFull);
       tc_fence_after_sync();
-      {
-        float* dst = a.dq_accum + (static_cast<size_t>(bh) * a.S_q_pad + i * kTileM + row) * D + half * (D / 2);
+      float* dst = a.dq_accum + (static_cast<size_t>(bh) * a.S_q_pad + it * kTileM + row) * D + cq * DQ;
 #pragma unroll
-        for (int c = 0; c < D / 64; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tmem_base + lane_addr + kColdQ + half * (D / 2) + c * 32, r);
-          tmem_wait_ld();
-          if (*abort_flag == 0) {
+      for (int c = 0; c < DQ / 16; ++c) {
+        uint32_t r[16];
+        tmem_ld16(tmem_base + lane_addr + kColdQ + cq * DQ + c * 16, r);
+        tmem_wait_ld();
+        if (*abort_flag == 0) {
 #pragma unroll
-            for (int q = 0; q < 8; ++q)
-              red_add_v4(dst + c * 32 + q * 4, __uint_as_float(r[q * 4]), __uint_as_float(r[q * 4 + 1]),
-                         __uint_as_float(r[q * 4 + 2]), __uint_as_float(r[q * 4 + 3]));
-          }
+          for (int q = 0; q < 4; ++q)
+            red_add_v4(dst + c * 16 + q * 4, __uint_as_float(r[q * 4]), __uint_as_float(r[q * 4 + 1]),
+                       __uint_as_float(r[q * 4 + 2]), __uint_as_float(r[q * 4 + 3]));
         }
       }
       tc_fence_before_sync();
       mbar_arrive(dq_free);
+    };
+
+    float lse2_next = INFINITY, delta_next = 0.f;
+    if (n_q > 0 && row < a.S_q) {
+      lse2_next = a.lse[static_cast<size_t>(bh) * a.S_q + row] * kLog2eB;
+      delta_next = a.delta[static_cast<size_t>(bh) * a.S_q + row] * inv_c;
     }
+
+    for (int i = 0; i < n_q; ++i) {
+      const int q_row = i * kTileM + row;
+      // lse in the log2 domain; +inf for rows past the end makes their probabilities zero
+      const float neg_lse2 = -lse2_next;
+      const float delta = delta_next;
+      {
+        const int nr = q_row + kTileM;  // prefetch the statistics of the next tile's row
+        const bool ok = (i + 1 < n_q) && nr < a.S_q;
+        lse2_next = ok ? a.lse[static_cast<size_t>(bh) * a.S_q + nr] * kLog2eB : INFINITY;
+        delta_next = ok ? a.delta[static_cast<size_t>(bh) * a.S_q + nr] * inv_c : 0.f;
+      }
+
+      if (tid == 0) TL(i * 16 + 8);
+      mbar_wait(sdp_full, i & 1, wctx, kSiteSdpFull);
+      if (tid == 0) TL(i * 16 + 9);
+      tc_fence_after_sync();
+      uint32_t rs[32], rp[32];
+      tmem_ld32(tmem_base + lane_addr + kColS + cbase, rs);
+      tmem_ld32(tmem_base + lane_addr + kColdP + cbase, rp);
+      tmem_wait_ld_dep(rs);
+      tmem_wait_ld_dep(rp);
+      tc_fence_before_sync();
+      mbar_arrive(sdp_free);   // the tensor core may overwrite S and dP now
+      if (tid == 0) TL(i * 16 + 10);
+
+      uint32_t pk_p[16], pk_ds[16];  // 32 columns: 16 packed pairs each
+      auto chunk = [&](auto edge_tag) {
+        constexpr bool EDGE = decltype(edge_tag)::value;
+        const float2 sl22 = make_float2(sl2, sl2);
+        const float2 nl2 = make_float2(neg_lse2, neg_lse2);
+        const float2 nd2 = make_float2(-delta, -delta);
+        [[maybe_unused]] uint32_t w[8];
+        if constexpr (DROP) {
+#pragma unroll
+          for (int d = 0; d < 2; ++d) {
+            const U4 draw = dropout_draw_keys(a.philox_keys, a.philox_offset, gbh, static_cast<uint32_t>(q_row),
+                                         static_cast<uint32_t>((k0 + cbase) / 16 + d));
+            w[d * 4 + 0] = (draw.x & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
+            w[d * 4 + 1] = (draw.y & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
+            w[d * 4 + 2] = (draw.z & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
+            w[d * 4 + 3] = (draw.w & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+          float2 x = make_float2(__uint_as_float(rs[2 * k]), __uint_as_float(rs[2 * k + 1]));
+          if constexpr (KEYADD) {
+            const float2 mk = *reinterpret_cast<const float2*>(sMask + cbase + 2 * k);
+            x = __fadd2_rn(__ffma2_rn(x, sl22, mk), nl2);
+          } else {
+            x = __ffma2_rn(x, sl22, nl2);
+          }
+          float2 p;
+          p.x = fast_exp2(x.x);
+          p.y = fast_exp2(x.y);
+          if constexpr (EDGE) {                            // keys past the valid length / tensor edge
+            if (cbase + 2 * k >= n_cols) p.x = 0.f;
+            if (cbase + 2 * k + 1 >= n_cols) p.y = 0.f;
+          }
+          const float2 dp = make_float2(__uint_as_float(rp[2 * k]), __uint_as_float(rp[2 * k + 1]));
+          float2 pkeep = p;
+          if constexpr (DROP) {
+            // bit 7 of byte e of the keep word decides element e; the permute smears it over 32 bits
+            const uint32_t kw = w[k >> 1];
+            const uint32_t m0 = prmt(kw, 0u, (k & 1) ? 0xAAAAu : 0x8888u);
+            const uint32_t m1 = prmt(kw, 0u, (k & 1) ? 0xBBBBu : 0x9999u);
+            pkeep.x = __uint_as_float(__float_as_uint(p.x) & m0);
+            pkeep.y = __uint_as_float(__float_as_uint(p.y) & m1);
+          }
+          const float2 ds = __ffma2_rn(pkeep, dp, __fmul2_rn(p, nd2));
+          pk_p[k] = pack2<BF16>(pkeep.x, pkeep.y);
+          pk_ds[k] = pack2<BF16>(ds.x, ds.y);
+        }
+      };
+      if (n_cols >= kTileN) chunk(std::false_type{});
+      else chunk(std::true_type{});
+
+      if (tid == 0) TL(i * 16 + 11);
+      // NB == 1: the MMAs that read P/dS of tile i-1 are complete (dq_readout(i-1) ran at the end of
+      // the previous iteration), so the single buffer can be overwritten.
+      {
+        // columns [32*cq, +32) of row `row`: 64 bytes = 16-byte chunks (cq%2)*4 .. +3 of sub-tile cq/2
+        const uint32_t bufP = smem_u32(sP + (i % NB) * kPdsBytes + (cq >> 1) * 16384);
+        const uint32_t bufS = smem_u32(sdS + (i % NB) * kPdsBytes + (cq >> 1) * 16384);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t off = sw128_offset(row, (cq & 1) * 4 + q);
+          sts128(bufP + off, pk_p[q * 4], pk_p[q * 4 + 1], pk_p[q * 4 + 2], pk_p[q * 4 + 3]);
+          sts128(bufS + off, pk_ds[q * 4], pk_ds[q * 4 + 1], pk_ds[q * 4 + 2], pk_ds[q * 4 + 3]);
+        }
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(pds_full);
+      if (tid == 0) TL(i * 16 + 12);
+      if constexpr (NB == 2) {
+        if (i > 0) dq_readout(i - 1);   // one iteration late: dV/dK/dQ of tile i-1 overlapped this tile's math
+      } else {
+        dq_readout(i);                  // dQ shares columns with dP: it must be out before dP of tile i+1
+      }
+      if (tid == 0) TL(i * 16 + 13);
+    }
+    if constexpr (NB == 2) {
+      if (n_q > 0) dq_readout(n_q - 1);
+    }
+    if (tid == 0) TL(202);
 
     // ---- epilogue: dK, dV -> 16-bit -> shared memory -> TMA store ----------------------
     if (n_q > 0) {
       mbar_wait(acc_full, 0, wctx, kSiteAccFull);
       tc_fence_after_sync();
     }
-    // sP / sdS are free (every MMA that read them has completed); dV goes to sP, dK to sdS.
+    // The P/dS buffers are free (every MMA that read them has completed); dV goes to sP, dK to sdS.
+    const float dscale = DROP ? a.dropout_scale : 1.0f;
 #pragma unroll
     for (int which = 0; which < 2; ++which) {
-      const uint32_t col = (which == 0 ? kColdV : kColdK) + half * (D / 2);
-      const float mul = (which == 0) ? dscale : a.scale;
+      const float mul = (which == 0) ? dscale : a.scale * dscale;
       uint8_t* stage = (which == 0) ? sP : sdS;
 #pragma unroll
-      for (int c = 0; c < D / 64; ++c) {
-        uint32_t r[32];
+      for (int c = 0; c < DQ / 16; ++c) {
+        const int dcol = cq * DQ + c * 16;               // first of 16 accumulator columns
+        uint32_t r[16];
         if (n_q > 0) {
-          tmem_ld32(tmem_base + lane_addr + col + c * 32, r);
+          tmem_ld16(tmem_base + lane_addr + (which == 0 ? kColdV : kColdK) + dcol, r);
           tmem_wait_ld();
         } else {
 #pragma unroll
-          for (int k = 0; k < 32; ++k) r[k] = 0u;
+          for (int k = 0; k < 16; ++k) r[k] = 0u;
         }
-        const int cc = (half * (D / 2) + c * 32) / 32;  // 32-element chunk within the D axis
-        uint8_t* tile = stage + (cc / 2) * 16384;
+        uint8_t* tile = stage + (dcol / 64) * 16384;     // 64-column sub-tile; 16 columns = two 16-byte chunks
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
+        for (int q = 0; q < 2; ++q) {
           uint4 w;
           w.x = pack2<BF16>(__uint_as_float(r[q * 8 + 0]) * mul, __uint_as_float(r[q * 8 + 1]) * mul);
           w.y = pack2<BF16>(__uint_as_float(r[q * 8 + 2]) * mul, __uint_as_float(r[q * 8 + 3]) * mul);
           w.z = pack2<BF16>(__uint_as_float(r[q * 8 + 4]) * mul, __uint_as_float(r[q * 8 + 5]) * mul);
           w.w = pack2<BF16>(__uint_as_float(r[q * 8 + 6]) * mul, __uint_as_float(r[q * 8 + 7]) * mul);
-          *reinterpret_cast<uint4*>(tile + sw128_offset(row, (cc % 2) * 4 + q)) = w;
+          *reinterpret_cast<uint4*>(tile + sw128_offset(row, ((dcol % 64) / 8) + q)) = w;
         }
       }
     }
     fence_proxy_async_smem();
-    named_bar_sync(1, 256);
+    named_bar_sync(1, kComputeThreads);
+    if (tid == 0) TL(203);
     if (tid == 0) {
       if (*abort_flag == 0) {
 #pragma unroll
@@ -490,7 +574,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
         }
         tma_store_commit();
       }
-      tma_store_wait_all();
+      tma_store_wait_read();
+      TL(204);
     }
   }
 
@@ -504,17 +589,24 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+#undef TL
 }
 
 // ---------------------------------------------------------------------------------------
 // launchers
 // ---------------------------------------------------------------------------------------
-template <int D, bool BF16>
+template <int D, bool BF16, bool KEYADD, bool DROP>
 static int launch_bwd_impl(const BwdArgs& a, cudaStream_t stream) {
   using L = BwdSmem<D>;
-  auto kfn = fmha_bwd_kernel<D, BF16>;
-  cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynBytes);
-  if (e != cudaSuccess) return static_cast<int>(e);
+  auto kfn = fmha_bwd_kernel<D, BF16, KEYADD, DROP>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
   dim3 grid((a.S_k + kTileN - 1) / kTileN, a.H, a.B);
   kfn<<<grid, kBwdThreads, L::kDynBytes, stream>>>(a);
   return static_cast<int>(cudaGetLastError());
@@ -522,8 +614,27 @@ static int launch_bwd_impl(const BwdArgs& a, cudaStream_t stream) {
 
 int launch_bwd(const BwdArgs& a, int D, int dtype, cudaStream_t stream) {
   const bool bf = dtype == FMHA_DTYPE_BF16;
-  if (D == 64) return bf ? launch_bwd_impl<64, true>(a, stream) : launch_bwd_impl<64, false>(a, stream);
-  if (D == 128) return bf ? launch_bwd_impl<128, true>(a, stream) : launch_bwd_impl<128, false>(a, stream);
+  const bool keyadd = a.mask_kind == FMHA_MASK_KEY_ADDITIVE;
+  const bool drop = a.dropout_kind == FMHA_DROPOUT_PHILOX;
+#define FMHA_BWD_CASE(DD, BF, KA, DR) \
+  if (D == DD && bf == BF && keyadd == KA && drop == DR) return launch_bwd_impl<DD, BF, KA, DR>(a, stream);
+  FMHA_BWD_CASE(64, false, false, false)
+  FMHA_BWD_CASE(64, false, false, true)
+  FMHA_BWD_CASE(64, false, true, false)
+  FMHA_BWD_CASE(64, false, true, true)
+  FMHA_BWD_CASE(64, true, false, false)
+  FMHA_BWD_CASE(64, true, false, true)
+  FMHA_BWD_CASE(64, true, true, false)
+  FMHA_BWD_CASE(64, true, true, true)
+  FMHA_BWD_CASE(128, false, false, false)
+  FMHA_BWD_CASE(128, false, false, true)
+  FMHA_BWD_CASE(128, false, true, false)
+  FMHA_BWD_CASE(128, false, true, true)
+  FMHA_BWD_CASE(128, true, false, false)
+  FMHA_BWD_CASE(128, true, false, true)
+  FMHA_BWD_CASE(128, true, true, false)
+  FMHA_BWD_CASE(128, true, true, true)
+#undef FMHA_BWD_CASE
   return static_cast<int>(cudaErrorInvalidValue);
 }
 

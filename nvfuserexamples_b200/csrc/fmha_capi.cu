@@ -173,6 +173,7 @@ int fmha_sm100_fwd(const fmha_fwd_params* p, void* stream) {
     if (thr == 0) a.dropout_kind = FMHA_DROPOUT_NONE;  // nothing is ever dropped
   }
   a.philox_seed = p->philox_seed;
+  a.philox_keys = philox_round_keys(p->philox_seed);
   a.philox_offset = static_cast<uint32_t>(p->philox_offset);
   a.philox_bh_offset = p->philox_bh_offset;
   a.save_softmax = p->save_softmax;
@@ -262,6 +263,7 @@ int fmha_sm100_bwd(const fmha_bwd_params* p, void* stream_) {
     if (thr == 0) a.dropout_kind = FMHA_DROPOUT_NONE;
   }
   a.philox_seed = p->philox_seed;
+  a.philox_keys = philox_round_keys(p->philox_seed);
   a.philox_offset = static_cast<uint32_t>(p->philox_offset);
   a.philox_bh_offset = p->philox_bh_offset;
   a.status = p->status;
@@ -274,7 +276,8 @@ int fmha_sm100_bwd(const fmha_bwd_params* p, void* stream_) {
   e = launch_bwd(a, p->D, p->dtype, stream);
   if (e != 0) return cuda_fail(static_cast<cudaError_t>(e));
   if (!(p->flags & FMHA_FLAG_BWD_SKIP_FINISH)) {
-    e = launch_bwd_finish(dq_accum, tdq, p->B, p->H, p->S_q, s_q_pad, p->D, p->dtype, p->scale, stream);
+    // the main kernel leaves the dropout factor 1/(1-p) out of dS; it is applied here (and to dK, dV in its epilogue)
+    e = launch_bwd_finish(dq_accum, tdq, p->B, p->H, p->S_q, s_q_pad, p->D, p->dtype, p->scale * a.dropout_scale, stream);
     if (e != 0) return cuda_fail(static_cast<cudaError_t>(e));
   }
   return FMHA_OK;

@@ -90,7 +90,7 @@ __device__ __forceinline__ void softmax_chunk(const uint32_t (&r)[32], int cbase
   if constexpr (DROP) {
 #pragma unroll
     for (int d = 0; d < 2; ++d) {
-      const U4 draw = dropout_draw(a.philox_seed, a.philox_offset, gbh, q_row, kb0 + d);
+      const U4 draw = dropout_draw_keys(a.philox_keys, a.philox_offset, gbh, q_row, kb0 + d);
       const uint32_t w[4] = {draw.x, draw.y, draw.z, draw.w};
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
@@ -201,31 +201,27 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D>::kCtasPerSm) fmha_fwd_fa
     if (lane == 0) {
       const uint32_t tS = tmem_base + kColS;
       const uint32_t tO = tmem_base + kColO;
-      const uint32_t sQ_addr = smem_u32(sQ);
+      const DescWords dq = desc_words(make_smem_desc_sw128(smem_u32(sQ), 16, 1024));
       mbar_wait(q_full, 0, wctx, kFQFull);
       for (int j = 0; j < n_kv; ++j) {
         const int s = j % ST;
         const uint32_t ph = (j / ST) & 1;
+        const DescWords dk = desc_words(make_smem_desc_sw128(smem_u32(sK + s * L::kTileBytes), 16, 1024));
+        const DescWords dv = desc_words(make_smem_desc_sw128(smem_u32(sV + s * L::kTileBytes), L::kSubTile, 1024));
         mbar_wait(k_full + s, ph, wctx, kFKFull);
         tc_fence_after_sync();
-        const uint32_t sK_addr = smem_u32(sK + s * L::kTileBytes);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t offq = (kk / 4) * 16384 + (kk % 4) * 32;
-          const uint32_t offk = (kk / 4) * L::kSubTile + (kk % 4) * 32;
-          umma_ss(tS, make_smem_desc_sw128(sQ_addr + offq, 16, 1024), make_smem_desc_sw128(sK_addr + offk, 16, 1024),
-                  kIdescQK, kk > 0 ? 1u : 0u);
-        }
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_ss_w(tS, dq.lo + kmajor_step(kk, 16384), dq.hi, dk.lo + kmajor_step(kk, L::kSubTile), dk.hi, kIdescQK,
+                    kk > 0 ? 1u : 0u);
         umma_commit(k_empty + s);
         umma_commit(s_full);
         mbar_wait(p_full, j & 1, wctx, kFPFull);
         mbar_wait(v_full + s, ph, wctx, kFVFull);
         tc_fence_after_sync();
-        const uint32_t sV_addr = smem_u32(sV + s * L::kTileBytes);
 #pragma unroll
         for (int kk = 0; kk < TN / 16; ++kk)
-          umma_ts(tO, tS + kk * 8, make_smem_desc_sw128(sV_addr + kk * 2048, L::kSubTile, 1024), kIdescPV,
-                  (j > 0 || kk > 0) ? 1u : 0u);
+          umma_ts_w(tO, tS + kk * 8, dv.lo + mnmajor_step(kk), dv.hi, kIdescPV, (j > 0 || kk > 0) ? 1u : 0u);
         umma_commit(v_empty + s);
       }
       umma_commit(o_full);

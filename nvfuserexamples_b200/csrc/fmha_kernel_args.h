@@ -6,6 +6,7 @@
 #include <stdint.h>
 
 #include "../../include/fmha_sm100.h"
+#include "philox.cuh"
 
 namespace fmha {
 
@@ -30,6 +31,7 @@ struct FwdArgs {
   float dropout_scale;   // multiplier applied to kept probabilities
   uint32_t philox_thr;   // 7-bit threshold
   uint64_t philox_seed;
+  PhiloxKeys philox_keys;  // round keys of philox_seed
   uint32_t philox_offset;
   int philox_bh_offset;
   void* save_softmax;
@@ -59,6 +61,7 @@ struct BwdArgs {
   float dropout_scale;
   uint32_t philox_thr;
   uint64_t philox_seed;
+  PhiloxKeys philox_keys;  // round keys of philox_seed
   uint32_t philox_offset;
   int philox_bh_offset;
   int* status;

@@ -58,6 +58,45 @@ FMHA_HD U4 philox4x32_10(uint32_t k0, uint32_t k1, uint32_t c0, uint32_t c1, uin
   return out;
 }
 
+// Same generator with the ten round keys supplied by the caller (key r = seed word + r * Weyl
+// constant).  The kernels receive them as launch parameters, so the per-round key update costs
+// no instruction: the key is a constant-bank operand of the XOR.
+struct PhiloxKeys {
+  uint32_t k[20];  // k[2r], k[2r+1] = keys of round r
+};
+FMHA_HD PhiloxKeys philox_round_keys(uint64_t seed) {
+  PhiloxKeys ks;
+  uint32_t k0 = static_cast<uint32_t>(seed), k1 = static_cast<uint32_t>(seed >> 32);
+  for (int r = 0; r < 10; ++r) {
+    ks.k[2 * r] = k0;
+    ks.k[2 * r + 1] = k1;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  return ks;
+}
+FMHA_HD U4 philox4x32_10_keys(const PhiloxKeys& ks, uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3) {
+  constexpr uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u;
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
+  for (int r = 0; r < 10; ++r) {
+    uint32_t hi0, lo0, hi1, lo1;
+    mulhilo32(M0, c0, hi0, lo0);
+    mulhilo32(M1, c2, hi1, lo1);
+    const uint32_t n0 = hi1 ^ c1 ^ ks.k[2 * r];
+    const uint32_t n2 = hi0 ^ c3 ^ ks.k[2 * r + 1];
+    c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;
+  }
+  U4 out;
+  out.x = c0; out.y = c1; out.z = c2; out.w = c3;
+  return out;
+}
+// The 16 random bytes that decide keys [16*kb, 16*kb+16) of query row `row` in head `bh`.
+FMHA_HD U4 dropout_draw_keys(const PhiloxKeys& ks, uint32_t offset, uint32_t bh, uint32_t row, uint32_t kb) {
+  return philox4x32_10_keys(ks, row, kb, bh, offset);
+}
+
 // T = round(128 p), clamped so that at least 1/128 of the entries survive.
 FMHA_HD int dropout_threshold(float p_drop) {
   int t = static_cast<int>(p_drop * 128.0f + 0.5f);

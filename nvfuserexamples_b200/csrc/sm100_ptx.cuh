@@ -66,6 +66,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// try_wait with a suspend-time hint: the thread may sleep in hardware up to `hint_ns` before the
+// instruction returns, which keeps waiting warps out of the issue slots of working ones.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+
 // Wall-time limit of one wait.  Legitimate waits inside a CTA last microseconds.
 constexpr uint64_t kWaitLimitNs = 400ull * 1000ull * 1000ull;
 
@@ -83,8 +99,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   uint64_t t0 = 0;
   uint32_t spins = 0;
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 0xff) == 0) {
+    if (mbar_try_wait_hint(bar, parity, 4000u)) return true;
+    if ((++spins & 0x3f) == 0) {
       if (*ctx.abort_flag) return false;
       const uint64_t now = globaltimer_ns();
       if (t0 == 0) {
@@ -220,6 +236,52 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The issuing thread is a single lane, so every instruction between two tcgen05.mma counts
+// (a 128x64x16 MMA occupies the tensor core for only ~48 cycles).  These variants take the
+// descriptor as (low word, high word): the caller builds the descriptor of a tile once and per
+// k-step only adds a constant to the low word (the 16-byte-unit start address lives in its low
+// 14 bits and a tile never crosses the 256 KB field).
+struct DescWords {
+  uint32_t lo, hi;
+};
+__device__ __forceinline__ DescWords desc_words(uint64_t d) {
+  DescWords w;
+  w.lo = static_cast<uint32_t>(d);
+  w.hi = static_cast<uint32_t>(d >> 32);
+  return w;
+}
+__device__ __forceinline__ void umma_ss_w(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_ts_w(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Low-word increments: k-step kk of a K-major operand (16 elements = 32 bytes, 64-column
+// sub-tiles `sub` bytes apart) and of an MN-major operand (16 rows = 2048 bytes).
+__host__ __device__ constexpr uint32_t kmajor_step(int kk, int sub) { return static_cast<uint32_t>(((kk / 4) * sub + (kk % 4) * 32) >> 4); }
+__host__ __device__ constexpr uint32_t mnmajor_step(int kk) { return static_cast<uint32_t>((kk * 2048) >> 4); }
+
 // Arrive on `bar` when every tcgen05.mma issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -307,6 +369,11 @@ __device__ __forceinline__ float fast_log2(float x) {
   float y;
   asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// 16-byte store to shared memory through a 32-bit shared address (one STS.128, no generic address).
+__device__ __forceinline__ void sts128(uint32_t saddr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(saddr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
 }
 
 // Byte offset of 16-byte chunk `chunk` (0..7) of row `row` inside a [rows x 128 B] tile
