@@ -40,10 +40,11 @@ enum FastWaitSite {
 // TN = keys per step.  D = 64 uses 64-key steps: S (64 columns) + O (64 columns) = 128 tensor-memory
 // columns and 48 KB of shared memory per CTA, so FOUR CTAs share an SM and their softmax and
 // tensor-core phases interleave; D = 128 uses 128-key steps and two CTAs per SM.
-template <int D>
+template <int D, bool DROP = false>
 struct FastSmem {
   static constexpr int TN = (D == 64) ? 64 : 128;
-  static constexpr int kCtasPerSm = (D == 64) ? 4 : 2;
+  // With dropout the Philox state needs registers: three CTAs (112 registers per thread) instead of four (80).
+  static constexpr int kCtasPerSm = (D == 64) ? (DROP ? 3 : 4) : 2;
   static constexpr int kStages = (D == 64) ? 2 : 1;
   static constexpr int kQBytes = kTileM * D * 2;
   static constexpr int kTileBytes = TN * D * 2;    // one K or V tile
@@ -106,7 +107,7 @@ __device__ __forceinline__ void softmax_chunk(const uint32_t (&r)[32], int cbase
 }  // namespace
 
 template <int D, bool BF16, bool KEYADD, bool DROP>
-__global__ void __launch_bounds__(kThreads, FastSmem<D>::kCtasPerSm) fmha_fwd_fast_kernel(const __grid_constant__ FwdArgs a) {
+__global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_fwd_fast_kernel(const __grid_constant__ FwdArgs a) {
   using L = FastSmem<D>;
   constexpr int ST = L::kStages;
   constexpr int TN = L::TN;
