@@ -133,6 +133,7 @@ def run_reference(args, rank):
     if rank != 0:
         return
     import torch
+    torch.set_num_threads(len(os.sched_getaffinity(0)))  # torchrun pins OMP_NUM_THREADS=1: use every host core we may
     sample_b = 2
     step, flops = cpu_composite_step(sample_b, 1004)
     steps = max(1, min(args.steps, 20))
@@ -343,6 +344,7 @@ def run_ours(args, rank, world, local_rank):
     # ---- CPU baseline (N = 1 only, bounded sample) ---------------------------------------------------
     cpu = None
     if rank == 0 and world == 1:
+        torch.set_num_threads(len(os.sched_getaffinity(0)))
         cstep, cflops = cpu_composite_step(2, 1004)
         n = 0
         cstep()

