@@ -40,9 +40,10 @@ B0, H, S, D = 32, 16, 512, 64
 LEN_RANGE = (256, 512)
 P_DROP = 0.1
 METRIC = "fused MHA fwd+bwd TFLOP/s at BERT-large shape (executed flops)"
-# ncu capture of fmha_bwd_kernel<64,fp16> at this workload (profiles/bwd_kernel_bert_large_train.md):
-# dram__bytes_read.sum + dram__bytes_write.sum per launch, bytes.  None until captured.
-BWD_KERNEL_DRAM_TRAFFIC = None
+# ncu capture of fmha_bwd_kernel<64,fp16,dropout> (profiles/bwd_kernel_b16_h16_s512_d64.md): at B=16 of this
+# workload dram__bytes_read.sum + dram__bytes_write.sum = 97.58 MB + 25.42 MB per launch; DRAM traffic of
+# the kernel is proportional to the batch (every CTA touches only its own head), so B=32 is twice that.
+BWD_KERNEL_DRAM_TRAFFIC_B16 = 97.58e6 + 25.42e6
 
 
 def executed_flops(lens, h, s_q, d, mult, granule=128):
@@ -298,12 +299,12 @@ def run_ours(args, rank, world, local_rank):
     exe_bwd = sum(executed_flops(l, H, S, D, 10.0) for l in lens_host) / n_sets
     exe_fwd = sum(executed_flops(l, H, S, D, 4.0, 64) for l in lens_host) / n_sets
     ach = exe_bwd / (bwd_main_ms * 1e-3) / 1e12
-    roofline = {"kernel": "fmha_bwd_kernel<64,fp16>", "bound": "tensor", "achieved": ach, "peak": pk["tflops"],
-                "unit": "TFLOP/s", "frac": ach / pk["tflops"], "traffic": BWD_KERNEL_DRAM_TRAFFIC,
+    roofline = {"kernel": "fmha_bwd_kernel<64,fp16,seqlen,dropout>", "bound": "tensor", "achieved": ach, "peak": pk["tflops"],
+                "unit": "TFLOP/s", "frac": ach / pk["tflops"], "traffic": BWD_KERNEL_DRAM_TRAFFIC_B16 * b_loc / 16.0, "traffic_unit": "bytes per launch (ncu at B=16, scaled by batch)",
                 "peak_source": f"{pk['source']} bf16 burst", "ms_per_launch": bwd_main_ms,
                 "algorithmic_flops_per_launch": exe_bwd}
     ach_f = exe_fwd / (fwd_ms * 1e-3) / 1e12
-    roofline_fwd = {"kernel": "fmha_fwd_kernel<64,fp16>", "bound": "tensor", "achieved": ach_f, "peak": pk["tflops"],
+    roofline_fwd = {"kernel": "fmha_fwd_fast_kernel<64,fp16,seqlen,dropout>", "bound": "tensor", "achieved": ach_f, "peak": pk["tflops"],
                     "unit": "TFLOP/s", "frac": ach_f / pk["tflops"], "ms_per_launch": fwd_ms}
 
     # ---- end to end through the operator layer, host buffers in and out --------------------------

@@ -33,6 +33,7 @@ namespace fmha {
 
 namespace {
 
+constexpr uint32_t kComputeSleepNs = 48;  // pause between barrier polls of the compute warps
 constexpr int kComputeThreads = 512;               // 16 compute warps
 constexpr int kBwdThreads = 64 + kComputeThreads;   // + producer warp + MMA warp
 constexpr float kLog2eB = 1.4426950408889634f;
@@ -398,7 +399,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
     // Every warp polls the mbarrier itself: funnelling the wait through one warp and a named barrier
     // was measured 8 % slower (it removes the skew between warps that lets their phases overlap).
     auto wait_all = [&](uint64_t* bar, uint32_t parity, int site) {
-      mbar_wait(bar, parity, wctx, site);
+      mbar_wait(bar, parity, wctx, site, kComputeSleepNs);
       tc_fence_after_sync();
     };
 

@@ -254,7 +254,7 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
               (c < a.S_k) ? reinterpret_cast<const float*>(a.mask)[static_cast<size_t>(b) * a.S_k + c] * kLog2eF : 0.f;
         named_bar_sync(1, 128);
       }
-      mbar_wait(s_full, j & 1, wctx, kFSFull);
+      mbar_wait(s_full, j & 1, wctx, kFSFull, 32);
       tc_fence_after_sync();
 
       // ---- sweep 1: row maximum --------------------------------------------------------
@@ -344,7 +344,7 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
     }
 
     // ---- epilogue ------------------------------------------------------------------------
-    mbar_wait(o_full, 0, wctx, kFOFull);
+    mbar_wait(o_full, 0, wctx, kFOFull, 32);
     tc_fence_after_sync();
     const float l_sum = sum2.x + sum2.y;
     const float out_scale = (DROP ? a.dropout_scale : 1.0f) / l_sum;

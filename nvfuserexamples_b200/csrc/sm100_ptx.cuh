@@ -94,11 +94,16 @@ struct WaitCtx {
 
 // Waits for `parity` of `bar`.  Returns false if the wait was given up (either because
 // this wait ran out of time, or because another thread of the CTA already did).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, int where) {
+// `sleep_ns` > 0 makes the waiter sleep between polls: for the many compute threads, whose polling
+// would otherwise take issue slots from the warps that are still working.  The single MMA and
+// TMA threads poll without sleeping (their wake-up latency is on the critical path).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, int where,
+                                          uint32_t sleep_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   uint32_t spins = 0;
   while (true) {
+    if (sleep_ns) __nanosleep(sleep_ns);
     if (mbar_try_wait_hint(bar, parity, 4000u)) return true;
     if ((++spins & 0x3f) == 0) {
       if (*ctx.abort_flag) return false;

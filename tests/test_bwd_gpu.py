@@ -102,3 +102,8 @@ def test_full_size_linearity_in_d_o(cuda_device):
     helpers.assert_close(sl(g1[0]), rdq, "dq slice")
     helpers.assert_close(sl(g1[1]), rdk, "dk slice")
     helpers.assert_close(sl(g1[2]), rdv, "dv slice")
+
+
+def test_long_sequence_head_dim_128_bf16(cuda_device):
+    """The long-sequence training shape (S = 2048, D = 128, bf16, no dropout) on two heads."""
+    _run(cuda_device, 1, 2, 2048, 2048, 128, torch.bfloat16, "seqlen", 0.0, seed=8)
