@@ -45,8 +45,9 @@ enum BwdWaitSite {
 
 template <int D>
 struct BwdSmem {
-  static constexpr int kStages = (D == 64) ? 2 : 1;   // Q / dO stages
-  static constexpr int kPdsBufs = (D == 64) ? 2 : 1;  // P / dS buffers
+  static constexpr int kStages = (D == 64) ? 3 : 1;   // Q / dO stages
+  static constexpr int kPdsBufs = 1;                  // P / dS buffers
+  static constexpr bool kTmaDq = (D == 64);           // dQ tiles leave through shared memory + TMA reduce-add
   static constexpr int kTileBytes = kTileM * D * 2;
   static constexpr int kOffK = 0;
   static constexpr int kOffV = kOffK + kTileBytes;
@@ -54,7 +55,8 @@ struct BwdSmem {
   static constexpr int kOffdO = kOffQ + kStages * kTileBytes;
   static constexpr int kOffP = kOffdO + kStages * kTileBytes;
   static constexpr int kOffdS = kOffP + kPdsBufs * kTileM * kTileN * 2;
-  static constexpr int kOffMask = kOffdS + kPdsBufs * kTileM * kTileN * 2;  // 128 floats
+  static constexpr int kOffDQ = kOffdS + kPdsBufs * kTileM * kTileN * 2;    // fp32 [128 x D] staging of a dQ tile
+  static constexpr int kOffMask = kOffDQ + (kTmaDq ? kTileM * D * 4 : 0);   // 128 floats
   static constexpr int kOffBar = kOffMask + kTileN * 4;
   static constexpr int kNumBars = 7 + 2 * kStages;
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;
@@ -169,6 +171,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
   using L = BwdSmem<D>;
   constexpr int ST = L::kStages;
   constexpr int NB = L::kPdsBufs;
+  constexpr bool TMADQ = L::kTmaDq;
   constexpr bool EARLY = (D == 64);  // S/dP of the next tile are issued before dV/dK/dQ of this one
   constexpr int kTmemCols = 512;
   constexpr uint32_t kColS = 0, kColdP = 128, kColdV = 256, kColdK = 256 + D;
@@ -187,6 +190,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
   uint8_t* sdO = smem + L::kOffdO;
   uint8_t* sP = smem + L::kOffP;
   uint8_t* sdS = smem + L::kOffdS;
+  uint8_t* sDQ = smem + L::kOffDQ;
   float* sMask = reinterpret_cast<float*>(smem + L::kOffMask);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
   uint64_t* kv_full = bars + 0;
@@ -237,6 +241,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
     tma_prefetch_desc(&a.tm_do);
     tma_prefetch_desc(&a.tm_dk);
     tma_prefetch_desc(&a.tm_dv);
+    tma_prefetch_desc(&a.tm_dq);
   }
   if (warp == 1) {
     tmem_alloc(tmem_base_slot, kTmemCols);
@@ -423,6 +428,34 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
       mbar_arrive(dq_free);
     };
 
+    // Same, through shared memory and one TMA reduce-add per 32-column half: the additions are
+    // performed line by line by the TMA unit instead of 2048 scattered 16-byte atomics per tile,
+    // which occupied the compute warps for ~1500 cycles per tile.
+    auto dq_readout_tma = [&](int it) {
+      wait_all(dq_full, it & 1, kSiteDqFull);
+      uint32_t r[16];
+      tmem_ld16(tmem_base + lane_addr + kColdQ + cq * DQ, r);
+      tmem_wait_ld();
+      tc_fence_before_sync();
+      mbar_arrive(dq_free);                          // the dQ columns may be overwritten
+      if (tid == 0) tma_store_wait_read();           // the previous tile's reduce has read the staging buffer
+      named_bar_sync(2, kComputeThreads);
+      {
+        const uint32_t tile = smem_u32(sDQ + (cq >> 1) * 16384);   // 32 fp32 columns = one 128-byte row
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          sts128(tile + sw128_offset(row, (cq & 1) * 4 + q), r[q * 4], r[q * 4 + 1], r[q * 4 + 2], r[q * 4 + 3]);
+      }
+      fence_proxy_async_smem();
+      named_bar_sync(3, kComputeThreads);
+      if (tid == 0 && *abort_flag == 0) {
+        const int row0 = bh * a.S_q_pad + it * kTileM;
+        tma_reduce_add_2d(&a.tm_dq, sDQ, 0, row0);
+        tma_reduce_add_2d(&a.tm_dq, sDQ + 16384, 32, row0);
+        tma_store_commit();
+      }
+    };
+
     float lse2_next = INFINITY, delta_next = 0.f;
     if (n_q > 0 && row < a.S_q) {
       lse2_next = a.lse[static_cast<size_t>(bh) * a.S_q + row] * kLog2eB;
@@ -506,8 +539,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
       else chunk(std::true_type{});
 
       if (tid == 0) TL(i * 16 + 11);
-      // NB == 1: the MMAs that read P/dS of tile i-1 are complete (dq_readout(i-1) ran at the end of
-      // the previous iteration), so the single buffer can be overwritten.
+      if constexpr (TMADQ) {
+        // dQ of the previous tile: waiting for it also guarantees that the MMAs which read the single
+        // P/dS buffer have completed, so it can be overwritten below.
+        if (i > 0) dq_readout_tma(i - 1);
+      }
       {
         // columns [32*cq, +32) of row `row`: 64 bytes = 16-byte chunks (cq%2)*4 .. +3 of sub-tile cq/2
         const uint32_t bufP = smem_u32(sP + (i % NB) * kPdsBytes + (cq >> 1) * 16384);
@@ -522,15 +558,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
       fence_proxy_async_smem();
       mbar_arrive(pds_full);
       if (tid == 0) TL(i * 16 + 12);
-      if constexpr (NB == 2) {
-        if (i > 0) dq_readout(i - 1);   // one iteration late: dV/dK/dQ of tile i-1 overlapped this tile's math
-      } else {
-        dq_readout(i);                  // dQ shares columns with dP: it must be out before dP of tile i+1
-      }
+      if constexpr (!TMADQ) dq_readout(i);   // D = 128: dQ shares columns with dP, it must be out before dP of tile i+1
       if (tid == 0) TL(i * 16 + 13);
     }
-    if constexpr (NB == 2) {
-      if (n_q > 0) dq_readout(n_q - 1);
+    if constexpr (TMADQ) {
+      if (n_q > 0) dq_readout_tma(n_q - 1);
     }
     if (tid == 0) TL(202);
 

@@ -58,6 +58,23 @@ static int make_tmap(CUtensorMap* out, const fmha_tensor4& t, int dtype, int B, 
   return FMHA_OK;
 }
 
+// Tensor map of the fp32 dQ accumulator [rows, D] with a {32 x 128} box and 128-byte swizzle.
+static int make_tmap_accum(CUtensorMap* out, float* ptr, uint64_t rows, int D) {
+  auto enc = get_encode_fn();
+  if (enc == nullptr) return FMHA_ERR_LAUNCH;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(D) * 4};
+  const cuuint32_t box[2] = {32, static_cast<cuuint32_t>(kTileM)};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_cuda_error = static_cast<int>(r);
+    return FMHA_ERR_LAUNCH;
+  }
+  return FMHA_OK;
+}
+
 static bool tensor_ok(const fmha_tensor4& t, int B, int H) {
   if (t.ptr == nullptr) return false;
   if (reinterpret_cast<uintptr_t>(t.ptr) & 15) return false;
@@ -245,6 +262,7 @@ int fmha_sm100_bwd(const fmha_bwd_params* p, void* stream_) {
   if ((rc = make_tmap(&a.tm_do, tdo, p->dtype, p->B, p->H, p->S_q, p->D, kTileM))) return rc;
   if ((rc = make_tmap(&a.tm_dk, tdk, p->dtype, p->B, p->H, p->S_k, p->D, kTileN))) return rc;
   if ((rc = make_tmap(&a.tm_dv, tdv, p->dtype, p->B, p->H, p->S_k, p->D, kTileN))) return rc;
+  if ((rc = make_tmap_accum(&a.tm_dq, dq_accum, static_cast<uint64_t>(bh) * s_q_pad, p->D))) return rc;
   a.B = p->B; a.H = p->H; a.S_q = p->S_q; a.S_k = p->S_k;
   a.scale = p->scale;
   a.scale_log2 = p->scale * 1.4426950408889634f;

@@ -48,6 +48,7 @@ struct BwdArgs {
   alignas(64) CUtensorMap tm_do;
   alignas(64) CUtensorMap tm_dk;
   alignas(64) CUtensorMap tm_dv;
+  alignas(64) CUtensorMap tm_dq;  // fp32 dQ accumulator as [B*H*S_q_pad, D], 32-column boxes (TMA reduce-add)
   int B, H, S_q, S_k;
   float scale;       // softmax scale
   float scale_log2;  // softmax scale * log2(e)

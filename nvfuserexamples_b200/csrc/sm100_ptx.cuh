@@ -165,6 +165,14 @@ __device__ __forceinline__ void tma_store_4d(const void* tmap, const void* smem_
       ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
+// Bulk reduction shared -> global: every element of the 2-D box is ADDED to the tensor in global
+// memory by the TMA unit (asynchronous, tracked by the same bulk groups as stores).
+__device__ __forceinline__ void tma_reduce_add_2d(const void* tmap, const void* smem_src, int c0, int c1) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+      ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
+      : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Waits until the shared-memory source of every committed store has been read.
 __device__ __forceinline__ void tma_store_wait_read() {
