@@ -14,7 +14,8 @@
 //                      dV += (keep*P)^T dO     dK += dS^T Q     dQ_tile = dS K
 //                    P and dS go through shared memory (16-bit, 128-byte swizzle) and are read
 //                    by the tensor core both as K-major (dQ) and as MN-major (dV, dK) operands;
-//                    dQ tiles are added to the fp32 accumulator with vector red.global.add;
+//                    dQ tiles are staged in shared memory and added to the fp32 accumulator by TMA
+//                    reduce-add (cp.reduce.async.bulk.tensor ... .add);
 //                    dK and dV leave through shared memory and TMA stores.
 //   3. bwd_finish  : dQ = (scale * accumulator) rounded to the 16-bit dtype
 #include <cuda_bf16.h>
@@ -47,7 +48,10 @@ template <int D>
 struct BwdSmem {
   static constexpr int kStages = (D == 64) ? 3 : 1;   // Q / dO stages
   static constexpr int kPdsBufs = 1;                  // P / dS buffers
-  static constexpr bool kTmaDq = (D == 64);           // dQ tiles leave through shared memory + TMA reduce-add
+  // dQ tiles leave through shared memory + TMA reduce-add.  D = 64 has a dedicated 32 KB staging tile;
+  // at D = 128 the 64 KB fp32 tile is staged in the P/dS buffers, which are idle between the completion
+  // of a tile's MMAs and the next tile's P/dS write.
+  static constexpr bool kDqStageOwn = (D == 64);
   static constexpr int kTileBytes = kTileM * D * 2;
   static constexpr int kOffK = 0;
   static constexpr int kOffV = kOffK + kTileBytes;
@@ -56,7 +60,7 @@ struct BwdSmem {
   static constexpr int kOffP = kOffdO + kStages * kTileBytes;
   static constexpr int kOffdS = kOffP + kPdsBufs * kTileM * kTileN * 2;
   static constexpr int kOffDQ = kOffdS + kPdsBufs * kTileM * kTileN * 2;    // fp32 [128 x D] staging of a dQ tile
-  static constexpr int kOffMask = kOffDQ + (kTmaDq ? kTileM * D * 4 : 0);   // 128 floats
+  static constexpr int kOffMask = kOffDQ + (kDqStageOwn ? kTileM * D * 4 : 0);   // 128 floats
   static constexpr int kOffBar = kOffMask + kTileN * 4;
   static constexpr int kNumBars = 7 + 2 * kStages;
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;
@@ -64,10 +68,6 @@ struct BwdSmem {
   static constexpr int kDynBytes = kBytes + 1024;
   static_assert(kDynBytes <= 232448, "shared memory budget of one CTA exceeded");
 };
-
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
 
 }  // namespace
 
@@ -171,7 +171,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
   using L = BwdSmem<D>;
   constexpr int ST = L::kStages;
   constexpr int NB = L::kPdsBufs;
-  constexpr bool TMADQ = L::kTmaDq;
+  constexpr bool OWNSTAGE = L::kDqStageOwn;
   constexpr bool EARLY = (D == 64);  // S/dP of the next tile are issued before dV/dK/dQ of this one
   constexpr int kTmemCols = 512;
   constexpr uint32_t kColS = 0, kColdP = 128, kColdV = 256, kColdK = 256 + D;
@@ -190,7 +190,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
   uint8_t* sdO = smem + L::kOffdO;
   uint8_t* sP = smem + L::kOffP;
   uint8_t* sdS = smem + L::kOffdS;
-  uint8_t* sDQ = smem + L::kOffDQ;
+  uint8_t* sDQ = OWNSTAGE ? smem + L::kOffDQ : smem + L::kOffP;   // fp32 dQ staging, [D/32] sub-tiles of 128 x 32 floats
   float* sMask = reinterpret_cast<float*>(smem + L::kOffMask);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
   uint64_t* kv_full = bars + 0;
@@ -408,50 +408,39 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
       tc_fence_after_sync();
     };
 
-    // dQ tile of query tile `it` -> global fp32 accumulator
-    auto dq_readout = [&](int it) {
-      wait_all(dq_full, it & 1, kSiteDqFull);
-      float* dst = a.dq_accum + (static_cast<size_t>(bh) * a.S_q_pad + it * kTileM + row) * D + cq * DQ;
-#pragma unroll
-      for (int c = 0; c < DQ / 16; ++c) {
-        uint32_t r[16];
-        tmem_ld16(tmem_base + lane_addr + kColdQ + cq * DQ + c * 16, r);
-        tmem_wait_ld();
-        if (*abort_flag == 0) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q)
-            red_add_v4(dst + c * 16 + q * 4, __uint_as_float(r[q * 4]), __uint_as_float(r[q * 4 + 1]),
-                       __uint_as_float(r[q * 4 + 2]), __uint_as_float(r[q * 4 + 3]));
-        }
-      }
-      tc_fence_before_sync();
-      mbar_arrive(dq_free);
-    };
-
-    // Same, through shared memory and one TMA reduce-add per 32-column half: the additions are
+    // dQ tile of query tile `it` -> global fp32 accumulator,
+    // through shared memory and one TMA reduce-add per 32-column group: the additions are
     // performed line by line by the TMA unit instead of 2048 scattered 16-byte atomics per tile,
     // which occupied the compute warps for ~1500 cycles per tile.
     auto dq_readout_tma = [&](int it) {
       wait_all(dq_full, it & 1, kSiteDqFull);
-      uint32_t r[16];
-      tmem_ld16(tmem_base + lane_addr + kColdQ + cq * DQ, r);
-      tmem_wait_ld();
+      uint32_t r[DQ];
+#pragma unroll
+      for (int c = 0; c < DQ / 16; ++c) {
+        uint32_t t16[16];
+        tmem_ld16(tmem_base + lane_addr + kColdQ + cq * DQ + c * 16, t16);
+        tmem_wait_ld();
+#pragma unroll
+        for (int k = 0; k < 16; ++k) r[c * 16 + k] = t16[k];
+      }
       tc_fence_before_sync();
       mbar_arrive(dq_free);                          // the dQ columns may be overwritten
-      if (tid == 0) tma_store_wait_read();           // the previous tile's reduce has read the staging buffer
+      if (tid == 0) tma_store_wait_read();           // an earlier reduce has read the staging buffer
       named_bar_sync(2, kComputeThreads);
       {
-        const uint32_t tile = smem_u32(sDQ + (cq >> 1) * 16384);   // 32 fp32 columns = one 128-byte row
+        // this thread's DQ floats of row `row`: sub-tile (cq*DQ)/32, 16-byte chunks from ((cq*DQ)%32)/4
+        const uint32_t tile = smem_u32(sDQ + ((cq * DQ) / 32) * 16384);
+        const int chunk0 = ((cq * DQ) % 32) / 4;
 #pragma unroll
-        for (int q = 0; q < 4; ++q)
-          sts128(tile + sw128_offset(row, (cq & 1) * 4 + q), r[q * 4], r[q * 4 + 1], r[q * 4 + 2], r[q * 4 + 3]);
+        for (int q = 0; q < DQ / 4; ++q)
+          sts128(tile + sw128_offset(row, chunk0 + q), r[q * 4], r[q * 4 + 1], r[q * 4 + 2], r[q * 4 + 3]);
       }
       fence_proxy_async_smem();
       named_bar_sync(3, kComputeThreads);
       if (tid == 0 && *abort_flag == 0) {
         const int row0 = bh * a.S_q_pad + it * kTileM;
-        tma_reduce_add_2d(&a.tm_dq, sDQ, 0, row0);
-        tma_reduce_add_2d(&a.tm_dq, sDQ + 16384, 32, row0);
+#pragma unroll
+        for (int t = 0; t < D / 32; ++t) tma_reduce_add_2d(&a.tm_dq, sDQ + t * 16384, t * 32, row0);
         tma_store_commit();
       }
     };
@@ -539,10 +528,16 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
       else chunk(std::true_type{});
 
       if (tid == 0) TL(i * 16 + 11);
-      if constexpr (TMADQ) {
+      if constexpr (EARLY) {
         // dQ of the previous tile: waiting for it also guarantees that the MMAs which read the single
         // P/dS buffer have completed, so it can be overwritten below.
         if (i > 0) dq_readout_tma(i - 1);
+      } else {
+        // D = 128: the previous tile's dQ was staged in the P/dS buffers; the reduce must have read them.
+        if (i > 0) {
+          if (tid == 0) tma_store_wait_read();
+          named_bar_sync(2, kComputeThreads);
+        }
       }
       {
         // columns [32*cq, +32) of row `row`: 64 bytes = 16-byte chunks (cq%2)*4 .. +3 of sub-tile cq/2
@@ -558,16 +553,20 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
       fence_proxy_async_smem();
       mbar_arrive(pds_full);
       if (tid == 0) TL(i * 16 + 12);
-      if constexpr (!TMADQ) dq_readout(i);   // D = 128: dQ shares columns with dP, it must be out before dP of tile i+1
+      if constexpr (!EARLY) dq_readout_tma(i);   // D = 128: dQ shares columns with dP, it must be out before dP of tile i+1
       if (tid == 0) TL(i * 16 + 13);
     }
-    if constexpr (TMADQ) {
+    if constexpr (EARLY) {
       if (n_q > 0) dq_readout_tma(n_q - 1);
     }
     if (tid == 0) TL(202);
 
     // ---- epilogue: dK, dV -> 16-bit -> shared memory -> TMA store ----------------------
     if (n_q > 0) wait_all(acc_full, 0, kSiteAccFull);
+    if constexpr (!OWNSTAGE) {
+      if (tid == 0) tma_store_wait_read();   // the last dQ reduce has read the P/dS buffers
+      named_bar_sync(2, kComputeThreads);
+    }
     // The P/dS buffers are free (every MMA that read them has completed); dV goes to sP, dK to sdS.
     const float dscale = DROP ? a.dropout_scale : 1.0f;
 #pragma unroll
