@@ -257,7 +257,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
   // status words; TL(slot) is issued by the MMA thread and by the first compute thread.
   long long* tl_buf = reinterpret_cast<long long*>(a.status + 16);
   const bool tl_cta = (blockIdx.x == 0 && blockIdx.y == 1 && blockIdx.z == gridDim.z / 2);
-#define TL(slot) do { if (tl_cta) tl_buf[slot] = clock64(); } while (0)
+#define TL(slot) do { if (tl_cta && lane == 0) tl_buf[slot] = clock64(); } while (0)
 #else
 #define TL(slot) do { } while (0)
 #endif
@@ -285,25 +285,43 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
     }
   } else if (warp == 1) {
     // ============================ MMA issuer ========================================
-    if (lane == 0 && n_q > 0) {
+    // The whole warp runs this loop convergently; the MMAs go out in bursts of 4 or 8 from one
+    // elected lane with descriptors prepared beforehand as warp-uniform values (see umma_ss_x4).
+    // A loop in which a single lane computes each descriptor and then issues was starved by the
+    // compute warps' arithmetic: ~150 cycles per MMA during their exp/Philox phase, which put the
+    // tensor core's work on the critical path of every tile.
+    if (n_q > 0) {
+      constexpr int KS = D / 16;      // k-steps of S and dP
       const uint32_t tS = tmem_base + kColS, tdP = tmem_base + kColdP, tdV = tmem_base + kColdV,
                      tdK = tmem_base + kColdK, tdQ = tmem_base + kColdQ;
-      const DescWords dK_k = desc_words(make_smem_desc_sw128(smem_u32(sK), 16, 1024));       // K as K-major B (S)
-      const DescWords dV_k = desc_words(make_smem_desc_sw128(smem_u32(sV), 16, 1024));       // V as K-major B (dP)
-      const DescWords dK_m = desc_words(make_smem_desc_sw128(smem_u32(sK), 16384, 1024));    // K as MN-major B (dQ)
-      auto issue_s = [&](int i) {
-        const DescWords dq = desc_words(make_smem_desc_sw128(smem_u32(sQ + (i % ST) * L::kTileBytes), 16, 1024));
+      const uint64_t dK_k = make_smem_desc_sw128(smem_u32(sK), 16, 1024);       // K as K-major B (S)
+      const uint64_t dV_k = make_smem_desc_sw128(smem_u32(sV), 16, 1024);       // V as K-major B (dP)
+      const uint64_t dK_m = make_smem_desc_sw128(smem_u32(sK), 16384, 1024);    // K as MN-major B (dQ)
+      uint64_t bK_k[KS], bV_k[KS], bK_m[8];
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
-          umma_ss_w(tS, dq.lo + kmajor_step(kk, 16384), dq.hi, dK_k.lo + kmajor_step(kk, 16384), dK_k.hi, kIdescS,
-                    kk > 0 ? 1u : 0u);
+      for (int kk = 0; kk < KS; ++kk) {
+        bK_k[kk] = dK_k + kmajor_step(kk, 16384);
+        bV_k[kk] = dV_k + kmajor_step(kk, 16384);
+      }
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) bK_m[kk] = dK_m + mnmajor_step(kk);
+
+      auto issue_s = [&](int i) {
+        const uint64_t dq = make_smem_desc_sw128(smem_u32(sQ + (i % ST) * L::kTileBytes), 16, 1024);
+        uint64_t aq[KS];
+#pragma unroll
+        for (int kk = 0; kk < KS; ++kk) aq[kk] = dq + kmajor_step(kk, 16384);
+        if constexpr (KS == 4) umma_ss_x4(tS, aq, bK_k, kIdescS, 0u);
+        else umma_ss_x8(tS, aq, bK_k, kIdescS, 0u);
       };
       auto issue_dp = [&](int i) {
-        const DescWords dd = desc_words(make_smem_desc_sw128(smem_u32(sdO + (i % ST) * L::kTileBytes), 16, 1024));
+        const uint64_t dd = make_smem_desc_sw128(smem_u32(sdO + (i % ST) * L::kTileBytes), 16, 1024);
+        uint64_t ad[KS];
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
-          umma_ss_w(tdP, dd.lo + kmajor_step(kk, 16384), dd.hi, dV_k.lo + kmajor_step(kk, 16384), dV_k.hi, kIdescS,
-                    kk > 0 ? 1u : 0u);
+        for (int kk = 0; kk < KS; ++kk) ad[kk] = dd + kmajor_step(kk, 16384);
+        if constexpr (KS == 4) umma_ss_x4(tdP, ad, bV_k, kIdescS, 0u);
+        else umma_ss_x8(tdP, ad, bV_k, kIdescS, 0u);
+        umma_commit_elect(sdp_full);
       };
       TL(200);
       mbar_wait(kv_full, 0, wctx, kSiteKvFull);
@@ -312,16 +330,24 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
       tc_fence_after_sync();
       issue_s(0);
       issue_dp(0);
-      umma_commit(sdp_full);
       for (int i = 0; i < n_q; ++i) {
         TL(i * 16 + 0);
         const int s = i % ST;
         // MN-major views of this tile's operands (16 rows = 2048 B per k-step, 64-wide halves 16 KB apart)
-        const DescWords dQ_m = desc_words(make_smem_desc_sw128(smem_u32(sQ + s * L::kTileBytes), 16384, 1024));
-        const DescWords ddO_m = desc_words(make_smem_desc_sw128(smem_u32(sdO + s * L::kTileBytes), 16384, 1024));
-        const DescWords dP_m = desc_words(make_smem_desc_sw128(smem_u32(sP + (i % NB) * kPdsBytes), 16384, 1024));
-        const DescWords ddS_m = desc_words(make_smem_desc_sw128(smem_u32(sdS + (i % NB) * kPdsBytes), 16384, 1024));
-        const DescWords ddS_k = desc_words(make_smem_desc_sw128(smem_u32(sdS + (i % NB) * kPdsBytes), 16, 1024));
+        const uint64_t dQ_m = make_smem_desc_sw128(smem_u32(sQ + s * L::kTileBytes), 16384, 1024);
+        const uint64_t ddO_m = make_smem_desc_sw128(smem_u32(sdO + s * L::kTileBytes), 16384, 1024);
+        const uint64_t dP_m = make_smem_desc_sw128(smem_u32(sP + (i % NB) * kPdsBytes), 16384, 1024);
+        const uint64_t ddS_m = make_smem_desc_sw128(smem_u32(sdS + (i % NB) * kPdsBytes), 16384, 1024);
+        const uint64_t ddS_k = make_smem_desc_sw128(smem_u32(sdS + (i % NB) * kPdsBytes), 16, 1024);
+        uint64_t aP[8], bdO[8], adS[8], bQ[8], adSk[8];
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          aP[kk] = dP_m + mnmajor_step(kk);
+          bdO[kk] = ddO_m + mnmajor_step(kk);
+          adS[kk] = ddS_m + mnmajor_step(kk);
+          bQ[kk] = dQ_m + mnmajor_step(kk);
+          adSk[kk] = ddS_k + kmajor_step(kk, 16384);
+        }
         if constexpr (EARLY) {
           if (i + 1 < n_q) {
             mbar_wait(sdp_free, i & 1, wctx, kSiteSdpFree);
@@ -330,7 +356,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
             TL(i * 16 + 1);
             issue_s(i + 1);
             issue_dp(i + 1);
-            umma_commit(sdp_full);
           }
         }
         TL(i * 16 + 2);
@@ -339,15 +364,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
         tc_fence_after_sync();
         // dV += P^T dO ; dK += dS^T Q : A is the [q x keys] tile read MN-major (keys contiguous),
         // 16 query rows (2048 B) per k-step, the two 64-key halves 16 KB apart.
-#pragma unroll
-        for (int kk = 0; kk < kTileM / 16; ++kk)
-          umma_ss_w(tdV, dP_m.lo + mnmajor_step(kk), dP_m.hi, ddO_m.lo + mnmajor_step(kk), ddO_m.hi, kIdescT,
-                    (i > 0 || kk > 0) ? 1u : 0u);
-#pragma unroll
-        for (int kk = 0; kk < kTileM / 16; ++kk)
-          umma_ss_w(tdK, ddS_m.lo + mnmajor_step(kk), ddS_m.hi, dQ_m.lo + mnmajor_step(kk), dQ_m.hi, kIdescT,
-                    (i > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(qdo_empty + s);  // Q and dO of this stage are not read again (dQ needs dS and K only)
+        const uint32_t acc0 = (i > 0) ? 1u : 0u;
+        umma_ss_x8(tdV, aP, bdO, kIdescT, acc0);
+        umma_ss_x8(tdK, adS, bQ, kIdescT, acc0);
+        umma_commit_elect(qdo_empty + s);  // Q and dO of this stage are not read again (dQ needs dS and K only)
         TL(i * 16 + 4);
         if (i > 0) {
           mbar_wait(dq_free, (i - 1) & 1, wctx, kSiteDqFree);
@@ -355,11 +375,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
         }
         TL(i * 16 + 5);
         // dQ tile = dS K : A K-major (keys along the row), B = K tile read MN-major
-#pragma unroll
-        for (int kk = 0; kk < kTileN / 16; ++kk)
-          umma_ss_w(tdQ, ddS_k.lo + kmajor_step(kk, 16384), ddS_k.hi, dK_m.lo + mnmajor_step(kk), dK_m.hi, kIdescQ,
-                    kk > 0 ? 1u : 0u);
-        umma_commit(dq_full);
+        umma_ss_x8(tdQ, adSk, bK_m, kIdescQ, 0u);
+        umma_commit_elect(dq_full);
         TL(i * 16 + 6);
         if constexpr (!EARLY) {
           if (i + 1 < n_q) {
@@ -369,11 +386,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
             mbar_wait(dq_free, i & 1, wctx, kSiteDqFree);       // dQ shares the dP columns
             tc_fence_after_sync();
             issue_dp(i + 1);
-            umma_commit(sdp_full);
           }
         }
       }
-      umma_commit(acc_full);
+      umma_commit_elect(acc_full);
     }
   } else {
     // ============================ compute warps =====================================
@@ -445,22 +461,53 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
       }
     };
 
-    float lse2_next = INFINITY, delta_next = 0.f;
+    // D = 64: every warp stages its own 32 rows x 16 columns (2 KB, 64-byte swizzle) and its lane 0
+    // issues the reduce, so the warps never wait for one another here.
+    auto dq_readout_warp = [&](int it) {
+      wait_all(dq_full, it & 1, kSiteDqFull);
+      uint32_t t16[16];
+      tmem_ld16(tmem_base + lane_addr + kColdQ + cq * 16, t16);
+      tmem_wait_ld();
+      tc_fence_before_sync();
+      mbar_arrive(dq_free);                          // the dQ columns may be overwritten
+      if (lane == 0) tma_store_wait_read();          // this warp's previous reduce has read its staging tile
+      __syncwarp();
+      uint8_t* stage = sDQ + cw * 2048;
+      const uint32_t rowaddr = smem_u32(stage) + lane * 64;
+      const uint32_t sw = (lane >> 1) & 3;           // 64-byte swizzle: 16-byte chunk ^= bits 7..8 of the offset
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        sts128(rowaddr + ((q ^ sw) << 4), t16[q * 4], t16[q * 4 + 1], t16[q * 4 + 2], t16[q * 4 + 3]);
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0 && *abort_flag == 0) {
+        tma_reduce_add_2d(&a.tm_dq, stage, cq * 16, bh * a.S_q_pad + it * kTileM + quad * 32);
+        tma_store_commit();
+      }
+    };
+
+    // Row statistics of the next tile are fetched one iteration ahead and kept RAW: any arithmetic
+    // on the loaded value here would make the warp wait for the load at once (~1000 cycles per tile).
+    float lse_next = INFINITY, delta_next = 0.f;
     if (n_q > 0 && row < a.S_q) {
-      lse2_next = a.lse[static_cast<size_t>(bh) * a.S_q + row] * kLog2eB;
-      delta_next = a.delta[static_cast<size_t>(bh) * a.S_q + row] * inv_c;
+      lse_next = a.lse[static_cast<size_t>(bh) * a.S_q + row];
+      delta_next = a.delta[static_cast<size_t>(bh) * a.S_q + row];
     }
 
     for (int i = 0; i < n_q; ++i) {
       const int q_row = i * kTileM + row;
       // lse in the log2 domain; +inf for rows past the end makes their probabilities zero
-      const float neg_lse2 = -lse2_next;
-      const float delta = delta_next;
+      const float neg_lse2 = -lse_next * kLog2eB;
+      const float delta = delta_next * inv_c;
       {
         const int nr = q_row + kTileM;  // prefetch the statistics of the next tile's row
         const bool ok = (i + 1 < n_q) && nr < a.S_q;
-        lse2_next = ok ? a.lse[static_cast<size_t>(bh) * a.S_q + nr] * kLog2eB : INFINITY;
-        delta_next = ok ? a.delta[static_cast<size_t>(bh) * a.S_q + nr] * inv_c : 0.f;
+        lse_next = INFINITY;
+        delta_next = 0.f;
+        if (ok) {
+          lse_next = a.lse[static_cast<size_t>(bh) * a.S_q + nr];
+          delta_next = a.delta[static_cast<size_t>(bh) * a.S_q + nr];
+        }
       }
 
       if (tid == 0) TL(i * 16 + 8);
@@ -529,9 +576,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
 
       if (tid == 0) TL(i * 16 + 11);
       if constexpr (EARLY) {
-        // dQ of the previous tile: waiting for it also guarantees that the MMAs which read the single
-        // P/dS buffer have completed, so it can be overwritten below.
-        if (i > 0) dq_readout_tma(i - 1);
+        // dQ of the previous tile is complete <=> the MMAs which read the single P/dS buffer have
+        // completed, so it can be overwritten below (the dQ tile itself is read out afterwards).
+        if (i > 0) wait_all(dq_full, (i - 1) & 1, kSiteDqFull);
       } else {
         // D = 128: the previous tile's dQ was staged in the P/dS buffers; the reduce must have read them.
         if (i > 0) {
@@ -553,11 +600,16 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
       fence_proxy_async_smem();
       mbar_arrive(pds_full);
       if (tid == 0) TL(i * 16 + 12);
-      if constexpr (!EARLY) dq_readout_tma(i);   // D = 128: dQ shares columns with dP, it must be out before dP of tile i+1
+      if constexpr (EARLY) {
+        if (i > 0) dq_readout_warp(i - 1);
+      } else {
+        dq_readout_tma(i);   // D = 128: dQ shares columns with dP, it must be out before dP of tile i+1
+      }
       if (tid == 0) TL(i * 16 + 13);
     }
     if constexpr (EARLY) {
-      if (n_q > 0) dq_readout_tma(n_q - 1);
+      if (n_q > 0) dq_readout_warp(n_q - 1);
+      if (lane == 0) tma_store_wait_read();   // shared memory must stay valid until the reduce has read it
     }
     if (tid == 0) TL(202);
 

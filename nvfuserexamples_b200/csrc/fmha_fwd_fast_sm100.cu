@@ -199,33 +199,50 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
     }
   } else if (warp == 1) {
     // ============================ MMA issuer ========================================
-    if (lane == 0) {
+    // The warp runs the loop convergently and issues the MMAs in bursts from one elected lane
+    // with descriptors prepared beforehand (see umma_ss_x4): a single lane that computes each
+    // descriptor and then issues is starved of issue slots by the softmax warps.
+    {
+      constexpr int KQ = D / 16;     // k-steps of S = Q K^T
+      constexpr int KP = TN / 16;    // k-steps of O += P V
       const uint32_t tS = tmem_base + kColS;
       const uint32_t tO = tmem_base + kColO;
-      const DescWords dq = desc_words(make_smem_desc_sw128(smem_u32(sQ), 16, 1024));
+      const uint64_t dq = make_smem_desc_sw128(smem_u32(sQ), 16, 1024);
+      uint64_t aq[KQ];
+#pragma unroll
+      for (int kk = 0; kk < KQ; ++kk) aq[kk] = dq + kmajor_step(kk, 16384);
       mbar_wait(q_full, 0, wctx, kFQFull);
       for (int j = 0; j < n_kv; ++j) {
         const int s = j % ST;
         const uint32_t ph = (j / ST) & 1;
-        const DescWords dk = desc_words(make_smem_desc_sw128(smem_u32(sK + s * L::kTileBytes), 16, 1024));
-        const DescWords dv = desc_words(make_smem_desc_sw128(smem_u32(sV + s * L::kTileBytes), L::kSubTile, 1024));
+        const uint64_t dk = make_smem_desc_sw128(smem_u32(sK + s * L::kTileBytes), 16, 1024);
+        const uint64_t dv = make_smem_desc_sw128(smem_u32(sV + s * L::kTileBytes), L::kSubTile, 1024);
+        uint64_t bk[KQ], bv[KP];
+#pragma unroll
+        for (int kk = 0; kk < KQ; ++kk) bk[kk] = dk + kmajor_step(kk, L::kSubTile);
+#pragma unroll
+        for (int kk = 0; kk < KP; ++kk) bv[kk] = dv + mnmajor_step(kk);
         mbar_wait(k_full + s, ph, wctx, kFKFull);
         tc_fence_after_sync();
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
-          umma_ss_w(tS, dq.lo + kmajor_step(kk, 16384), dq.hi, dk.lo + kmajor_step(kk, L::kSubTile), dk.hi, kIdescQK,
-                    kk > 0 ? 1u : 0u);
-        umma_commit(k_empty + s);
-        umma_commit(s_full);
+        if constexpr (KQ == 4) umma_ss_x4(tS, aq, bk, kIdescQK, 0u);
+        else umma_ss_x8(tS, aq, bk, kIdescQK, 0u);
+        umma_commit_elect(k_empty + s);
+        umma_commit_elect(s_full);
         mbar_wait(p_full, j & 1, wctx, kFPFull);
         mbar_wait(v_full + s, ph, wctx, kFVFull);
         tc_fence_after_sync();
-#pragma unroll
-        for (int kk = 0; kk < TN / 16; ++kk)
-          umma_ts_w(tO, tS + kk * 8, dv.lo + mnmajor_step(kk), dv.hi, kIdescPV, (j > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(v_empty + s);
+        const uint32_t acc0 = (j > 0) ? 1u : 0u;
+        {
+          const uint64_t (&b0)[4] = *reinterpret_cast<const uint64_t (*)[4]>(&bv[0]);
+          umma_ts_x4(tO, tS, 8u, b0, kIdescPV, acc0);
+        }
+        if constexpr (KP == 8) {
+          const uint64_t (&b1)[4] = *reinterpret_cast<const uint64_t (*)[4]>(&bv[4]);
+          umma_ts_x4(tO, tS + 32u, 8u, b1, kIdescPV, 1u);
+        }
+        umma_commit_elect(v_empty + s);
       }
-      umma_commit(o_full);
+      umma_commit_elect(o_full);
     }
   } else {
     // ============================ softmax / epilogue ================================

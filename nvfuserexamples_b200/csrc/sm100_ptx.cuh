@@ -290,6 +290,88 @@ __device__ __forceinline__ void umma_ts_w(uint32_t d_tmem, uint32_t a_tmem, uint
       ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// ---- burst issue from a converged warp ---------------------------------------------------
+// The warp scheduler gives a warp whose next instruction is not ready no slot, and a warp that
+// competes with arithmetic-heavy warps waits tens of cycles for each slot it asks for.  An MMA loop
+// written as "one lane computes a descriptor, then issues" therefore degrades from ~50 to ~150
+// cycles per MMA next to busy softmax warps (measured: 147 cycles against a backward-like
+// instruction mix, 1600 against pure Philox).  These helpers are executed by ALL 32 lanes of a
+// converged warp: the descriptors are warp-uniform values prepared beforehand, one lane is elected
+// inside the block and the MMAs follow each other without branches or dependent arithmetic
+// (measured under the same load: 62 cycles per MMA).
+//   acc_first: accumulate flag of the first MMA; the others always accumulate.
+__device__ __forceinline__ void umma_ss_x4(uint32_t d_tmem, const uint64_t (&a)[4], const uint64_t (&b)[4], uint32_t idesc,
+                                           uint32_t acc_first) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q, pe;\n\t"
+      "setp.ne.b32 p, %10, 0;\n\t"
+      "setp.eq.b32 q, 0, 0;\n\t"
+      "elect.sync _|pe, 0xffffffff;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %9, p;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %3, %4, %9, q;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %5, %6, %9, q;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %7, %8, %9, q;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "l"(a[0]), "l"(b[0]), "l"(a[1]), "l"(b[1]), "l"(a[2]), "l"(b[2]), "l"(a[3]), "l"(b[3]), "r"(idesc),
+        "r"(acc_first)
+      : "memory");
+}
+__device__ __forceinline__ void umma_ss_x8(uint32_t d_tmem, const uint64_t (&a)[8], const uint64_t (&b)[8], uint32_t idesc,
+                                           uint32_t acc_first) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q, pe;\n\t"
+      "setp.ne.b32 p, %18, 0;\n\t"
+      "setp.eq.b32 q, 0, 0;\n\t"
+      "elect.sync _|pe, 0xffffffff;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %17, p;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %3, %4, %17, q;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %5, %6, %17, q;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %7, %8, %17, q;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %9, %10, %17, q;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %11, %12, %17, q;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %13, %14, %17, q;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %15, %16, %17, q;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "l"(a[0]), "l"(b[0]), "l"(a[1]), "l"(b[1]), "l"(a[2]), "l"(b[2]), "l"(a[3]), "l"(b[3]), "l"(a[4]), "l"(b[4]),
+        "l"(a[5]), "l"(b[5]), "l"(a[6]), "l"(b[6]), "l"(a[7]), "l"(b[7]), "r"(idesc), "r"(acc_first)
+      : "memory");
+}
+// A from tensor memory: a_tmem + k * a_step is the A address of MMA k.
+__device__ __forceinline__ void umma_ts_x4(uint32_t d_tmem, uint32_t a_tmem, uint32_t a_step, const uint64_t (&b)[4],
+                                           uint32_t idesc, uint32_t acc_first) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q, pe;\n\t"
+      ".reg .b32 a1, a2, a3;\n\t"
+      "setp.ne.b32 p, %8, 0;\n\t"
+      "setp.eq.b32 q, 0, 0;\n\t"
+      "add.u32 a1, %1, %2;\n\t"
+      "add.u32 a2, a1, %2;\n\t"
+      "add.u32 a3, a2, %2;\n\t"
+      "elect.sync _|pe, 0xffffffff;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %3, %7, p;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], %4, %7, q;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], %5, %7, q;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [a3], %6, %7, q;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(a_step), "l"(b[0]), "l"(b[1]), "l"(b[2]), "l"(b[3]), "r"(idesc), "r"(acc_first)
+      : "memory");
+}
+// tcgen05.commit by the elected lane of a converged warp.  elect.sync picks the same lane every
+// time for a full mask, so the commit tracks the MMAs issued by the helpers above.
+__device__ __forceinline__ void umma_commit_elect(uint64_t* bar) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred pe;\n\t"
+      "elect.sync _|pe, 0xffffffff;\n\t"
+      "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+      "}\n"
+      ::"r"(smem_u32(bar))
+      : "memory");
+}
+
 // Low-word increments: k-step kk of a K-major operand (16 elements = 32 bytes, 64-column
 // sub-tiles `sub` bytes apart) and of an MN-major operand (16 rows = 2048 bytes).
 __host__ __device__ constexpr uint32_t kmajor_step(int kk, int sub) { return static_cast<uint32_t>(((kk / 4) * sub + (kk % 4) * 32) >> 4); }
