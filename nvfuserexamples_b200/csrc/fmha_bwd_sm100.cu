@@ -7,7 +7,8 @@
 //
 // Three kernels per call:
 //   1. bwd_prepare : delta[row] = sum_d dO[row,d] * O[row,d]  and zero the fp32 dQ accumulator
-//   2. bwd_main    : one CTA per (128-key tile, head, batch) loops over the 128-row query tiles
+//   2. bwd_main    : persistent CTAs (one per SM) draw (128-key tile, head, batch) work items from a
+//                    counter and loop over the 128-row query tiles of each
 //                      S  = Q K^T            dP = dO V^T              (tcgen05.mma, fp32 in TMEM)
 //                      P  = exp2(S*scale*log2e + mask - lse*log2e)   (16 warps, thread = row, a quarter of the columns)
 //                      dS = P * (keep*c*dP - delta)                   c = 1/(1-p_drop)
@@ -16,7 +17,7 @@
 //                    by the tensor core both as K-major (dQ) and as MN-major (dV, dK) operands;
 //                    dQ tiles are staged in shared memory and added to the fp32 accumulator by TMA
 //                    reduce-add (cp.reduce.async.bulk.tensor ... .add);
-//                    dK and dV leave through shared memory and TMA stores.
+//                    dK and dV are written from registers when the next item is already under way.
 //   3. bwd_finish  : dQ = (scale * accumulator) rounded to the 16-bit dtype
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -41,28 +42,32 @@ constexpr float kLog2eB = 1.4426950408889634f;
 
 enum BwdWaitSite {
   kSiteKvFull = 201, kSiteQdoFull = 202, kSiteQdoEmpty = 203, kSiteSdpFull = 204, kSitePdsFull = 205,
-  kSiteDqFull = 206, kSiteDqFree = 207, kSiteAccFull = 208, kSiteSdpFree = 209
+  kSiteDqFull = 206, kSiteDqFree = 207, kSiteAccFull = 208, kSiteSdpFree = 209, kSiteKvEmpty = 210,
+  kSiteItemFull = 211, kSiteItemEmpty = 212
 };
 
 template <int D>
 struct BwdSmem {
-  static constexpr int kStages = (D == 64) ? 3 : 1;   // Q / dO stages
+  // D = 64: two K/V buffers (the next work item's K and V arrive while this one finishes) and two
+  // Q/dO stages.  D = 128 fills shared memory with one of each.
+  static constexpr int kKvBufs = (D == 64) ? 2 : 1;
+  static constexpr int kStages = (D == 64) ? 2 : 1;   // Q / dO stages
   static constexpr int kPdsBufs = 1;                  // P / dS buffers
-  // dQ tiles leave through shared memory + TMA reduce-add.  D = 64 has a dedicated 32 KB staging tile;
-  // at D = 128 the 64 KB fp32 tile is staged in the P/dS buffers, which are idle between the completion
-  // of a tile's MMAs and the next tile's P/dS write.
+  // dQ tiles leave through shared memory + TMA reduce-add.  D = 64 has a dedicated 32 KB staging area
+  // (2 KB per compute warp); at D = 128 the 64 KB fp32 tile is staged in the P/dS buffers, which are
+  // idle between the completion of a tile's MMAs and the next tile's P/dS write.
   static constexpr bool kDqStageOwn = (D == 64);
   static constexpr int kTileBytes = kTileM * D * 2;
   static constexpr int kOffK = 0;
-  static constexpr int kOffV = kOffK + kTileBytes;
-  static constexpr int kOffQ = kOffV + kTileBytes;
+  static constexpr int kOffV = kOffK + kKvBufs * kTileBytes;
+  static constexpr int kOffQ = kOffV + kKvBufs * kTileBytes;
   static constexpr int kOffdO = kOffQ + kStages * kTileBytes;
   static constexpr int kOffP = kOffdO + kStages * kTileBytes;
   static constexpr int kOffdS = kOffP + kPdsBufs * kTileM * kTileN * 2;
-  static constexpr int kOffDQ = kOffdS + kPdsBufs * kTileM * kTileN * 2;    // fp32 [128 x D] staging of a dQ tile
-  static constexpr int kOffMask = kOffDQ + (kDqStageOwn ? kTileM * D * 4 : 0);   // 128 floats
-  static constexpr int kOffBar = kOffMask + kTileN * 4;
-  static constexpr int kNumBars = 7 + 2 * kStages;
+  static constexpr int kOffDQ = kOffdS + kPdsBufs * kTileM * kTileN * 2;    // fp32 staging of dQ
+  static constexpr int kOffMask = kOffDQ + (kDqStageOwn ? kTileM * D * 4 : 0);   // 2 x 128 floats
+  static constexpr int kOffBar = kOffMask + 2 * kTileN * 4;
+  static constexpr int kNumBars = 6 + 2 * kKvBufs + 2 * kStages + 4;
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;
   static constexpr int kBytes = kOffMisc + 16;
   static constexpr int kDynBytes = kBytes + 1024;
@@ -81,6 +86,7 @@ struct PrepArgs {
   int B, H, S_q, S_q_pad, D;
   float* delta;     // [B*H, S_q]
   float* dq_accum;  // [B*H, S_q_pad, D]
+  int* work_counter;  // the main kernel's work-item counter, cleared here
 };
 
 template <bool BF16>
@@ -91,6 +97,7 @@ __global__ void __launch_bounds__(256) bwd_prepare_kernel(const PrepArgs a) {
   const int part = threadIdx.x & 7;
   const int64_t n_rows = static_cast<int64_t>(a.B) * a.H * a.S_q_pad;
   const bool in_range = row_global < n_rows;  // no early exit: the shuffles below need every lane
+  if (blockIdx.x == 0 && threadIdx.x == 0 && a.work_counter != nullptr) *a.work_counter = 0;
   const int r = in_range ? static_cast<int>(row_global % a.S_q_pad) : a.S_q_pad;
   const int64_t bh = row_global / a.S_q_pad;
   const int h = static_cast<int>(bh % a.H);
@@ -159,18 +166,30 @@ __global__ void __launch_bounds__(256) bwd_finish_kernel(const FinishArgs a) {
 // ---------------------------------------------------------------------------------------
 // 2. main kernel
 // ---------------------------------------------------------------------------------------
-// Schedule.  The eight compute warps copy S and dP of query tile i into registers as soon as the
-// tensor core has produced them and release the tensor-memory columns at once (sdp_free), so the
-// MMA warp can already issue S and dP of tile i+1 while tile i is still being turned into P and
-// dS.  At D = 64 P and dS are double-buffered in shared memory, so dV/dK/dQ of tile i run on the
-// tensor core while the compute warps work on tile i+1, and the dQ tile of i is read out one
-// iteration later.  At D = 128 (shared memory and tensor memory are full) P/dS are single
-// buffered and dQ shares the dP columns, so only the S/dP copy-out overlaps.
+// Work.  An item is one (128-key tile, head, batch); kv tile is the fastest index.  One CTA per SM
+// draws items from a global counter (the first item is blockIdx.x), so the fixed cost of an item --
+// loading K and V, the first S/dP, the last tile's dV/dK/dQ, the dQ reduce and the dK/dV write-out --
+// overlaps the neighbouring items instead of leaving the SM idle (it was ~30 % of a CTA's life when
+// every item was its own CTA).  Items whose key tile lies wholly past the valid length write zeros.
+//
+// Schedule inside the stream of (item, query tile) pairs, numbered t = 0, 1, ...:
+//   compute warps:  S,dP(t) -> registers, release the columns (sdp_free) -> P, dS in registers ->
+//                   [first tile of an item: dK, dV of the previous item -> global memory] ->
+//                   P,dS(t) -> shared memory (pds_full) -> dQ(t-1) -> staging -> TMA reduce-add
+//   MMA warp:       S,dP(t+1) as soon as sdp_free(t), also across an item boundary (D = 64: the next
+//                   item's K and V are already in the second buffer) -> dV,dK(t) -> dQ(t)
+// At D = 128 shared and tensor memory are full: one K/V buffer, dQ shares the dP columns and is read
+// out at the end of its own iteration, S/dP(t+1) follow dQ(t).
+struct BwdItem {
+  int id;      // < 0: no more work
+  int b, h, bh, k0, n_cols;   // n_cols <= 0: key tile wholly masked out
+};
+
 template <int D, bool BF16, bool KEYADD, bool DROP>
 __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_constant__ BwdArgs a) {
   using L = BwdSmem<D>;
   constexpr int ST = L::kStages;
-  constexpr int NB = L::kPdsBufs;
+  constexpr int KV = L::kKvBufs;
   constexpr bool OWNSTAGE = L::kDqStageOwn;
   constexpr bool EARLY = (D == 64);  // S/dP of the next tile are issued before dV/dK/dQ of this one
   constexpr int kTmemCols = 512;
@@ -180,7 +199,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
   constexpr uint32_t kIdescS = make_idesc_f16(128, 128, kFmt, false, false);
   constexpr uint32_t kIdescT = make_idesc_f16(128, D, kFmt, true, true);    // dV, dK: A and B MN-major
   constexpr uint32_t kIdescQ = make_idesc_f16(128, D, kFmt, false, true);   // dQ: A K-major, B MN-major
-  constexpr int kPdsBytes = kTileM * kTileN * 2;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -190,57 +208,56 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
   uint8_t* sdO = smem + L::kOffdO;
   uint8_t* sP = smem + L::kOffP;
   uint8_t* sdS = smem + L::kOffdS;
-  uint8_t* sDQ = OWNSTAGE ? smem + L::kOffDQ : smem + L::kOffP;   // fp32 dQ staging, [D/32] sub-tiles of 128 x 32 floats
-  float* sMask = reinterpret_cast<float*>(smem + L::kOffMask);
+  uint8_t* sDQ = OWNSTAGE ? smem + L::kOffDQ : smem + L::kOffP;   // fp32 dQ staging
+  float* sMask = reinterpret_cast<float*>(smem + L::kOffMask);     // [2][128], by work-item parity
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
-  uint64_t* kv_full = bars + 0;
-  uint64_t* sdp_full = bars + 1;   // S and dP of a tile are in tensor memory
-  uint64_t* sdp_free = bars + 2;   // ... and have been copied to registers (all compute threads arrive)
-  uint64_t* pds_full = bars + 3;   // P and dS are in shared memory (all compute threads arrive)
-  uint64_t* dq_full = bars + 4;    // dQ tile is in tensor memory; dV/dK/dQ of that tile are complete
-  uint64_t* dq_free = bars + 5;    // dQ tile has been read out (all compute threads arrive)
-  uint64_t* acc_full = bars + 6;   // dK / dV accumulation finished
-  uint64_t* qdo_full = bars + 7;
+  uint64_t* sdp_full = bars + 0;   // S and dP of a tile are in tensor memory
+  uint64_t* sdp_free = bars + 1;   // ... and have been copied to registers (all compute threads arrive)
+  uint64_t* pds_full = bars + 2;   // P and dS are in shared memory (all compute threads arrive)
+  uint64_t* dq_full = bars + 3;    // dQ tile is in tensor memory; dV/dK/dQ of that tile are complete
+  uint64_t* dq_free = bars + 4;    // dQ tile has been read out (all compute threads arrive)
+  uint64_t* acc_full = bars + 5;   // dK / dV of a work item are complete
+  uint64_t* kv_full = bars + 6;
+  uint64_t* kv_empty = kv_full + KV;
+  uint64_t* qdo_full = kv_empty + KV;
   uint64_t* qdo_empty = qdo_full + ST;
+  uint64_t* item_full = qdo_empty + ST;   // [2] ring of work-item ids
+  uint64_t* item_empty = item_full + 2;
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(smem + L::kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kOffMisc + 4);
+  volatile int* ring = reinterpret_cast<volatile int*>(smem + L::kOffMisc + 8);   // [2]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int kv_tile = blockIdx.x;
-  const int h = blockIdx.y;
-  const int b = blockIdx.z;
-  const int k0 = kv_tile * kTileN;
-  const int bh = b * a.H + h;
-
-  int k_limit = a.S_k;
-  if (a.mask_kind == FMHA_MASK_SEQLEN) {
-    const int len = reinterpret_cast<const int*>(a.mask)[b];
-    if (len > 0 && len < a.S_k) k_limit = len;
-  }
-  const int n_cols = min(kTileN, k_limit - k0);  // <= 0: this key tile is masked out entirely
-  const int n_q = (n_cols > 0) ? (a.S_q + kTileM - 1) / kTileM : 0;
+  const int kv_tiles = (a.S_k + kTileN - 1) / kTileN;
+  const int n_q = (a.S_q + kTileM - 1) / kTileM;
+  const int num_items = kv_tiles * a.H * a.B;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    mbar_init(kv_full, 1);
     mbar_init(sdp_full, 1);
     mbar_init(sdp_free, kComputeThreads);
     mbar_init(pds_full, kComputeThreads);
     mbar_init(dq_full, 1);
     mbar_init(dq_free, kComputeThreads);
     mbar_init(acc_full, 1);
+    for (int s = 0; s < KV; ++s) {
+      mbar_init(kv_full + s, 1);
+      mbar_init(kv_empty + s, 1);
+    }
     for (int s = 0; s < ST; ++s) {
       mbar_init(qdo_full + s, 1);
       mbar_init(qdo_empty + s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(item_full + s, 1);
+      mbar_init(item_empty + s, 1 + kComputeThreads / 32);   // the MMA warp and every compute warp
     }
     mbar_fence_init();
     tma_prefetch_desc(&a.tm_q);
     tma_prefetch_desc(&a.tm_k);
     tma_prefetch_desc(&a.tm_v);
     tma_prefetch_desc(&a.tm_do);
-    tma_prefetch_desc(&a.tm_dk);
-    tma_prefetch_desc(&a.tm_dv);
     tma_prefetch_desc(&a.tm_dq);
   }
   if (warp == 1) {
@@ -253,34 +270,80 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
   const uint32_t tmem_base = *tmem_base_slot;
   const WaitCtx wctx{abort_flag, a.status};
 #ifdef FMHA_TIMELINE
-  // Development aid (not compiled into the library): one CTA records clock64() stamps after its
-  // status words; TL(slot) is issued by the MMA thread and by the first compute thread.
+  // Development aid (not compiled into the library): CTA 0 records clock64() stamps after its
+  // status words; TL(slot) is issued by the MMA warp and by the first compute thread.
   long long* tl_buf = reinterpret_cast<long long*>(a.status + 16);
-  const bool tl_cta = (blockIdx.x == 0 && blockIdx.y == 1 && blockIdx.z == gridDim.z / 2);
-#define TL(slot) do { if (tl_cta && lane == 0) tl_buf[slot] = clock64(); } while (0)
+  const bool tl_cta = (blockIdx.x == 0);
+#define TL(slot) do { if (tl_cta && lane == 0 && (slot) < 256) tl_buf[slot] = clock64(); } while (0)
 #else
 #define TL(slot) do { } while (0)
 #endif
-  if (threadIdx.x == 0) TL(205);
+  if (threadIdx.x == 0) TL(255);
+
+  auto decode = [&](int id) {
+    BwdItem it;
+    it.id = id;
+    it.b = it.h = it.bh = it.k0 = 0;
+    it.n_cols = 0;
+    if (id >= 0) {
+      const int kv_tile = id % kv_tiles;
+      it.bh = id / kv_tiles;
+      it.h = it.bh % a.H;
+      it.b = it.bh / a.H;
+      it.k0 = kv_tile * kTileN;
+      int k_limit = a.S_k;
+      if (a.mask_kind == FMHA_MASK_SEQLEN) {
+        const int len = reinterpret_cast<const int*>(a.mask)[it.b];
+        if (len > 0 && len < a.S_k) k_limit = len;
+      }
+      it.n_cols = min(kTileN, k_limit - it.k0);
+    }
+    return it;
+  };
+  // Consumer side of the work-item ring (whole warp): item number `n` of this CTA.
+  auto fetch_item = [&](int n, uint32_t sleep_ns) {
+    const int slot = n & 1;
+    mbar_wait(item_full + slot, (n >> 1) & 1, wctx, kSiteItemFull, sleep_ns);
+    int id = ring[slot];
+    if (*abort_flag) id = -1;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(item_empty + slot);
+    return decode(id);
+  };
 
   if (warp == 0) {
     // ============================ TMA producer ======================================
-    if (lane == 0 && n_q > 0) {
-      mbar_arrive_expect_tx(kv_full, 2 * L::kTileBytes);
-#pragma unroll
-      for (int c = 0; c < D / 64; ++c) {
-        tma_load_4d(sK + c * 16384, &a.tm_k, kv_full, c * 64, k0, h, b);
-        tma_load_4d(sV + c * 16384, &a.tm_v, kv_full, c * 64, k0, h, b);
-      }
-      for (int i = 0; i < n_q; ++i) {
-        const int s = i % ST;
-        if (i >= ST) mbar_wait(qdo_empty + s, ((i / ST) - 1) & 1, wctx, kSiteQdoEmpty);
-        mbar_arrive_expect_tx(qdo_full + s, 2 * L::kTileBytes);
+    if (lane == 0) {
+      int w = 0, g = 0;   // work items with keys / query tiles loaded so far
+      for (int n = 0;; ++n) {
+        const int slot = n & 1;
+        if (n >= 2) mbar_wait(item_empty + slot, ((n >> 1) - 1) & 1, wctx, kSiteItemEmpty);
+        int id = (n == 0) ? static_cast<int>(blockIdx.x) : atomicAdd(a.work_counter, 1) + static_cast<int>(gridDim.x);
+        if (id >= num_items || *abort_flag) id = -1;
+        ring[slot] = id;
+        mbar_arrive(item_full + slot);
+        if (id < 0) break;
+        const BwdItem it = decode(id);
+        if (it.n_cols <= 0) continue;
+        const int kvb = w % KV;
+        if (w >= KV) mbar_wait(kv_empty + kvb, ((w / KV) - 1) & 1, wctx, kSiteKvEmpty);
+        mbar_arrive_expect_tx(kv_full + kvb, 2 * L::kTileBytes);
 #pragma unroll
         for (int c = 0; c < D / 64; ++c) {
-          tma_load_4d(sQ + s * L::kTileBytes + c * 16384, &a.tm_q, qdo_full + s, c * 64, i * kTileM, h, b);
-          tma_load_4d(sdO + s * L::kTileBytes + c * 16384, &a.tm_do, qdo_full + s, c * 64, i * kTileM, h, b);
+          tma_load_4d(sK + kvb * L::kTileBytes + c * 16384, &a.tm_k, kv_full + kvb, c * 64, it.k0, it.h, it.b);
+          tma_load_4d(sV + kvb * L::kTileBytes + c * 16384, &a.tm_v, kv_full + kvb, c * 64, it.k0, it.h, it.b);
         }
+        for (int i = 0; i < n_q; ++i, ++g) {
+          const int s = g % ST;
+          if (g >= ST) mbar_wait(qdo_empty + s, ((g / ST) - 1) & 1, wctx, kSiteQdoEmpty);
+          mbar_arrive_expect_tx(qdo_full + s, 2 * L::kTileBytes);
+#pragma unroll
+          for (int c = 0; c < D / 64; ++c) {
+            tma_load_4d(sQ + s * L::kTileBytes + c * 16384, &a.tm_q, qdo_full + s, c * 64, i * kTileM, it.h, it.b);
+            tma_load_4d(sdO + s * L::kTileBytes + c * 16384, &a.tm_do, qdo_full + s, c * 64, i * kTileM, it.h, it.b);
+          }
+        }
+        ++w;
       }
     }
   } else if (warp == 1) {
@@ -290,106 +353,152 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
     // A loop in which a single lane computes each descriptor and then issues was starved by the
     // compute warps' arithmetic: ~150 cycles per MMA during their exp/Philox phase, which put the
     // tensor core's work on the critical path of every tile.
-    if (n_q > 0) {
-      constexpr int KS = D / 16;      // k-steps of S and dP
-      const uint32_t tS = tmem_base + kColS, tdP = tmem_base + kColdP, tdV = tmem_base + kColdV,
-                     tdK = tmem_base + kColdK, tdQ = tmem_base + kColdQ;
-      const uint64_t dK_k = make_smem_desc_sw128(smem_u32(sK), 16, 1024);       // K as K-major B (S)
-      const uint64_t dV_k = make_smem_desc_sw128(smem_u32(sV), 16, 1024);       // V as K-major B (dP)
-      const uint64_t dK_m = make_smem_desc_sw128(smem_u32(sK), 16384, 1024);    // K as MN-major B (dQ)
-      uint64_t bK_k[KS], bV_k[KS], bK_m[8];
+    constexpr int KS = D / 16;      // k-steps of S and dP
+    const uint32_t tS = tmem_base + kColS, tdP = tmem_base + kColdP, tdV = tmem_base + kColdV,
+                   tdK = tmem_base + kColdK, tdQ = tmem_base + kColdQ;
+    auto issue_s = [&](int stage, int kvb) {
+      const uint64_t dq = make_smem_desc_sw128(smem_u32(sQ + stage * L::kTileBytes), 16, 1024);
+      const uint64_t dk = make_smem_desc_sw128(smem_u32(sK + kvb * L::kTileBytes), 16, 1024);   // K as K-major B
+      uint64_t aq[KS], bk[KS];
 #pragma unroll
       for (int kk = 0; kk < KS; ++kk) {
-        bK_k[kk] = dK_k + kmajor_step(kk, 16384);
-        bV_k[kk] = dV_k + kmajor_step(kk, 16384);
+        aq[kk] = dq + kmajor_step(kk, 16384);
+        bk[kk] = dk + kmajor_step(kk, 16384);
       }
+      if constexpr (KS == 4) umma_ss_x4(tS, aq, bk, kIdescS, 0u);
+      else umma_ss_x8(tS, aq, bk, kIdescS, 0u);
+    };
+    auto issue_dp = [&](int stage, int kvb) {
+      const uint64_t dd = make_smem_desc_sw128(smem_u32(sdO + stage * L::kTileBytes), 16, 1024);
+      const uint64_t dv = make_smem_desc_sw128(smem_u32(sV + kvb * L::kTileBytes), 16, 1024);   // V as K-major B
+      uint64_t ad[KS], bv[KS];
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk) bK_m[kk] = dK_m + mnmajor_step(kk);
+      for (int kk = 0; kk < KS; ++kk) {
+        ad[kk] = dd + kmajor_step(kk, 16384);
+        bv[kk] = dv + kmajor_step(kk, 16384);
+      }
+      if constexpr (KS == 4) umma_ss_x4(tdP, ad, bv, kIdescS, 0u);
+      else umma_ss_x8(tdP, ad, bv, kIdescS, 0u);
+      umma_commit_elect(sdp_full);
+    };
 
-      auto issue_s = [&](int i) {
-        const uint64_t dq = make_smem_desc_sw128(smem_u32(sQ + (i % ST) * L::kTileBytes), 16, 1024);
-        uint64_t aq[KS];
-#pragma unroll
-        for (int kk = 0; kk < KS; ++kk) aq[kk] = dq + kmajor_step(kk, 16384);
-        if constexpr (KS == 4) umma_ss_x4(tS, aq, bK_k, kIdescS, 0u);
-        else umma_ss_x8(tS, aq, bK_k, kIdescS, 0u);
-      };
-      auto issue_dp = [&](int i) {
-        const uint64_t dd = make_smem_desc_sw128(smem_u32(sdO + (i % ST) * L::kTileBytes), 16, 1024);
-        uint64_t ad[KS];
-#pragma unroll
-        for (int kk = 0; kk < KS; ++kk) ad[kk] = dd + kmajor_step(kk, 16384);
-        if constexpr (KS == 4) umma_ss_x4(tdP, ad, bV_k, kIdescS, 0u);
-        else umma_ss_x8(tdP, ad, bV_k, kIdescS, 0u);
-        umma_commit_elect(sdp_full);
-      };
-      TL(200);
-      mbar_wait(kv_full, 0, wctx, kSiteKvFull);
-      mbar_wait(qdo_full + 0, 0, wctx, kSiteQdoFull);
-      TL(201);
-      tc_fence_after_sync();
-      issue_s(0);
-      issue_dp(0);
-      for (int i = 0; i < n_q; ++i) {
-        TL(i * 16 + 0);
-        const int s = i % ST;
+    int n = 0, w = 0, t = 0;   // items fetched, items with work, query tiles so far
+    bool ahead = false;         // S and dP of the current item's first tile were issued during the previous item
+    BwdItem cur = fetch_item(n++, 0);
+    while (cur.id >= 0) {
+      if (cur.n_cols <= 0) {
+        cur = fetch_item(n++, 0);
+        continue;
+      }
+      const int kvb = w % KV;
+      if (!ahead) {
+        mbar_wait(kv_full + kvb, (w / KV) & 1, wctx, kSiteKvFull);
+        if (t > 0) {
+          mbar_wait(sdp_free, (t - 1) & 1, wctx, kSiteSdpFree);
+          if constexpr (!EARLY) mbar_wait(dq_free, (t - 1) & 1, wctx, kSiteDqFree);   // dQ shares the dP columns
+        }
+        mbar_wait(qdo_full + (t % ST), (t / ST) & 1, wctx, kSiteQdoFull);
+        tc_fence_after_sync();
+        issue_s(t % ST, kvb);
+        issue_dp(t % ST, kvb);
+      }
+      ahead = false;
+      BwdItem nxt = cur;
+      bool have_nxt = false;
+      const uint64_t dK_m = make_smem_desc_sw128(smem_u32(sK + kvb * L::kTileBytes), 16384, 1024);   // K as MN-major B (dQ)
+      for (int i = 0; i < n_q; ++i, ++t) {
+        TL(t * 16 + 0);
+        const int s = t % ST;
+        if constexpr (EARLY) {
+          if (i + 1 < n_q) {
+            mbar_wait(sdp_free, t & 1, wctx, kSiteSdpFree);
+            mbar_wait(qdo_full + ((t + 1) % ST), ((t + 1) / ST) & 1, wctx, kSiteQdoFull);
+            tc_fence_after_sync();
+            TL(t * 16 + 1);
+            issue_s((t + 1) % ST, kvb);
+            issue_dp((t + 1) % ST, kvb);
+          } else {
+            // last tile of this item: look at the next item and start its first tile now
+            nxt = fetch_item(n++, 0);
+            have_nxt = true;
+            if (nxt.id >= 0 && nxt.n_cols > 0) {
+              const int nkvb = (w + 1) % KV;
+              mbar_wait(kv_full + nkvb, ((w + 1) / KV) & 1, wctx, kSiteKvFull);
+              mbar_wait(sdp_free, t & 1, wctx, kSiteSdpFree);
+              mbar_wait(qdo_full + ((t + 1) % ST), ((t + 1) / ST) & 1, wctx, kSiteQdoFull);
+              tc_fence_after_sync();
+              TL(t * 16 + 1);
+              issue_s((t + 1) % ST, nkvb);
+              issue_dp((t + 1) % ST, nkvb);
+              ahead = true;
+            }
+          }
+        }
         // MN-major views of this tile's operands (16 rows = 2048 B per k-step, 64-wide halves 16 KB apart)
         const uint64_t dQ_m = make_smem_desc_sw128(smem_u32(sQ + s * L::kTileBytes), 16384, 1024);
         const uint64_t ddO_m = make_smem_desc_sw128(smem_u32(sdO + s * L::kTileBytes), 16384, 1024);
-        const uint64_t dP_m = make_smem_desc_sw128(smem_u32(sP + (i % NB) * kPdsBytes), 16384, 1024);
-        const uint64_t ddS_m = make_smem_desc_sw128(smem_u32(sdS + (i % NB) * kPdsBytes), 16384, 1024);
-        const uint64_t ddS_k = make_smem_desc_sw128(smem_u32(sdS + (i % NB) * kPdsBytes), 16, 1024);
-        uint64_t aP[8], bdO[8], adS[8], bQ[8], adSk[8];
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          aP[kk] = dP_m + mnmajor_step(kk);
-          bdO[kk] = ddO_m + mnmajor_step(kk);
-          adS[kk] = ddS_m + mnmajor_step(kk);
-          bQ[kk] = dQ_m + mnmajor_step(kk);
-          adSk[kk] = ddS_k + kmajor_step(kk, 16384);
-        }
-        if constexpr (EARLY) {
-          if (i + 1 < n_q) {
-            mbar_wait(sdp_free, i & 1, wctx, kSiteSdpFree);
-            mbar_wait(qdo_full + ((i + 1) % ST), ((i + 1) / ST) & 1, wctx, kSiteQdoFull);
-            tc_fence_after_sync();
-            TL(i * 16 + 1);
-            issue_s(i + 1);
-            issue_dp(i + 1);
-          }
-        }
-        TL(i * 16 + 2);
-        mbar_wait(pds_full, i & 1, wctx, kSitePdsFull);
-        TL(i * 16 + 3);
+        const uint64_t dP_m = make_smem_desc_sw128(smem_u32(sP), 16384, 1024);
+        const uint64_t ddS_m = make_smem_desc_sw128(smem_u32(sdS), 16384, 1024);
+        const uint64_t ddS_k = make_smem_desc_sw128(smem_u32(sdS), 16, 1024);
+        TL(t * 16 + 2);
+        mbar_wait(pds_full, t & 1, wctx, kSitePdsFull);
+        TL(t * 16 + 3);
         tc_fence_after_sync();
         // dV += P^T dO ; dK += dS^T Q : A is the [q x keys] tile read MN-major (keys contiguous),
         // 16 query rows (2048 B) per k-step, the two 64-key halves 16 KB apart.
         const uint32_t acc0 = (i > 0) ? 1u : 0u;
-        umma_ss_x8(tdV, aP, bdO, kIdescT, acc0);
-        umma_ss_x8(tdK, adS, bQ, kIdescT, acc0);
+        {
+          uint64_t x[8], y[8];
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            x[kk] = dP_m + mnmajor_step(kk);
+            y[kk] = ddO_m + mnmajor_step(kk);
+          }
+          umma_ss_x8(tdV, x, y, kIdescT, acc0);
+        }
+        {
+          uint64_t x[8], y[8];
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            x[kk] = ddS_m + mnmajor_step(kk);
+            y[kk] = dQ_m + mnmajor_step(kk);
+          }
+          umma_ss_x8(tdK, x, y, kIdescT, acc0);
+        }
         umma_commit_elect(qdo_empty + s);  // Q and dO of this stage are not read again (dQ needs dS and K only)
-        TL(i * 16 + 4);
-        if (i > 0) {
-          mbar_wait(dq_free, (i - 1) & 1, wctx, kSiteDqFree);
+        if (i == n_q - 1) umma_commit_elect(acc_full);
+        TL(t * 16 + 4);
+        if (t > 0) {
+          mbar_wait(dq_free, (t - 1) & 1, wctx, kSiteDqFree);
           tc_fence_after_sync();
         }
-        TL(i * 16 + 5);
+        TL(t * 16 + 5);
         // dQ tile = dS K : A K-major (keys along the row), B = K tile read MN-major
-        umma_ss_x8(tdQ, adSk, bK_m, kIdescQ, 0u);
+        {
+          uint64_t x[8], y[8];
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            x[kk] = ddS_k + kmajor_step(kk, 16384);
+            y[kk] = dK_m + mnmajor_step(kk);
+          }
+          umma_ss_x8(tdQ, x, y, kIdescQ, 0u);
+        }
         umma_commit_elect(dq_full);
-        TL(i * 16 + 6);
+        if (i == n_q - 1) umma_commit_elect(kv_empty + kvb);   // K and V of this item are not read again
+        TL(t * 16 + 6);
         if constexpr (!EARLY) {
           if (i + 1 < n_q) {
-            mbar_wait(qdo_full + ((i + 1) % ST), ((i + 1) / ST) & 1, wctx, kSiteQdoFull);
+            mbar_wait(qdo_full + ((t + 1) % ST), ((t + 1) / ST) & 1, wctx, kSiteQdoFull);
             tc_fence_after_sync();
-            issue_s(i + 1);                                      // S columns were released before pds_full(i)
-            mbar_wait(dq_free, i & 1, wctx, kSiteDqFree);       // dQ shares the dP columns
+            issue_s((t + 1) % ST, kvb);                          // S columns were released before pds_full(t)
+            mbar_wait(dq_free, t & 1, wctx, kSiteDqFree);        // dQ shares the dP columns
             tc_fence_after_sync();
-            issue_dp(i + 1);
+            issue_dp((t + 1) % ST, kvb);
           }
         }
       }
-      umma_commit_elect(acc_full);
+      ++w;
+      cur = have_nxt ? nxt : fetch_item(n++, 0);
     }
   } else {
     // ============================ compute warps =====================================
@@ -402,20 +511,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
     const int tid = threadIdx.x - 64;    // 0..511
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const float sl2 = a.scale_log2;
-    const uint32_t gbh = static_cast<uint32_t>(a.philox_bh_offset + bh);
     // With dropout dS is formed as keep*P*dP - P*delta/c and the factor c = 1/(1-p) moves into the
     // final scaling of dQ and dK (and of dV, whose P operand is unscaled as well).
     const float inv_c = DROP ? 1.0f / a.dropout_scale : 1.0f;
+    const float dscale = DROP ? a.dropout_scale : 1.0f;
     const int cbase = cq * 32;           // first column of this thread within the tile
     constexpr int DQ = D / 4;            // columns of a [128 x D] accumulator handled by one thread
-
-    if constexpr (KEYADD) {
-      if (n_q > 0 && tid < kTileN) {
-        const int c = k0 + tid;
-        sMask[tid] = (c < a.S_k) ? reinterpret_cast<const float*>(a.mask)[static_cast<size_t>(b) * a.S_k + c] * kLog2eB : 0.f;
-      }
-    }
-    named_bar_sync(1, kComputeThreads);
 
     // Every warp polls the mbarrier itself: funnelling the wait through one warp and a named barrier
     // was measured 8 % slower (it removes the skew between warps that lets their phases overlap).
@@ -424,12 +525,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
       tc_fence_after_sync();
     };
 
-    // dQ tile of query tile `it` -> global fp32 accumulator,
-    // through shared memory and one TMA reduce-add per 32-column group: the additions are
-    // performed line by line by the TMA unit instead of 2048 scattered 16-byte atomics per tile,
-    // which occupied the compute warps for ~1500 cycles per tile.
-    auto dq_readout_tma = [&](int it) {
-      wait_all(dq_full, it & 1, kSiteDqFull);
+    // D = 128: dQ tile `tt` (rows from `row0` of the accumulator) -> shared memory (the idle P/dS
+    // buffers) -> one TMA reduce-add per 32-column group.  The additions are performed line by line
+    // by the TMA unit instead of 2048 scattered 16-byte atomics per tile, which occupied the
+    // compute warps for ~1500 cycles per tile.
+    auto dq_readout_tma = [&](int tt, int row0) {
+      wait_all(dq_full, tt & 1, kSiteDqFull);
       uint32_t r[DQ];
 #pragma unroll
       for (int c = 0; c < DQ / 16; ++c) {
@@ -441,8 +542,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
       }
       tc_fence_before_sync();
       mbar_arrive(dq_free);                          // the dQ columns may be overwritten
-      if (tid == 0) tma_store_wait_read();           // an earlier reduce has read the staging buffer
-      named_bar_sync(2, kComputeThreads);
       {
         // this thread's DQ floats of row `row`: sub-tile (cq*DQ)/32, 16-byte chunks from ((cq*DQ)%32)/4
         const uint32_t tile = smem_u32(sDQ + ((cq * DQ) / 32) * 16384);
@@ -454,17 +553,15 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
       fence_proxy_async_smem();
       named_bar_sync(3, kComputeThreads);
       if (tid == 0 && *abort_flag == 0) {
-        const int row0 = bh * a.S_q_pad + it * kTileM;
 #pragma unroll
-        for (int t = 0; t < D / 32; ++t) tma_reduce_add_2d(&a.tm_dq, sDQ + t * 16384, t * 32, row0);
+        for (int g = 0; g < D / 32; ++g) tma_reduce_add_2d(&a.tm_dq, sDQ + g * 16384, g * 32, row0);
         tma_store_commit();
       }
     };
-
     // D = 64: every warp stages its own 32 rows x 16 columns (2 KB, 64-byte swizzle) and its lane 0
     // issues the reduce, so the warps never wait for one another here.
-    auto dq_readout_warp = [&](int it) {
-      wait_all(dq_full, it & 1, kSiteDqFull);
+    auto dq_readout_warp = [&](int tt, int row0) {
+      wait_all(dq_full, tt & 1, kSiteDqFull);
       uint32_t t16[16];
       tmem_ld16(tmem_base + lane_addr + kColdQ + cq * 16, t16);
       tmem_wait_ld();
@@ -481,188 +578,220 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0 && *abort_flag == 0) {
-        tma_reduce_add_2d(&a.tm_dq, stage, cq * 16, bh * a.S_q_pad + it * kTileM + quad * 32);
+        tma_reduce_add_2d(&a.tm_dq, stage, cq * 16, row0 + quad * 32);
         tma_store_commit();
       }
     };
-
-    // Row statistics of the next tile are fetched one iteration ahead and kept RAW: any arithmetic
-    // on the loaded value here would make the warp wait for the load at once (~1000 cycles per tile).
-    float lse_next = INFINITY, delta_next = 0.f;
-    if (n_q > 0 && row < a.S_q) {
-      lse_next = a.lse[static_cast<size_t>(bh) * a.S_q + row];
-      delta_next = a.delta[static_cast<size_t>(bh) * a.S_q + row];
-    }
-
-    for (int i = 0; i < n_q; ++i) {
-      const int q_row = i * kTileM + row;
-      // lse in the log2 domain; +inf for rows past the end makes their probabilities zero
-      const float neg_lse2 = -lse_next * kLog2eB;
-      const float delta = delta_next * inv_c;
-      {
-        const int nr = q_row + kTileM;  // prefetch the statistics of the next tile's row
-        const bool ok = (i + 1 < n_q) && nr < a.S_q;
-        lse_next = INFINITY;
-        delta_next = 0.f;
-        if (ok) {
-          lse_next = a.lse[static_cast<size_t>(bh) * a.S_q + nr];
-          delta_next = a.delta[static_cast<size_t>(bh) * a.S_q + nr];
-        }
-      }
-
-      if (tid == 0) TL(i * 16 + 8);
-      wait_all(sdp_full, i & 1, kSiteSdpFull);
-      if (tid == 0) TL(i * 16 + 9);
-      uint32_t rs[32], rp[32];
-      tmem_ld32(tmem_base + lane_addr + kColS + cbase, rs);
-      tmem_ld32(tmem_base + lane_addr + kColdP + cbase, rp);
-      tmem_wait_ld_dep(rs);
-      tmem_wait_ld_dep(rp);
-      tc_fence_before_sync();
-      mbar_arrive(sdp_free);   // the tensor core may overwrite S and dP now
-      if (tid == 0) TL(i * 16 + 10);
-
-      uint32_t pk_p[16], pk_ds[16];  // 32 columns: 16 packed pairs each
-      auto chunk = [&](auto edge_tag) {
-        constexpr bool EDGE = decltype(edge_tag)::value;
-        const float2 sl22 = make_float2(sl2, sl2);
-        const float2 nl2 = make_float2(neg_lse2, neg_lse2);
-        const float2 nd2 = make_float2(-delta, -delta);
-        [[maybe_unused]] uint32_t w[8];
-        if constexpr (DROP) {
+    // dK and dV of a finished item: tensor memory -> registers -> global memory (16-bit).  Thread
+    // (row, cq) holds DQ consecutive columns of key row k0 + row.
+    auto store_dkdv = [&](int item_id, bool from_tmem) {
+      const BwdItem it = decode(item_id);
+      const int key = it.k0 + row;
 #pragma unroll
-          for (int d = 0; d < 2; ++d) {
-            const U4 draw = dropout_draw_keys(a.philox_keys, a.philox_offset, gbh, static_cast<uint32_t>(q_row),
-                                         static_cast<uint32_t>((k0 + cbase) / 16 + d));
-            w[d * 4 + 0] = (draw.x & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
-            w[d * 4 + 1] = (draw.y & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
-            w[d * 4 + 2] = (draw.z & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
-            w[d * 4 + 3] = (draw.w & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
-          }
-        }
+      for (int which = 0; which < 2; ++which) {
+        const float mul = (which == 0) ? dscale : a.scale * dscale;
+        unsigned short* base = reinterpret_cast<unsigned short*>(which == 0 ? a.dv : a.dk);
+        const int64_t off = (which == 0)
+                                ? it.b * a.dv_sb + it.h * a.dv_sh + static_cast<int64_t>(key) * a.dv_ss
+                                : it.b * a.dk_sb + it.h * a.dk_sh + static_cast<int64_t>(key) * a.dk_ss;
 #pragma unroll
-        for (int k = 0; k < 16; ++k) {
-          float2 x = make_float2(__uint_as_float(rs[2 * k]), __uint_as_float(rs[2 * k + 1]));
-          if constexpr (KEYADD) {
-            const float2 mk = *reinterpret_cast<const float2*>(sMask + cbase + 2 * k);
-            x = __fadd2_rn(__ffma2_rn(x, sl22, mk), nl2);
+        for (int c = 0; c < DQ / 16; ++c) {
+          const int dcol = cq * DQ + c * 16;               // first of 16 accumulator columns
+          uint32_t r[16];
+          if (from_tmem) {
+            tmem_ld16(tmem_base + lane_addr + (which == 0 ? kColdV : kColdK) + dcol, r);
+            tmem_wait_ld();
           } else {
-            x = __ffma2_rn(x, sl22, nl2);
+#pragma unroll
+            for (int k = 0; k < 16; ++k) r[k] = 0u;
           }
-          float2 p;
-          p.x = fast_exp2(x.x);
-          p.y = fast_exp2(x.y);
-          if constexpr (EDGE) {                            // keys past the valid length / tensor edge
-            if (cbase + 2 * k >= n_cols) p.x = 0.f;
-            if (cbase + 2 * k + 1 >= n_cols) p.y = 0.f;
+          if (key < a.S_k) {
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              uint4 w;
+              w.x = pack2<BF16>(__uint_as_float(r[q * 8 + 0]) * mul, __uint_as_float(r[q * 8 + 1]) * mul);
+              w.y = pack2<BF16>(__uint_as_float(r[q * 8 + 2]) * mul, __uint_as_float(r[q * 8 + 3]) * mul);
+              w.z = pack2<BF16>(__uint_as_float(r[q * 8 + 4]) * mul, __uint_as_float(r[q * 8 + 5]) * mul);
+              w.w = pack2<BF16>(__uint_as_float(r[q * 8 + 6]) * mul, __uint_as_float(r[q * 8 + 7]) * mul);
+              *reinterpret_cast<uint4*>(base + off + dcol + q * 8) = w;
+            }
           }
-          const float2 dp = make_float2(__uint_as_float(rp[2 * k]), __uint_as_float(rp[2 * k + 1]));
-          float2 pkeep = p;
+        }
+      }
+    };
+
+    int n = 0, w = 0, t = 0;      // items fetched, items with work, query tiles so far
+    bool prev_pending = false;    // dK/dV of item `prev` are still in tensor memory
+    int prev_id = -1;
+    int prev_row0 = 0;            // accumulator row of the tile whose dQ is still in tensor memory (D = 64)
+
+    while (true) {
+      const BwdItem cur = fetch_item(n++, kComputeSleepNs);
+      if (cur.id < 0) break;
+      if (cur.n_cols <= 0) {
+        store_dkdv(cur.id, false);   // key tile wholly past the valid length: its gradients are zero
+        continue;
+      }
+      const int k0 = cur.k0, n_cols = cur.n_cols, bh = cur.bh;
+      const uint32_t gbh = static_cast<uint32_t>(a.philox_bh_offset + bh);
+      const float* mask_row = sMask + (w & 1) * kTileN;
+      if constexpr (KEYADD) {
+        // both barriers are needed: a slower warp may still read the other item's values (first),
+        // and every warp reads what the first four wrote (second)
+        named_bar_sync(1, kComputeThreads);
+        if (tid < kTileN) {
+          const int c = k0 + tid;
+          sMask[(w & 1) * kTileN + tid] =
+              (c < a.S_k) ? reinterpret_cast<const float*>(a.mask)[static_cast<size_t>(cur.b) * a.S_k + c] * kLog2eB : 0.f;
+        }
+        named_bar_sync(1, kComputeThreads);
+      }
+
+      // Row statistics of the next tile are fetched one iteration ahead and kept RAW: any arithmetic
+      // on the loaded value here would make the warp wait for the load at once (~1000 cycles per tile).
+      float lse_next = INFINITY, delta_next = 0.f;
+      if (row < a.S_q) {
+        lse_next = a.lse[static_cast<size_t>(bh) * a.S_q + row];
+        delta_next = a.delta[static_cast<size_t>(bh) * a.S_q + row];
+      }
+
+      for (int i = 0; i < n_q; ++i, ++t) {
+        const int q_row = i * kTileM + row;
+        // lse in the log2 domain; +inf for rows past the end makes their probabilities zero
+        const float neg_lse2 = -lse_next * kLog2eB;
+        const float delta = delta_next * inv_c;
+        {
+          const int nr = q_row + kTileM;  // prefetch the statistics of the next tile's row
+          const bool ok = (i + 1 < n_q) && nr < a.S_q;
+          lse_next = INFINITY;
+          delta_next = 0.f;
+          if (ok) {
+            lse_next = a.lse[static_cast<size_t>(bh) * a.S_q + nr];
+            delta_next = a.delta[static_cast<size_t>(bh) * a.S_q + nr];
+          }
+        }
+
+        if (tid == 0) TL(t * 16 + 8);
+        wait_all(sdp_full, t & 1, kSiteSdpFull);
+        if (tid == 0) TL(t * 16 + 9);
+        uint32_t rs[32], rp[32];
+        tmem_ld32(tmem_base + lane_addr + kColS + cbase, rs);
+        tmem_ld32(tmem_base + lane_addr + kColdP + cbase, rp);
+        tmem_wait_ld_dep(rs);
+        tmem_wait_ld_dep(rp);
+        tc_fence_before_sync();
+        mbar_arrive(sdp_free);   // the tensor core may overwrite S and dP now
+        if (tid == 0) TL(t * 16 + 10);
+
+        uint32_t pk_p[16], pk_ds[16];  // 32 columns: 16 packed pairs each
+        auto chunk = [&](auto edge_tag) {
+          constexpr bool EDGE = decltype(edge_tag)::value;
+          const float2 sl22 = make_float2(sl2, sl2);
+          const float2 nl2 = make_float2(neg_lse2, neg_lse2);
+          const float2 nd2 = make_float2(-delta, -delta);
+          [[maybe_unused]] uint32_t kw8[8];
           if constexpr (DROP) {
-            // bit 7 of byte e of the keep word decides element e; the permute smears it over 32 bits
-            const uint32_t kw = w[k >> 1];
-            const uint32_t m0 = prmt(kw, 0u, (k & 1) ? 0xAAAAu : 0x8888u);
-            const uint32_t m1 = prmt(kw, 0u, (k & 1) ? 0xBBBBu : 0x9999u);
-            pkeep.x = __uint_as_float(__float_as_uint(p.x) & m0);
-            pkeep.y = __uint_as_float(__float_as_uint(p.y) & m1);
+#pragma unroll
+            for (int d = 0; d < 2; ++d) {
+              const U4 draw = dropout_draw_keys(a.philox_keys, a.philox_offset, gbh, static_cast<uint32_t>(q_row),
+                                           static_cast<uint32_t>((k0 + cbase) / 16 + d));
+              kw8[d * 4 + 0] = (draw.x & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
+              kw8[d * 4 + 1] = (draw.y & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
+              kw8[d * 4 + 2] = (draw.z & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
+              kw8[d * 4 + 3] = (draw.w & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
+            }
           }
-          const float2 ds = __ffma2_rn(pkeep, dp, __fmul2_rn(p, nd2));
-          pk_p[k] = pack2<BF16>(pkeep.x, pkeep.y);
-          pk_ds[k] = pack2<BF16>(ds.x, ds.y);
-        }
-      };
-      if (n_cols >= kTileN) chunk(std::false_type{});
-      else chunk(std::true_type{});
+#pragma unroll
+          for (int k = 0; k < 16; ++k) {
+            float2 x = make_float2(__uint_as_float(rs[2 * k]), __uint_as_float(rs[2 * k + 1]));
+            if constexpr (KEYADD) {
+              const float2 mk = *reinterpret_cast<const float2*>(mask_row + cbase + 2 * k);
+              x = __fadd2_rn(__ffma2_rn(x, sl22, mk), nl2);
+            } else {
+              x = __ffma2_rn(x, sl22, nl2);
+            }
+            float2 p;
+            p.x = fast_exp2(x.x);
+            p.y = fast_exp2(x.y);
+            if constexpr (EDGE) {                            // keys past the valid length / tensor edge
+              if (cbase + 2 * k >= n_cols) p.x = 0.f;
+              if (cbase + 2 * k + 1 >= n_cols) p.y = 0.f;
+            }
+            const float2 dp = make_float2(__uint_as_float(rp[2 * k]), __uint_as_float(rp[2 * k + 1]));
+            float2 pkeep = p;
+            if constexpr (DROP) {
+              // bit 7 of byte e of the keep word decides element e; the permute smears it over 32 bits
+              const uint32_t kw = kw8[k >> 1];
+              const uint32_t m0 = prmt(kw, 0u, (k & 1) ? 0xAAAAu : 0x8888u);
+              const uint32_t m1 = prmt(kw, 0u, (k & 1) ? 0xBBBBu : 0x9999u);
+              pkeep.x = __uint_as_float(__float_as_uint(p.x) & m0);
+              pkeep.y = __uint_as_float(__float_as_uint(p.y) & m1);
+            }
+            const float2 ds = __ffma2_rn(pkeep, dp, __fmul2_rn(p, nd2));
+            pk_p[k] = pack2<BF16>(pkeep.x, pkeep.y);
+            pk_ds[k] = pack2<BF16>(ds.x, ds.y);
+          }
+        };
+        if (n_cols >= kTileN) chunk(std::false_type{});
+        else chunk(std::true_type{});
 
-      if (tid == 0) TL(i * 16 + 11);
-      if constexpr (EARLY) {
-        // dQ of the previous tile is complete <=> the MMAs which read the single P/dS buffer have
-        // completed, so it can be overwritten below (the dQ tile itself is read out afterwards).
-        if (i > 0) wait_all(dq_full, (i - 1) & 1, kSiteDqFull);
-      } else {
-        // D = 128: the previous tile's dQ was staged in the P/dS buffers; the reduce must have read them.
-        if (i > 0) {
-          if (tid == 0) tma_store_wait_read();
-          named_bar_sync(2, kComputeThreads);
-        }
-      }
-      {
-        // columns [32*cq, +32) of row `row`: 64 bytes = 16-byte chunks (cq%2)*4 .. +3 of sub-tile cq/2
-        const uint32_t bufP = smem_u32(sP + (i % NB) * kPdsBytes + (cq >> 1) * 16384);
-        const uint32_t bufS = smem_u32(sdS + (i % NB) * kPdsBytes + (cq >> 1) * 16384);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const uint32_t off = sw128_offset(row, (cq & 1) * 4 + q);
-          sts128(bufP + off, pk_p[q * 4], pk_p[q * 4 + 1], pk_p[q * 4 + 2], pk_p[q * 4 + 3]);
-          sts128(bufS + off, pk_ds[q * 4], pk_ds[q * 4 + 1], pk_ds[q * 4 + 2], pk_ds[q * 4 + 3]);
-        }
-      }
-      fence_proxy_async_smem();
-      mbar_arrive(pds_full);
-      if (tid == 0) TL(i * 16 + 12);
-      if constexpr (EARLY) {
-        if (i > 0) dq_readout_warp(i - 1);
-      } else {
-        dq_readout_tma(i);   // D = 128: dQ shares columns with dP, it must be out before dP of tile i+1
-      }
-      if (tid == 0) TL(i * 16 + 13);
-    }
-    if constexpr (EARLY) {
-      if (n_q > 0) dq_readout_warp(n_q - 1);
-      if (lane == 0) tma_store_wait_read();   // shared memory must stay valid until the reduce has read it
-    }
-    if (tid == 0) TL(202);
-
-    // ---- epilogue: dK, dV -> 16-bit -> shared memory -> TMA store ----------------------
-    if (n_q > 0) wait_all(acc_full, 0, kSiteAccFull);
-    if constexpr (!OWNSTAGE) {
-      if (tid == 0) tma_store_wait_read();   // the last dQ reduce has read the P/dS buffers
-      named_bar_sync(2, kComputeThreads);
-    }
-    // The P/dS buffers are free (every MMA that read them has completed); dV goes to sP, dK to sdS.
-    const float dscale = DROP ? a.dropout_scale : 1.0f;
-#pragma unroll
-    for (int which = 0; which < 2; ++which) {
-      const float mul = (which == 0) ? dscale : a.scale * dscale;
-      uint8_t* stage = (which == 0) ? sP : sdS;
-#pragma unroll
-      for (int c = 0; c < DQ / 16; ++c) {
-        const int dcol = cq * DQ + c * 16;               // first of 16 accumulator columns
-        uint32_t r[16];
-        if (n_q > 0) {
-          tmem_ld16(tmem_base + lane_addr + (which == 0 ? kColdV : kColdK) + dcol, r);
-          tmem_wait_ld();
+        if (tid == 0) TL(t * 16 + 11);
+        if constexpr (EARLY) {
+          // dQ of the previous tile is complete <=> the MMAs which read the single P/dS buffer have
+          // completed, so it can be overwritten below (the dQ tile itself is read out afterwards).
+          if (t > 0) wait_all(dq_full, (t - 1) & 1, kSiteDqFull);
         } else {
-#pragma unroll
-          for (int k = 0; k < 16; ++k) r[k] = 0u;
+          // D = 128: the previous tile's dQ was staged in the P/dS buffers; the reduce must have read them.
+          if (t > 0) {
+            if (tid == 0) tma_store_wait_read();
+            named_bar_sync(2, kComputeThreads);
+          }
         }
-        uint8_t* tile = stage + (dcol / 64) * 16384;     // 64-column sub-tile; 16 columns = two 16-byte chunks
-#pragma unroll
-        for (int q = 0; q < 2; ++q) {
-          uint4 w;
-          w.x = pack2<BF16>(__uint_as_float(r[q * 8 + 0]) * mul, __uint_as_float(r[q * 8 + 1]) * mul);
-          w.y = pack2<BF16>(__uint_as_float(r[q * 8 + 2]) * mul, __uint_as_float(r[q * 8 + 3]) * mul);
-          w.z = pack2<BF16>(__uint_as_float(r[q * 8 + 4]) * mul, __uint_as_float(r[q * 8 + 5]) * mul);
-          w.w = pack2<BF16>(__uint_as_float(r[q * 8 + 6]) * mul, __uint_as_float(r[q * 8 + 7]) * mul);
-          *reinterpret_cast<uint4*>(tile + sw128_offset(row, ((dcol % 64) / 8) + q)) = w;
+        if (i == 0 && prev_pending) {
+          // dK and dV of the previous item: complete since its last dV/dK MMAs, and they must be out
+          // of tensor memory before this tile's P and dS let the tensor core overwrite them.
+          wait_all(acc_full, (w - 1) & 1, kSiteAccFull);
+          store_dkdv(prev_id, true);
+          tc_fence_before_sync();
+          prev_pending = false;
         }
+        {
+          // columns [32*cq, +32) of row `row`: 64 bytes = 16-byte chunks (cq%2)*4 .. +3 of sub-tile cq/2
+          const uint32_t bufP = smem_u32(sP + (cq >> 1) * 16384);
+          const uint32_t bufS = smem_u32(sdS + (cq >> 1) * 16384);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const uint32_t off = sw128_offset(row, (cq & 1) * 4 + q);
+            sts128(bufP + off, pk_p[q * 4], pk_p[q * 4 + 1], pk_p[q * 4 + 2], pk_p[q * 4 + 3]);
+            sts128(bufS + off, pk_ds[q * 4], pk_ds[q * 4 + 1], pk_ds[q * 4 + 2], pk_ds[q * 4 + 3]);
+          }
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(pds_full);
+        if (tid == 0) TL(t * 16 + 12);
+        const int row0 = bh * a.S_q_pad + i * kTileM;
+        if constexpr (EARLY) {
+          if (t > 0) dq_readout_warp(t - 1, prev_row0);
+          prev_row0 = row0;
+        } else {
+          dq_readout_tma(t, row0);   // D = 128: dQ shares columns with dP, it must be out before dP of tile t+1
+        }
+        if (tid == 0) TL(t * 16 + 13);
       }
+      prev_id = cur.id;
+      prev_pending = true;
+      ++w;
     }
-    fence_proxy_async_smem();
-    named_bar_sync(1, kComputeThreads);
-    if (tid == 0) TL(203);
-    if (tid == 0) {
-      if (*abort_flag == 0) {
-#pragma unroll
-        for (int c = 0; c < D / 64; ++c) {
-          tma_store_4d(&a.tm_dv, sP + c * 16384, c * 64, k0, h, b);
-          tma_store_4d(&a.tm_dk, sdS + c * 16384, c * 64, k0, h, b);
-        }
-        tma_store_commit();
-      }
-      tma_store_wait_read();
-      TL(204);
+    // ---- drain: the last tile's dQ and the last item's dK, dV ------------------------------
+    if constexpr (EARLY) {
+      if (t > 0) dq_readout_warp(t - 1, prev_row0);
     }
+    if (prev_pending) {
+      wait_all(acc_full, (w - 1) & 1, kSiteAccFull);
+      store_dkdv(prev_id, true);
+    }
+    if (OWNSTAGE ? (lane == 0) : (tid == 0)) tma_store_wait_read();   // shared memory stays valid until the reduce has read it
+    if (tid == 0) TL(254);
   }
 
   tc_fence_before_sync();
@@ -686,14 +815,24 @@ static int launch_bwd_impl(const BwdArgs& a, cudaStream_t stream) {
   using L = BwdSmem<D>;
   auto kfn = fmha_bwd_kernel<D, BF16, KEYADD, DROP>;
   static bool configured[64] = {};
+  static int sm_count[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
+  int sms = 0;
   if (dev < 0 || dev >= 64 || !configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
-    if (dev >= 0 && dev < 64) configured[dev] = true;
+    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (dev >= 0 && dev < 64) {
+      sm_count[dev] = sms;
+      configured[dev] = true;
+    }
+  } else {
+    sms = sm_count[dev];
   }
-  dim3 grid((a.S_k + kTileN - 1) / kTileN, a.H, a.B);
+  const int64_t items = static_cast<int64_t>((a.S_k + kTileN - 1) / kTileN) * a.H * a.B;
+  const int grid = static_cast<int>(items < sms ? items : sms);   // one persistent CTA per SM
   kfn<<<grid, kBwdThreads, L::kDynBytes, stream>>>(a);
   return static_cast<int>(cudaGetLastError());
 }
@@ -725,14 +864,14 @@ int launch_bwd(const BwdArgs& a, int D, int dtype, cudaStream_t stream) {
 }
 
 int launch_bwd_prepare(const void* o, const fmha_tensor4& ot, const fmha_tensor4& dot, int B, int H, int S_q, int S_q_pad,
-                       int D, int dtype, float* delta, float* dq_accum, cudaStream_t stream) {
+                       int D, int dtype, float* delta, float* dq_accum, int* work_counter, cudaStream_t stream) {
   PrepArgs p;
   p.o = ot.ptr; p.d_o = dot.ptr;
   (void)o;
   p.o_sb = ot.stride_b; p.o_sh = ot.stride_h; p.o_ss = ot.stride_s;
   p.do_sb = dot.stride_b; p.do_sh = dot.stride_h; p.do_ss = dot.stride_s;
   p.B = B; p.H = H; p.S_q = S_q; p.S_q_pad = S_q_pad; p.D = D;
-  p.delta = delta; p.dq_accum = dq_accum;
+  p.delta = delta; p.dq_accum = dq_accum; p.work_counter = work_counter;
   const int64_t threads = static_cast<int64_t>(B) * H * S_q_pad * 8;
   const int block = 256;
   const int64_t blocks = (threads + block - 1) / block;

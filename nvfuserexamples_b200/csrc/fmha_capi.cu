@@ -217,7 +217,8 @@ int fmha_sm100_bwd_workspace_bytes(const fmha_bwd_params* p, size_t* bytes) {
   if (rc != FMHA_OK) return rc;
   const size_t bh = static_cast<size_t>(p->B) * p->H;
   const size_t s_q_pad = (static_cast<size_t>(p->S_q) + kTileM - 1) / kTileM * kTileM;
-  *bytes = align256(bh * s_q_pad * p->D * sizeof(float)) + align256(bh * p->S_q * sizeof(float));
+  // fp32 dQ accumulator, delta, and the work-item counter of the persistent main kernel
+  *bytes = align256(bh * s_q_pad * p->D * sizeof(float)) + align256(bh * p->S_q * sizeof(float)) + 256;
   return FMHA_OK;
 }
 
@@ -253,6 +254,7 @@ int fmha_sm100_bwd(const fmha_bwd_params* p, void* stream_) {
   const size_t bh = static_cast<size_t>(p->B) * p->H;
   float* dq_accum = reinterpret_cast<float*>(p->workspace);
   float* delta = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p->workspace) + align256(bh * s_q_pad * p->D * sizeof(float)));
+  int* work_counter = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(delta) + align256(bh * p->S_q * sizeof(float)));
 
   BwdArgs a;
   std::memset(&a, 0, sizeof(a));
@@ -264,8 +266,9 @@ int fmha_sm100_bwd(const fmha_bwd_params* p, void* stream_) {
   if ((rc = make_tmap(&a.tm_k, tk, p->dtype, p->B, p->H, p->S_k, p->D, kTileN))) return rc;
   if ((rc = make_tmap(&a.tm_v, tv, p->dtype, p->B, p->H, p->S_k, p->D, kTileN))) return rc;
   if ((rc = make_tmap(&a.tm_do, tdo, p->dtype, p->B, p->H, p->S_q, p->D, kTileM))) return rc;
-  if ((rc = make_tmap(&a.tm_dk, tdk, p->dtype, p->B, p->H, p->S_k, p->D, kTileN))) return rc;
-  if ((rc = make_tmap(&a.tm_dv, tdv, p->dtype, p->B, p->H, p->S_k, p->D, kTileN))) return rc;
+  a.dk = tdk.ptr; a.dk_sb = tdk.stride_b; a.dk_sh = tdk.stride_h; a.dk_ss = tdk.stride_s;
+  a.dv = tdv.ptr; a.dv_sb = tdv.stride_b; a.dv_sh = tdv.stride_h; a.dv_ss = tdv.stride_s;
+  a.work_counter = work_counter;
   if ((rc = make_tmap_accum(&a.tm_dq, dq_accum, static_cast<uint64_t>(bh) * s_q_pad, p->D))) return rc;
   a.B = p->B; a.H = p->H; a.S_q = p->S_q; a.S_k = p->S_k;
   a.scale = p->scale;
@@ -292,8 +295,12 @@ int fmha_sm100_bwd(const fmha_bwd_params* p, void* stream_) {
 
   int e = 0;
   if (!(p->flags & FMHA_FLAG_BWD_SKIP_PREPARE)) {
-    e = launch_bwd_prepare(nullptr, to, tdo, p->B, p->H, p->S_q, s_q_pad, p->D, p->dtype, delta, dq_accum, stream);
+    e = launch_bwd_prepare(nullptr, to, tdo, p->B, p->H, p->S_q, s_q_pad, p->D, p->dtype, delta, dq_accum, work_counter, stream);
     if (e != 0) return cuda_fail(static_cast<cudaError_t>(e));
+  } else {
+    // the caller prepared delta and the accumulator itself; the work counter is still ours to clear
+    cudaError_t ce = cudaMemsetAsync(work_counter, 0, sizeof(int), stream);
+    if (ce != cudaSuccess) return cuda_fail(ce);
   }
   e = launch_bwd(a, p->D, p->dtype, stream);
   if (e != 0) return cuda_fail(static_cast<cudaError_t>(e));

@@ -46,8 +46,6 @@ struct BwdArgs {
   alignas(64) CUtensorMap tm_k;
   alignas(64) CUtensorMap tm_v;
   alignas(64) CUtensorMap tm_do;
-  alignas(64) CUtensorMap tm_dk;
-  alignas(64) CUtensorMap tm_dv;
   alignas(64) CUtensorMap tm_dq;  // fp32 dQ accumulator as [B*H*S_q_pad, D], 32-column boxes (TMA reduce-add)
   int B, H, S_q, S_k;
   float scale;       // softmax scale
@@ -55,6 +53,10 @@ struct BwdArgs {
   const float* lse;  // [B*H, S_q] natural log
   const float* delta;  // [B*H, S_q] rowsum(dO * O)
   float* dq_accum;     // [B*H, S_q_pad, D] fp32, zero on entry
+  int* work_counter;   // zero on entry; the persistent CTAs draw their work items from it
+  void* dk;            // 16-bit outputs, written from registers: element strides of b, h, s
+  void* dv;
+  int64_t dk_sb, dk_sh, dk_ss, dv_sb, dv_sh, dv_ss;
   int S_q_pad;         // S_q rounded up to the tile
   int mask_kind;
   const void* mask;
@@ -73,7 +75,7 @@ int launch_fwd(const FwdArgs& a, int D, int dtype, bool legacy, bool p_via_smem,
 int launch_fwd_fast(const FwdArgs& a, int D, int dtype, cudaStream_t stream);
 int launch_bwd(const BwdArgs& a, int D, int dtype, cudaStream_t stream);
 int launch_bwd_prepare(const void* o, const fmha_tensor4& ot, const fmha_tensor4& dot, int B, int H, int S_q, int S_q_pad,
-                       int D, int dtype, float* delta, float* dq_accum, cudaStream_t stream);
+                       int D, int dtype, float* delta, float* dq_accum, int* work_counter, cudaStream_t stream);
 int launch_bwd_finish(const float* dq_accum, const fmha_tensor4& dq, int B, int H, int S_q, int S_q_pad, int D, int dtype,
                       float scale, cudaStream_t stream);
 
