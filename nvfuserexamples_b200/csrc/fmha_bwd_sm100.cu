@@ -35,7 +35,10 @@ namespace fmha {
 
 namespace {
 
-constexpr uint32_t kComputeSleepNs = 48;  // pause between barrier polls of the compute warps
+#ifndef FMHA_BWD_POLL_SLEEP_NS
+#define FMHA_BWD_POLL_SLEEP_NS 48
+#endif
+constexpr uint32_t kComputeSleepNs = FMHA_BWD_POLL_SLEEP_NS;  // pause between barrier polls of the compute warps
 constexpr int kComputeThreads = 512;               // 16 compute warps
 constexpr int kBwdThreads = 64 + kComputeThreads;   // + producer warp + MMA warp
 constexpr float kLog2eB = 1.4426950408889634f;
@@ -258,6 +261,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
     tma_prefetch_desc(&a.tm_k);
     tma_prefetch_desc(&a.tm_v);
     tma_prefetch_desc(&a.tm_do);
+    tma_prefetch_desc(&a.tm_dk);
+    tma_prefetch_desc(&a.tm_dv);
     tma_prefetch_desc(&a.tm_dq);
   }
   if (warp == 1) {
@@ -562,13 +567,16 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
     // issues the reduce, so the warps never wait for one another here.
     auto dq_readout_warp = [&](int tt, int row0) {
       wait_all(dq_full, tt & 1, kSiteDqFull);
+      if (tid == 0) TL((tt + 1) * 16 + 7);
       uint32_t t16[16];
       tmem_ld16(tmem_base + lane_addr + kColdQ + cq * 16, t16);
       tmem_wait_ld();
       tc_fence_before_sync();
       mbar_arrive(dq_free);                          // the dQ columns may be overwritten
+      if (tid == 0) TL((tt + 1) * 16 + 14);
       if (lane == 0) tma_store_wait_read();          // this warp's previous reduce has read its staging tile
       __syncwarp();
+      if (tid == 0) TL((tt + 1) * 16 + 15);
       uint8_t* stage = sDQ + cw * 2048;
       const uint32_t rowaddr = smem_u32(stage) + lane * 64;
       const uint32_t sw = (lane >> 1) & 3;           // 64-byte swizzle: 16-byte chunk ^= bits 7..8 of the offset
@@ -582,42 +590,51 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
         tma_store_commit();
       }
     };
-    // dK and dV of a finished item: tensor memory -> registers -> global memory (16-bit).  Thread
-    // (row, cq) holds DQ consecutive columns of key row k0 + row.
+    // dK and dV of a finished item: tensor memory -> registers -> this warp's staging tile -> two TMA
+    // stores issued by its lane 0.  Warp (quad, cq) holds key rows [32*quad, +32) x columns [cq*DQ, +DQ)
+    // of both accumulators: 32 rows of DQ*2 bytes each, dV first, dK behind it.  The staging tile is the
+    // warp's dQ staging slot (D = 64) or its 4 KB share of the idle P/dS buffers (D = 128).  Rows past
+    // S_k are clipped by the TMA unit.  The caller orders this against other users of the tile.
+    constexpr int kDkvRowBytes = DQ * 2;
     auto store_dkdv = [&](int item_id, bool from_tmem) {
       const BwdItem it = decode(item_id);
-      const int key = it.k0 + row;
+      uint8_t* stage = OWNSTAGE ? sDQ + cw * 2048 : sP + cw * 4096;
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         const float mul = (which == 0) ? dscale : a.scale * dscale;
-        unsigned short* base = reinterpret_cast<unsigned short*>(which == 0 ? a.dv : a.dk);
-        const int64_t off = (which == 0)
-                                ? it.b * a.dv_sb + it.h * a.dv_sh + static_cast<int64_t>(key) * a.dv_ss
-                                : it.b * a.dk_sb + it.h * a.dk_sh + static_cast<int64_t>(key) * a.dk_ss;
+        const uint32_t rowaddr = smem_u32(stage) + which * 32 * kDkvRowBytes + lane * kDkvRowBytes;
 #pragma unroll
         for (int c = 0; c < DQ / 16; ++c) {
-          const int dcol = cq * DQ + c * 16;               // first of 16 accumulator columns
           uint32_t r[16];
           if (from_tmem) {
-            tmem_ld16(tmem_base + lane_addr + (which == 0 ? kColdV : kColdK) + dcol, r);
+            tmem_ld16(tmem_base + lane_addr + (which == 0 ? kColdV : kColdK) + cq * DQ + c * 16, r);
             tmem_wait_ld();
           } else {
 #pragma unroll
             for (int k = 0; k < 16; ++k) r[k] = 0u;
           }
-          if (key < a.S_k) {
 #pragma unroll
-            for (int q = 0; q < 2; ++q) {
-              uint4 w;
-              w.x = pack2<BF16>(__uint_as_float(r[q * 8 + 0]) * mul, __uint_as_float(r[q * 8 + 1]) * mul);
-              w.y = pack2<BF16>(__uint_as_float(r[q * 8 + 2]) * mul, __uint_as_float(r[q * 8 + 3]) * mul);
-              w.z = pack2<BF16>(__uint_as_float(r[q * 8 + 4]) * mul, __uint_as_float(r[q * 8 + 5]) * mul);
-              w.w = pack2<BF16>(__uint_as_float(r[q * 8 + 6]) * mul, __uint_as_float(r[q * 8 + 7]) * mul);
-              *reinterpret_cast<uint4*>(base + off + dcol + q * 8) = w;
-            }
-          }
+          for (int q = 0; q < 2; ++q)
+            sts128(rowaddr + c * 32 + q * 16,
+                   pack2<BF16>(__uint_as_float(r[q * 8 + 0]) * mul, __uint_as_float(r[q * 8 + 1]) * mul),
+                   pack2<BF16>(__uint_as_float(r[q * 8 + 2]) * mul, __uint_as_float(r[q * 8 + 3]) * mul),
+                   pack2<BF16>(__uint_as_float(r[q * 8 + 4]) * mul, __uint_as_float(r[q * 8 + 5]) * mul),
+                   pack2<BF16>(__uint_as_float(r[q * 8 + 6]) * mul, __uint_as_float(r[q * 8 + 7]) * mul));
         }
       }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0 && *abort_flag == 0) {
+        tma_store_4d(&a.tm_dv, stage, cq * DQ, it.k0 + quad * 32, it.h, it.b);
+        tma_store_4d(&a.tm_dk, stage + 32 * kDkvRowBytes, cq * DQ, it.k0 + quad * 32, it.h, it.b);
+        tma_store_commit();
+      }
+    };
+    // Frees the warp's staging tile for store_dkdv / the next dQ tile (D = 64 only: at D = 128 the
+    // tile lies in the P/dS buffers, whose users are ordered by the CTA-wide barrier 2).
+    auto own_stage_free = [&]() {
+      if (lane == 0) tma_store_wait_read();
+      __syncwarp();
     };
 
     int n = 0, w = 0, t = 0;      // items fetched, items with work, query tiles so far
@@ -629,7 +646,20 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
       const BwdItem cur = fetch_item(n++, kComputeSleepNs);
       if (cur.id < 0) break;
       if (cur.n_cols <= 0) {
-        store_dkdv(cur.id, false);   // key tile wholly past the valid length: its gradients are zero
+        // key tile wholly past the valid length: its gradients are zero
+        if constexpr (OWNSTAGE) {
+          own_stage_free();
+          store_dkdv(cur.id, false);
+        } else {
+          // the P/dS buffers may still be read by the previous tile's MMAs and dQ reduce
+          if (t > 0) {
+            if (tid == 0) tma_store_wait_read();
+            named_bar_sync(2, kComputeThreads);
+          }
+          store_dkdv(cur.id, false);
+          if (lane == 0) tma_store_wait_read();
+          named_bar_sync(2, kComputeThreads);
+        }
         continue;
       }
       const int k0 = cur.k0, n_cols = cur.n_cols, bh = cur.bh;
@@ -751,7 +781,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
           // dK and dV of the previous item: complete since its last dV/dK MMAs, and they must be out
           // of tensor memory before this tile's P and dS let the tensor core overwrite them.
           wait_all(acc_full, (w - 1) & 1, kSiteAccFull);
-          store_dkdv(prev_id, true);
+          if constexpr (OWNSTAGE) {
+            own_stage_free();
+            store_dkdv(prev_id, true);
+          } else {
+            store_dkdv(prev_id, true);
+            if (lane == 0) tma_store_wait_read();   // every warp's slice must be read before P and dS land there
+            named_bar_sync(2, kComputeThreads);
+          }
           tc_fence_before_sync();
           prev_pending = false;
         }
@@ -788,9 +825,15 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
     }
     if (prev_pending) {
       wait_all(acc_full, (w - 1) & 1, kSiteAccFull);
+      if constexpr (OWNSTAGE) {
+        own_stage_free();
+      } else {
+        if (tid == 0) tma_store_wait_read();   // the last dQ reduce has read the P/dS buffers
+        named_bar_sync(2, kComputeThreads);
+      }
       store_dkdv(prev_id, true);
     }
-    if (OWNSTAGE ? (lane == 0) : (tid == 0)) tma_store_wait_read();   // shared memory stays valid until the reduce has read it
+    if (lane == 0) tma_store_wait_read();   // shared memory stays valid until the TMA unit has read it
     if (tid == 0) TL(254);
   }
 

@@ -38,19 +38,23 @@ static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
   return fn;
 }
 
-// Tensor map of a [B,H,S,D] view with a {64 x box_rows x 1 x 1} box and 128-byte swizzle.
-static int make_tmap(CUtensorMap* out, const fmha_tensor4& t, int dtype, int B, int H, int S, int D, int box_rows) {
+// Tensor map of a [B,H,S,D] view.  Default: {64 x box_rows x 1 x 1} boxes with 128-byte swizzle (operand
+// tiles).  box_cols > 0: {box_cols x box_rows x 1 x 1} boxes without swizzle (the per-warp slices in which
+// the backward kernel writes dK and dV).
+static int make_tmap(CUtensorMap* out, const fmha_tensor4& t, int dtype, int B, int H, int S, int D, int box_rows,
+                     int box_cols = 0) {
   auto enc = get_encode_fn();
   if (enc == nullptr) return FMHA_ERR_LAUNCH;
   const cuuint64_t dims[4] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(H),
                               static_cast<cuuint64_t>(B)};
   const cuuint64_t strides[3] = {static_cast<cuuint64_t>(t.stride_s) * 2, static_cast<cuuint64_t>(t.stride_h) * 2,
                                  static_cast<cuuint64_t>(t.stride_b) * 2};
-  const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), 1, 1};
+  const cuuint32_t box[4] = {box_cols > 0 ? static_cast<cuuint32_t>(box_cols) : 64u, static_cast<cuuint32_t>(box_rows), 1, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   const CUtensorMapDataType dt = (dtype == FMHA_DTYPE_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUresult r = enc(out, dt, 4, t.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                   box_cols > 0 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     g_last_cuda_error = static_cast<int>(r);
     return FMHA_ERR_LAUNCH;
@@ -266,8 +270,9 @@ int fmha_sm100_bwd(const fmha_bwd_params* p, void* stream_) {
   if ((rc = make_tmap(&a.tm_k, tk, p->dtype, p->B, p->H, p->S_k, p->D, kTileN))) return rc;
   if ((rc = make_tmap(&a.tm_v, tv, p->dtype, p->B, p->H, p->S_k, p->D, kTileN))) return rc;
   if ((rc = make_tmap(&a.tm_do, tdo, p->dtype, p->B, p->H, p->S_q, p->D, kTileM))) return rc;
-  a.dk = tdk.ptr; a.dk_sb = tdk.stride_b; a.dk_sh = tdk.stride_h; a.dk_ss = tdk.stride_s;
-  a.dv = tdv.ptr; a.dv_sb = tdv.stride_b; a.dv_sh = tdv.stride_h; a.dv_ss = tdv.stride_s;
+  // dK and dV leave in per-warp slices of 32 key rows x D/4 columns
+  if ((rc = make_tmap(&a.tm_dk, tdk, p->dtype, p->B, p->H, p->S_k, p->D, 32, p->D / 4))) return rc;
+  if ((rc = make_tmap(&a.tm_dv, tdv, p->dtype, p->B, p->H, p->S_k, p->D, 32, p->D / 4))) return rc;
   a.work_counter = work_counter;
   if ((rc = make_tmap_accum(&a.tm_dq, dq_accum, static_cast<uint64_t>(bh) * s_q_pad, p->D))) return rc;
   a.B = p->B; a.H = p->H; a.S_q = p->S_q; a.S_k = p->S_k;

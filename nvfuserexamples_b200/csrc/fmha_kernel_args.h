@@ -46,6 +46,8 @@ struct BwdArgs {
   alignas(64) CUtensorMap tm_k;
   alignas(64) CUtensorMap tm_v;
   alignas(64) CUtensorMap tm_do;
+  alignas(64) CUtensorMap tm_dk;  // 16-bit outputs, {D/4 x 32} boxes (one per compute warp), no swizzle
+  alignas(64) CUtensorMap tm_dv;
   alignas(64) CUtensorMap tm_dq;  // fp32 dQ accumulator as [B*H*S_q_pad, D], 32-column boxes (TMA reduce-add)
   int B, H, S_q, S_k;
   float scale;       // softmax scale
@@ -54,9 +56,6 @@ struct BwdArgs {
   const float* delta;  // [B*H, S_q] rowsum(dO * O)
   float* dq_accum;     // [B*H, S_q_pad, D] fp32, zero on entry
   int* work_counter;   // zero on entry; the persistent CTAs draw their work items from it
-  void* dk;            // 16-bit outputs, written from registers: element strides of b, h, s
-  void* dv;
-  int64_t dk_sb, dk_sh, dk_ss, dv_sb, dv_sh, dv_ss;
   int S_q_pad;         // S_q rounded up to the tile
   int mask_kind;
   const void* mask;
