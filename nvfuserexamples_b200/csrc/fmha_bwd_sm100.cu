@@ -638,8 +638,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
     };
 
     int n = 0, w = 0, t = 0;      // items fetched, items with work, query tiles so far
-    bool prev_pending = false;    // dK/dV of item `prev` are still in tensor memory
-    int prev_id = -1;
+    int prev_id = -1;             // >= 0: dK/dV of that item are still in tensor memory
     int prev_row0 = 0;            // accumulator row of the tile whose dQ is still in tensor memory (D = 64)
 
     while (true) {
@@ -701,41 +700,40 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
           }
         }
 
+        // keep decisions of the 32 columns: two Philox draws, computed together (their rounds
+        // interleave) and before S and dP are needed
+        [[maybe_unused]] uint32_t kw8[8];
+        if constexpr (DROP) {
+#pragma unroll
+          for (int d = 0; d < 2; ++d) {
+            const U4 draw = dropout_draw_keys(a.philox_keys, a.philox_offset, gbh, static_cast<uint32_t>(q_row),
+                                         static_cast<uint32_t>((k0 + cbase) / 16 + d));
+            kw8[d * 4 + 0] = (draw.x & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
+            kw8[d * 4 + 1] = (draw.y & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
+            kw8[d * 4 + 2] = (draw.z & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
+            kw8[d * 4 + 3] = (draw.w & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
+          }
+        }
         if (tid == 0) TL(t * 16 + 8);
         wait_all(sdp_full, t & 1, kSiteSdpFull);
         if (tid == 0) TL(t * 16 + 9);
-        uint32_t rs[32], rp[32];
-        tmem_ld32(tmem_base + lane_addr + kColS + cbase, rs);
-        tmem_ld32(tmem_base + lane_addr + kColdP + cbase, rp);
-        tmem_wait_ld_dep(rs);
-        tmem_wait_ld_dep(rp);
-        tc_fence_before_sync();
-        mbar_arrive(sdp_free);   // the tensor core may overwrite S and dP now
-        if (tid == 0) TL(t * 16 + 10);
-
+        // The 32 columns are processed as two halves of 16: the second half of S and dP is fetched
+        // from tensor memory only after the first has been turned into packed P and dS, which keeps
+        // 32 fewer values live (the kernel is bound by the ALU pipe, and with all 64 values in
+        // registers the compiler spilled and shuffled registers in this loop).
         uint32_t pk_p[16], pk_ds[16];  // 32 columns: 16 packed pairs each
-        auto chunk = [&](auto edge_tag) {
+        auto half_chunk = [&](auto edge_tag, auto half_tag, const uint32_t (&rs)[16], const uint32_t (&rp)[16]) {
           constexpr bool EDGE = decltype(edge_tag)::value;
+          constexpr int HALF = decltype(half_tag)::value;
           const float2 sl22 = make_float2(sl2, sl2);
           const float2 nl2 = make_float2(neg_lse2, neg_lse2);
           const float2 nd2 = make_float2(-delta, -delta);
-          [[maybe_unused]] uint32_t kw8[8];
-          if constexpr (DROP) {
 #pragma unroll
-            for (int d = 0; d < 2; ++d) {
-              const U4 draw = dropout_draw_keys(a.philox_keys, a.philox_offset, gbh, static_cast<uint32_t>(q_row),
-                                           static_cast<uint32_t>((k0 + cbase) / 16 + d));
-              kw8[d * 4 + 0] = (draw.x & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
-              kw8[d * 4 + 1] = (draw.y & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
-              kw8[d * 4 + 2] = (draw.z & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
-              kw8[d * 4 + 3] = (draw.w & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
-            }
-          }
-#pragma unroll
-          for (int k = 0; k < 16; ++k) {
+          for (int k = 0; k < 8; ++k) {
+            const int col = cbase + HALF * 16 + 2 * k;       // column of the pair within the tile
             float2 x = make_float2(__uint_as_float(rs[2 * k]), __uint_as_float(rs[2 * k + 1]));
             if constexpr (KEYADD) {
-              const float2 mk = *reinterpret_cast<const float2*>(mask_row + cbase + 2 * k);
+              const float2 mk = *reinterpret_cast<const float2*>(mask_row + col);
               x = __fadd2_rn(__ffma2_rn(x, sl22, mk), nl2);
             } else {
               x = __ffma2_rn(x, sl22, nl2);
@@ -744,26 +742,43 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
             p.x = fast_exp2(x.x);
             p.y = fast_exp2(x.y);
             if constexpr (EDGE) {                            // keys past the valid length / tensor edge
-              if (cbase + 2 * k >= n_cols) p.x = 0.f;
-              if (cbase + 2 * k + 1 >= n_cols) p.y = 0.f;
+              if (col >= n_cols) p.x = 0.f;
+              if (col + 1 >= n_cols) p.y = 0.f;
             }
             const float2 dp = make_float2(__uint_as_float(rp[2 * k]), __uint_as_float(rp[2 * k + 1]));
             float2 pkeep = p;
             if constexpr (DROP) {
               // bit 7 of byte e of the keep word decides element e; the permute smears it over 32 bits
-              const uint32_t kw = kw8[k >> 1];
+              const uint32_t kw = kw8[HALF * 4 + (k >> 1)];
               const uint32_t m0 = prmt(kw, 0u, (k & 1) ? 0xAAAAu : 0x8888u);
               const uint32_t m1 = prmt(kw, 0u, (k & 1) ? 0xBBBBu : 0x9999u);
               pkeep.x = __uint_as_float(__float_as_uint(p.x) & m0);
               pkeep.y = __uint_as_float(__float_as_uint(p.y) & m1);
             }
             const float2 ds = __ffma2_rn(pkeep, dp, __fmul2_rn(p, nd2));
-            pk_p[k] = pack2<BF16>(pkeep.x, pkeep.y);
-            pk_ds[k] = pack2<BF16>(ds.x, ds.y);
+            pk_p[HALF * 8 + k] = pack2<BF16>(pkeep.x, pkeep.y);
+            pk_ds[HALF * 8 + k] = pack2<BF16>(ds.x, ds.y);
           }
         };
-        if (n_cols >= kTileN) chunk(std::false_type{});
-        else chunk(std::true_type{});
+        {
+          uint32_t rs[16], rp[16];
+          tmem_ld16(tmem_base + lane_addr + kColS + cbase, rs);
+          tmem_ld16(tmem_base + lane_addr + kColdP + cbase, rp);
+          tmem_wait_ld_dep16(rs, rp);
+          if (n_cols >= kTileN) half_chunk(std::false_type{}, std::integral_constant<int, 0>{}, rs, rp);
+          else half_chunk(std::true_type{}, std::integral_constant<int, 0>{}, rs, rp);
+        }
+        {
+          uint32_t rs[16], rp[16];
+          tmem_ld16(tmem_base + lane_addr + kColS + cbase + 16, rs);
+          tmem_ld16(tmem_base + lane_addr + kColdP + cbase + 16, rp);
+          tmem_wait_ld_dep16(rs, rp);
+          tc_fence_before_sync();
+          mbar_arrive(sdp_free);   // the tensor core may overwrite S and dP now
+          if (tid == 0) TL(t * 16 + 10);
+          if (n_cols >= kTileN) half_chunk(std::false_type{}, std::integral_constant<int, 1>{}, rs, rp);
+          else half_chunk(std::true_type{}, std::integral_constant<int, 1>{}, rs, rp);
+        }
 
         if (tid == 0) TL(t * 16 + 11);
         if constexpr (EARLY) {
@@ -777,7 +792,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
             named_bar_sync(2, kComputeThreads);
           }
         }
-        if (i == 0 && prev_pending) {
+        if (i == 0 && prev_id >= 0) {
           // dK and dV of the previous item: complete since its last dV/dK MMAs, and they must be out
           // of tensor memory before this tile's P and dS let the tensor core overwrite them.
           wait_all(acc_full, (w - 1) & 1, kSiteAccFull);
@@ -790,7 +805,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
             named_bar_sync(2, kComputeThreads);
           }
           tc_fence_before_sync();
-          prev_pending = false;
+          prev_id = -1;
         }
         {
           // columns [32*cq, +32) of row `row`: 64 bytes = 16-byte chunks (cq%2)*4 .. +3 of sub-tile cq/2
@@ -816,14 +831,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
         if (tid == 0) TL(t * 16 + 13);
       }
       prev_id = cur.id;
-      prev_pending = true;
       ++w;
     }
     // ---- drain: the last tile's dQ and the last item's dK, dV ------------------------------
     if constexpr (EARLY) {
       if (t > 0) dq_readout_warp(t - 1, prev_row0);
     }
-    if (prev_pending) {
+    if (prev_id >= 0) {
       wait_all(acc_full, (w - 1) & 1, kSiteAccFull);
       if constexpr (OWNSTAGE) {
         own_stage_free();
