@@ -66,7 +66,7 @@ struct FastSmem {
 template <bool BF16, bool KEYADD, bool DROP, bool BOUNDARY>
 __device__ __forceinline__ void softmax_chunk(const uint32_t (&r)[32], int cbase, int n_cols, float sl2, float neg_m,
                                               const float* mask_stage, float2& sum2, uint32_t (&packed)[16],
-                                              const FwdArgs& a, uint32_t gbh, uint32_t q_row, uint32_t kb0) {
+                                              const uint32_t* keepw) {
   const float2 sl22 = make_float2(sl2, sl2);
   const float2 negm2 = make_float2(neg_m, neg_m);
 #pragma unroll
@@ -89,17 +89,11 @@ __device__ __forceinline__ void softmax_chunk(const uint32_t (&r)[32], int cbase
     packed[k] = pack2<BF16>(p.x, p.y);
   }
   if constexpr (DROP) {
+    // keepw[i]: bit 7 of byte e = keep decision of column cbase + 4*i + e; the permutes replicate it over a 16-bit lane
 #pragma unroll
-    for (int d = 0; d < 2; ++d) {
-      const U4 draw = dropout_draw_keys(a.philox_keys, a.philox_offset, gbh, q_row, kb0 + d);
-      const uint32_t w[4] = {draw.x, draw.y, draw.z, draw.w};
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        // bit 7 of every byte = keep decision; the permutes replicate it over a 16-bit lane
-        const uint32_t keep = (w[k] & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
-        packed[d * 8 + 2 * k] &= prmt(keep, 0u, 0x9988u);
-        packed[d * 8 + 2 * k + 1] &= prmt(keep, 0u, 0xBBAAu);
-      }
+    for (int i = 0; i < 8; ++i) {
+      packed[2 * i] &= prmt(keepw[i], 0u, 0x9988u);
+      packed[2 * i + 1] &= prmt(keepw[i], 0u, 0xBBAAu);
     }
   }
 }
@@ -271,6 +265,20 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
               (c < a.S_k) ? reinterpret_cast<const float*>(a.mask)[static_cast<size_t>(b) * a.S_k + c] * kLog2eF : 0.f;
         named_bar_sync(1, 128);
       }
+      // Keep decisions of this step's TN columns: Philox does not depend on the scores, so it runs
+      // before they are awaited, while the tensor core is still busy with Q K^T.
+      [[maybe_unused]] uint32_t keepw[DROP ? TN / 4 : 1];
+      if constexpr (DROP) {
+        const uint32_t kb0 = static_cast<uint32_t>(col0 / 16);
+#pragma unroll
+        for (int d = 0; d < TN / 16; ++d) {
+          const U4 draw = dropout_draw_keys(a.philox_keys, a.philox_offset, gbh, static_cast<uint32_t>(q_row), kb0 + d);
+          keepw[d * 4 + 0] = (draw.x & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
+          keepw[d * 4 + 1] = (draw.y & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
+          keepw[d * 4 + 2] = (draw.z & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
+          keepw[d * 4 + 3] = (draw.w & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
+        }
+      }
       mbar_wait(s_full, j & 1, wctx, kFSFull, 32);
       tc_fence_after_sync();
 
@@ -333,16 +341,13 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
       // ---- sweep 2: exponentials, dropout, P (next chunk's load in flight) ----------------------
       {
         const float neg_m = -m_ref;
-        const uint32_t kb0 = static_cast<uint32_t>(col0 / 16);
         uint32_t ra[32], rb[32], packed[16];
         tmem_ld32(tS + 0, ra);
         auto run = [&](const uint32_t (&r)[32], int c) {
           if (n_cols >= TN)
-            softmax_chunk<BF16, KEYADD, DROP, false>(r, c * 32, n_cols, sl2, neg_m, mask_stage, sum2, packed, a, gbh,
-                                                     static_cast<uint32_t>(q_row), kb0 + 2 * c);
+            softmax_chunk<BF16, KEYADD, DROP, false>(r, c * 32, n_cols, sl2, neg_m, mask_stage, sum2, packed, keepw + (DROP ? c * 8 : 0));
           else
-            softmax_chunk<BF16, KEYADD, DROP, true>(r, c * 32, n_cols, sl2, neg_m, mask_stage, sum2, packed, a, gbh,
-                                                    static_cast<uint32_t>(q_row), kb0 + 2 * c);
+            softmax_chunk<BF16, KEYADD, DROP, true>(r, c * 32, n_cols, sl2, neg_m, mask_stage, sum2, packed, keepw + (DROP ? c * 8 : 0));
           tmem_st16(tS + c * 16, packed);
         };
 #pragma unroll
