@@ -40,7 +40,8 @@ enum {
   FMHA_ERR_LAUNCH = 3,         /* CUDA runtime / driver call failed (see fmha_sm100_last_cuda_error) */
   FMHA_ERR_DEVICE_TIMEOUT = 4, /* a bounded in-kernel wait ran out (read back by fmha_sm100_check_status) */
   FMHA_ERR_NO_DEVICE = 5,      /* no sm_100 device is current                               */
-  FMHA_ERR_TOO_LARGE = 6       /* size exceeds a documented maximum                         */
+  FMHA_ERR_TOO_LARGE = 6       /* size exceeds a documented maximum: B, H <= 65535, B*H < 2^31,
+                                  S_q, S_k <= 2^20 (or the static scratch, where that is used)  */
 };
 
 /* ---- enums ---------------------------------------------------------------------- */

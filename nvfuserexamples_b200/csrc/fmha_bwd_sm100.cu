@@ -94,23 +94,22 @@ struct PrepArgs {
 
 template <bool BF16>
 __global__ void __launch_bounds__(256) bwd_prepare_kernel(const PrepArgs a) {
-  // 8 threads per row (D = 64: 8 elements each; D = 128: 16 elements each)
+  // grid = (B*H, blocks of 32 rows); 8 threads per row (D = 64: 8 elements each; D = 128: 16 each).
+  // The head index comes from the grid, so no thread divides 64-bit indices.
   const int per = a.D / 8;
-  const int64_t row_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 3;
   const int part = threadIdx.x & 7;
-  const int64_t n_rows = static_cast<int64_t>(a.B) * a.H * a.S_q_pad;
-  const bool in_range = row_global < n_rows;  // no early exit: the shuffles below need every lane
-  if (blockIdx.x == 0 && threadIdx.x == 0 && a.work_counter != nullptr) *a.work_counter = 0;
-  const int r = in_range ? static_cast<int>(row_global % a.S_q_pad) : a.S_q_pad;
-  const int64_t bh = row_global / a.S_q_pad;
-  const int h = static_cast<int>(bh % a.H);
-  const int b = static_cast<int>(bh / a.H);
+  const int bh = blockIdx.x;
+  const int h = bh % a.H;
+  const int b = bh / a.H;
+  const int r = blockIdx.y * 32 + (threadIdx.x >> 3);
+  const bool in_range = r < a.S_q_pad;  // no early exit: the shuffles below need every lane
+  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && a.work_counter != nullptr) *a.work_counter = 0;
   if (in_range) {
-    float4* acc = reinterpret_cast<float4*>(a.dq_accum + row_global * a.D + part * per);
+    float4* acc = reinterpret_cast<float4*>(a.dq_accum + (static_cast<int64_t>(bh) * a.S_q_pad + r) * a.D + part * per);
     for (int i = 0; i < per / 4; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
   float sum = 0.f;
-  if (r < a.S_q) {
+  if (in_range && r < a.S_q) {
     const unsigned short* po = reinterpret_cast<const unsigned short*>(a.o) + b * a.o_sb + h * a.o_sh + r * a.o_ss + part * per;
     const unsigned short* pd = reinterpret_cast<const unsigned short*>(a.d_o) + b * a.do_sb + h * a.do_sh + r * a.do_ss + part * per;
     for (int i = 0; i < per / 8; ++i) {
@@ -128,7 +127,7 @@ __global__ void __launch_bounds__(256) bwd_prepare_kernel(const PrepArgs a) {
   sum += __shfl_xor_sync(0xffffffffu, sum, 1);
   sum += __shfl_xor_sync(0xffffffffu, sum, 2);
   sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-  if (part == 0 && r < a.S_q) a.delta[bh * a.S_q + r] = sum;
+  if (part == 0 && in_range && r < a.S_q) a.delta[static_cast<int64_t>(bh) * a.S_q + r] = sum;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -144,18 +143,15 @@ struct FinishArgs {
 
 template <bool BF16>
 __global__ void __launch_bounds__(256) bwd_finish_kernel(const FinishArgs a) {
-  // one thread converts 8 consecutive elements
+  // grid = (B*H, row blocks); one thread converts 8 consecutive elements, D/8 threads per row
   const int per_row = a.D / 8;
-  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const int64_t total = static_cast<int64_t>(a.B) * a.H * a.S_q * per_row;
-  if (idx >= total) return;
-  const int part = static_cast<int>(idx % per_row);
-  const int64_t row = idx / per_row;
-  const int r = static_cast<int>(row % a.S_q);
-  const int64_t bh = row / a.S_q;
-  const int h = static_cast<int>(bh % a.H);
-  const int b = static_cast<int>(bh / a.H);
-  const float4* src = reinterpret_cast<const float4*>(a.dq_accum + (bh * a.S_q_pad + r) * a.D + part * 8);
+  const int part = threadIdx.x % per_row;
+  const int r = blockIdx.y * (256 / per_row) + threadIdx.x / per_row;
+  if (r >= a.S_q) return;
+  const int bh = blockIdx.x;
+  const int h = bh % a.H;
+  const int b = bh / a.H;
+  const float4* src = reinterpret_cast<const float4*>(a.dq_accum + (static_cast<int64_t>(bh) * a.S_q_pad + r) * a.D + part * 8);
   const float4 x = src[0], y = src[1];
   uint4 w;
   w.x = pack2<BF16>(x.x * a.scale, x.y * a.scale);
@@ -929,11 +925,9 @@ int launch_bwd_prepare(const void* o, const fmha_tensor4& ot, const fmha_tensor4
   p.do_sb = dot.stride_b; p.do_sh = dot.stride_h; p.do_ss = dot.stride_s;
   p.B = B; p.H = H; p.S_q = S_q; p.S_q_pad = S_q_pad; p.D = D;
   p.delta = delta; p.dq_accum = dq_accum; p.work_counter = work_counter;
-  const int64_t threads = static_cast<int64_t>(B) * H * S_q_pad * 8;
-  const int block = 256;
-  const int64_t blocks = (threads + block - 1) / block;
-  if (dtype == FMHA_DTYPE_BF16) bwd_prepare_kernel<true><<<static_cast<unsigned>(blocks), block, 0, stream>>>(p);
-  else bwd_prepare_kernel<false><<<static_cast<unsigned>(blocks), block, 0, stream>>>(p);
+  const dim3 grid(static_cast<unsigned>(B) * H, static_cast<unsigned>((S_q_pad + 31) / 32));
+  if (dtype == FMHA_DTYPE_BF16) bwd_prepare_kernel<true><<<grid, 256, 0, stream>>>(p);
+  else bwd_prepare_kernel<false><<<grid, 256, 0, stream>>>(p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -943,11 +937,10 @@ int launch_bwd_finish(const float* dq_accum, const fmha_tensor4& dq, int B, int 
   f.dq_accum = dq_accum; f.dq = dq.ptr;
   f.sb = dq.stride_b; f.sh = dq.stride_h; f.ss = dq.stride_s;
   f.B = B; f.H = H; f.S_q = S_q; f.S_q_pad = S_q_pad; f.D = D; f.scale = scale;
-  const int64_t threads = static_cast<int64_t>(B) * H * S_q * (D / 8);
-  const int block = 256;
-  const int64_t blocks = (threads + block - 1) / block;
-  if (dtype == FMHA_DTYPE_BF16) bwd_finish_kernel<true><<<static_cast<unsigned>(blocks), block, 0, stream>>>(f);
-  else bwd_finish_kernel<false><<<static_cast<unsigned>(blocks), block, 0, stream>>>(f);
+  const int rows_per_block = 256 / (D / 8);
+  const dim3 grid(static_cast<unsigned>(B) * H, static_cast<unsigned>((S_q + rows_per_block - 1) / rows_per_block));
+  if (dtype == FMHA_DTYPE_BF16) bwd_finish_kernel<true><<<grid, 256, 0, stream>>>(f);
+  else bwd_finish_kernel<false><<<grid, 256, 0, stream>>>(f);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -122,6 +122,8 @@ static int validate_common(int struct_bytes, size_t expect, int dtype, int B, in
   if (D != 64 && D != 128) return FMHA_ERR_UNSUPPORTED;
   if (B < 0 || H < 0 || S_q < 0 || S_k < 0) return FMHA_ERR_BAD_ARG;
   if (B > 65535 || H > 65535) return FMHA_ERR_TOO_LARGE;
+  // grids: B*H heads along x (< 2^31), blocks of query / key rows along y (<= 65535 blocks of >= 16 rows)
+  if (static_cast<int64_t>(B) * H > 0x7fffffffll || S_q > (1 << 20) || S_k > (1 << 20)) return FMHA_ERR_TOO_LARGE;
   if (!(scale > 0.f) || !std::isfinite(scale)) return FMHA_ERR_BAD_ARG;
   return FMHA_OK;
 }
