@@ -336,7 +336,14 @@ class FmhaFunction : public torch::autograd::Function<FmhaFunction> {
                             const c10::optional<at::Tensor>& seqlens, double p_drop, int64_t seed, int64_t offset,
                             c10::optional<double> scale) {
     at::AutoDispatchBelowADInplaceOrView guard;
-    auto [o, lse] = fmha_fwd(q, k, v, mask, seqlens, p_drop, seed, offset, scale, 0);
+    // through the dispatcher, so that fake / meta tensors reach the shape-only kernels
+    static auto op = c10::Dispatcher::singleton()
+                         .findSchemaOrThrow("mha_manual::fmha_fwd", "")
+                         .typed<std::tuple<at::Tensor, at::Tensor>(const at::Tensor&, const at::Tensor&, const at::Tensor&,
+                                                                   const c10::optional<at::Tensor>&,
+                                                                   const c10::optional<at::Tensor>&, double, int64_t, int64_t,
+                                                                   c10::optional<double>, int64_t)>();
+    auto [o, lse] = op.call(q, k, v, mask, seqlens, p_drop, seed, offset, scale, 0);
     ctx->save_for_backward({q, k, v, o, lse, mask.has_value() ? *mask : at::Tensor(),
                             seqlens.has_value() ? *seqlens : at::Tensor()});
     ctx->saved_data["p_drop"] = p_drop;
@@ -354,9 +361,16 @@ class FmhaFunction : public torch::autograd::Function<FmhaFunction> {
     if (saved[6].defined()) seqlens = saved[6];
     c10::optional<double> scale;
     if (ctx->saved_data["has_scale"].toBool()) scale = ctx->saved_data["scale"].toDouble();
-    auto [dq, dk, dv] = fmha_bwd(grads[0], saved[0], saved[1], saved[2], saved[3], saved[4], mask, seqlens,
-                                 ctx->saved_data["p_drop"].toDouble(), ctx->saved_data["seed"].toInt(),
-                                 ctx->saved_data["offset"].toInt(), scale, 0);
+    static auto op =
+        c10::Dispatcher::singleton()
+            .findSchemaOrThrow("mha_manual::fmha_bwd", "")
+            .typed<std::tuple<at::Tensor, at::Tensor, at::Tensor>(
+                const at::Tensor&, const at::Tensor&, const at::Tensor&, const at::Tensor&, const at::Tensor&, const at::Tensor&,
+                const c10::optional<at::Tensor>&, const c10::optional<at::Tensor>&, double, int64_t, int64_t,
+                c10::optional<double>, int64_t)>();
+    auto [dq, dk, dv] = op.call(grads[0], saved[0], saved[1], saved[2], saved[3], saved[4], mask, seqlens,
+                                ctx->saved_data["p_drop"].toDouble(), ctx->saved_data["seed"].toInt(),
+                                ctx->saved_data["offset"].toInt(), scale, 0);
     return {dq, dk, dv, at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor()};
   }
 };
@@ -365,6 +379,79 @@ at::Tensor fmha_autograd(const at::Tensor& q, const at::Tensor& k, const at::Ten
                          const c10::optional<at::Tensor>& mask, const c10::optional<at::Tensor>& seqlens, double p_drop,
                          int64_t seed, int64_t offset, c10::optional<double> scale) {
   return FmhaFunction::apply(q, k, v, mask, seqlens, p_drop, seed, offset, scale);
+}
+
+// ---------------------------------------------------------------------------------------
+// shape-only kernels (Meta key): what fake-tensor tracing and torch.compile need.  They check the
+// same shape rules as the CUDA kernels' wrappers and allocate outputs of the same shapes.
+// ---------------------------------------------------------------------------------------
+struct MetaDims {
+  int64_t B, H, S, D;
+};
+MetaDims meta_dims(const at::Tensor& t, const char* name) {
+  TORCH_CHECK(t.dim() == 3 || t.dim() == 4, "mha_manual: ", name, " must be [B*H,S,D] or [B,H,S,D]");
+  if (t.dim() == 3) return {t.size(0), 1, t.size(1), t.size(2)};
+  return {t.size(0), t.size(1), t.size(2), t.size(3)};
+}
+void meta_check_qkv(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v) {
+  const MetaDims dq = meta_dims(q, "q"), dk = meta_dims(k, "k"), dv = meta_dims(v, "v");
+  TORCH_CHECK(q.scalar_type() == at::kHalf || q.scalar_type() == at::kBFloat16, "mha_manual: q must be float16 or bfloat16");
+  TORCH_CHECK(k.scalar_type() == q.scalar_type() && v.scalar_type() == q.scalar_type(), "mha_manual: q, k, v dtypes differ");
+  TORCH_CHECK(dq.D == 64 || dq.D == 128, "mha_manual: head dimension must be 64 or 128, got ", dq.D);
+  TORCH_CHECK(dk.D == dq.D && dv.D == dq.D, "mha_manual: q, k, v head dimensions differ");
+  TORCH_CHECK(dk.B == dq.B && dv.B == dq.B && dk.H == dq.H && dv.H == dq.H, "mha_manual: q, k, v batch/head sizes differ");
+  TORCH_CHECK(dk.S == dv.S, "mha_manual: k and v sequence lengths differ");
+}
+std::vector<at::Tensor> legacy_meta(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& mask,
+                                    const at::Tensor* dropout_mask, bool save) {
+  meta_check_qkv(q, k, v);
+  const MetaDims dq = meta_dims(q, "q"), dk = meta_dims(k, "k");
+  const int64_t bh = dq.B * dq.H;
+  TORCH_CHECK(mask.numel() == bh * dq.S * dk.S, "mha_manual: mask must have B*H*S_q*S_k elements");
+  if (dropout_mask) TORCH_CHECK(dropout_mask->numel() == bh * dq.S * dk.S, "mha_manual: dropout_mask must have B*H*S_q*S_k elements");
+  std::vector<at::Tensor> outs{at::empty(q.sizes(), q.options())};
+  if (save) {
+    outs.push_back(at::empty({bh, dq.S, dk.S}, q.options()));
+    outs.push_back(at::empty({bh, dq.S, dk.S}, q.options()));
+  }
+  return outs;
+}
+at::Tensor fmha_nvfuser_meta(const at::Tensor& input, const at::Tensor& qk, const at::Tensor& v, const at::Tensor& amask) {
+  return legacy_meta(input, qk, v, amask, nullptr, false)[0];
+}
+at::Tensor fmha_train_nvfuser_meta(const at::Tensor& input, const at::Tensor& qk, const at::Tensor& v,
+                                   const at::Tensor& pad_mask, const at::Tensor& dropout_mask) {
+  return legacy_meta(input, qk, v, pad_mask, &dropout_mask, false)[0];
+}
+std::vector<at::Tensor> fmha_train_saveim_nvfuser_meta(const at::Tensor& input, const at::Tensor& qk, const at::Tensor& v,
+                                                       const at::Tensor& pad_mask, const at::Tensor& dropout_mask) {
+  return legacy_meta(input, qk, v, pad_mask, &dropout_mask, true);
+}
+std::tuple<at::Tensor, at::Tensor> fmha_fwd_meta(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                                                 const c10::optional<at::Tensor>& mask,
+                                                 const c10::optional<at::Tensor>& seqlens, double p_drop, int64_t, int64_t offset,
+                                                 c10::optional<double>, int64_t) {
+  meta_check_qkv(q, k, v);
+  const MetaDims dq = meta_dims(q, "q"), dk = meta_dims(k, "k");
+  TORCH_CHECK(!(mask.has_value() && seqlens.has_value()), "mha_manual: pass either mask or seqlens, not both");
+  if (mask.has_value()) TORCH_CHECK(mask->numel() == dq.B * dk.S, "mha_manual: mask must hold B*S_k additive values");
+  if (seqlens.has_value()) TORCH_CHECK(seqlens->numel() == dq.B, "mha_manual: seqlens must be [B]");
+  TORCH_CHECK(p_drop >= 0.0 && p_drop < 1.0, "mha_manual: p_drop must be in [0, 1)");
+  TORCH_CHECK(offset >= 0 && offset < (int64_t(1) << 32), "mha_manual: offset must be in [0, 2^32)");
+  std::vector<int64_t> lse_shape{dq.B, dq.S};
+  if (q.dim() == 4) lse_shape = {dq.B, dq.H, dq.S};
+  return {at::empty(q.sizes(), q.options()), at::empty(lse_shape, q.options().dtype(at::kFloat))};
+}
+std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_bwd_meta(const at::Tensor& d_o, const at::Tensor& q, const at::Tensor& k,
+                                                             const at::Tensor& v, const at::Tensor& o, const at::Tensor& lse,
+                                                             const c10::optional<at::Tensor>&, const c10::optional<at::Tensor>&,
+                                                             double, int64_t, int64_t, c10::optional<double>, int64_t) {
+  meta_check_qkv(q, k, v);
+  const MetaDims dq = meta_dims(q, "q");
+  TORCH_CHECK(o.sizes() == q.sizes(), "mha_manual: o must have the shape of q");
+  TORCH_CHECK(d_o.sizes() == q.sizes(), "mha_manual: d_o must have the shape of q");
+  TORCH_CHECK(lse.scalar_type() == at::kFloat && lse.numel() == dq.B * dq.H * dq.S, "mha_manual: lse must be float32 [B,H,S_q]");
+  return {at::empty(q.sizes(), q.options()), at::empty(k.sizes(), k.options()), at::empty(v.sizes(), v.options())};
 }
 
 }  // namespace
@@ -391,6 +478,14 @@ TORCH_LIBRARY_IMPL(mha_manual, CUDA, m) {
   m.impl("fmha_train_saveim_nvfuser", fmha_train_saveim_nvfuser);
   m.impl("fmha_fwd", fmha_fwd);
   m.impl("fmha_bwd", fmha_bwd);
+}
+
+TORCH_LIBRARY_IMPL(mha_manual, Meta, m) {
+  m.impl("fmha_nvfuser", fmha_nvfuser_meta);
+  m.impl("fmha_train_nvfuser", fmha_train_nvfuser_meta);
+  m.impl("fmha_train_saveim_nvfuser", fmha_train_saveim_nvfuser_meta);
+  m.impl("fmha_fwd", fmha_fwd_meta);
+  m.impl("fmha_bwd", fmha_bwd_meta);
 }
 
 TORCH_LIBRARY_IMPL(mha_manual, Autograd, m) { m.impl("fmha", fmha_autograd); }

@@ -103,6 +103,32 @@ def test_autograd_operator(ops, cuda_device):
     helpers.assert_close(v.grad, rdv, "dv")
 
 
+def test_operators_can_be_captured_in_a_cuda_graph(ops, cuda_device):
+    """Forward and backward replayed from a CUDA graph give what the eager calls gave.  The Philox
+    offset is a launch parameter, so a captured graph replays the same dropout pattern."""
+    B, H, S, D = 4, 4, 384, 64
+    q, k, v, d_o, lens = helpers.randn_like_config(B, H, S, S, D, torch.float16, seed=8, device=cuda_device)
+    args = (None, lens, 0.1, 11, 3)
+    o0, lse0 = ops.fmha_fwd(q, k, v, *args)                      # warm-up: one-time set-up happens outside the capture
+    dq0, dk0, dv0 = ops.fmha_bwd(d_o, q, k, v, o0, lse0, *args)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream(device=cuda_device)
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            o1, lse1 = ops.fmha_fwd(q, k, v, *args)
+            dq1, dk1, dv1 = ops.fmha_bwd(d_o, q, k, v, o1, lse1, *args)
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(o1, o0) and torch.equal(lse1, lse0)
+    assert torch.equal(dk1, dk0) and torch.equal(dv1, dv0)
+    helpers.assert_close(dq1, dq0.float(), "dq replayed")        # summed by atomics: equal up to the order of additions
+    ops.check_status()
+
+
 def test_operator_errors(ops, cuda_device):
     x = torch.zeros(2, 128, 64, dtype=torch.half, device=cuda_device)
     with pytest.raises(RuntimeError):

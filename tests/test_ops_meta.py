@@ -1,0 +1,60 @@
+"""Shape-only (Meta) kernels of the torch operators: what fake-tensor tracing needs.  Runs without a GPU.
+
+The reference registers its three operators for the CUDA key only (fmha/fmha_manual.cpp:1240-1250 of
+shmsong/NvFuserExamples) and has no backward; the Meta kernels and the autograd operator are additions."""
+import pytest
+import torch
+
+
+@pytest.fixture(scope="module")
+def ops():
+    import mha_manual  # noqa: F401  (registers torch.ops.mha_manual)
+    return torch.ops.mha_manual
+
+
+def meta(*shape, dtype=torch.float16):
+    return torch.empty(*shape, dtype=dtype, device="meta")
+
+
+def test_legacy_ops_infer_shapes(ops):
+    q, k, v = meta(512, 128, 64), meta(512, 128, 64), meta(512, 128, 64)
+    m = meta(512, 128, 128)
+    assert ops.fmha_nvfuser(q, k, v, m).shape == (512, 128, 64)
+    assert ops.fmha_train_nvfuser(q, k, v, m, m).shape == (512, 128, 64)
+    outs = ops.fmha_train_saveim_nvfuser(q, k, v, m, m)
+    assert [tuple(o.shape) for o in outs] == [(512, 128, 64), (512, 128, 128), (512, 128, 128)]
+    assert all(o.device.type == "meta" and o.dtype == torch.float16 for o in outs)
+
+
+def test_forward_backward_infer_shapes(ops):
+    q, k, v = meta(2, 4, 200, 128, dtype=torch.bfloat16), meta(2, 4, 77, 128, dtype=torch.bfloat16), meta(2, 4, 77, 128, dtype=torch.bfloat16)
+    lens = torch.empty(2, dtype=torch.int32, device="meta")
+    o, lse = ops.fmha_fwd(q, k, v, None, lens, 0.1, 5, 9)
+    assert o.shape == q.shape and o.dtype == torch.bfloat16
+    assert lse.shape == (2, 4, 200) and lse.dtype == torch.float32
+    dq, dk, dv = ops.fmha_bwd(torch.empty_like(o), q, k, v, o, lse, None, lens, 0.1, 5, 9)
+    assert dq.shape == q.shape and dk.shape == k.shape and dv.shape == v.shape
+    # [B*H, S, D] inputs give a [B*H, S] logsumexp
+    o3, lse3 = ops.fmha_fwd(meta(6, 50, 64), meta(6, 40, 64), meta(6, 40, 64))
+    assert o3.shape == (6, 50, 64) and lse3.shape == (6, 50)
+
+
+def test_autograd_operator_traces_on_meta_tensors(ops):
+    q = meta(2, 3, 64, 64).requires_grad_()
+    k = meta(2, 3, 96, 64).requires_grad_()
+    v = meta(2, 3, 96, 64).requires_grad_()
+    o = ops.fmha(q, k, v, None, None, 0.0, 0, 0)
+    assert o.shape == q.shape and o.requires_grad
+    gq, gk, gv = torch.autograd.grad(o, (q, k, v), torch.empty_like(o))
+    assert gq.shape == q.shape and gk.shape == k.shape and gv.shape == v.shape
+
+
+def test_shape_errors_are_raised_without_a_device(ops):
+    with pytest.raises(RuntimeError, match="head dimension"):
+        ops.fmha_fwd(meta(1, 1, 16, 32), meta(1, 1, 16, 32), meta(1, 1, 16, 32))
+    with pytest.raises(RuntimeError, match="sequence lengths differ"):
+        ops.fmha_fwd(meta(1, 1, 16, 64), meta(1, 1, 16, 64), meta(1, 1, 24, 64))
+    with pytest.raises(RuntimeError, match="float16 or bfloat16"):
+        ops.fmha_fwd(meta(1, 1, 16, 64, dtype=torch.float32), meta(1, 1, 16, 64, dtype=torch.float32), meta(1, 1, 16, 64, dtype=torch.float32))
+    with pytest.raises(RuntimeError, match="B\\*H\\*S_q\\*S_k"):
+        ops.fmha_nvfuser(meta(4, 16, 64), meta(4, 16, 64), meta(4, 16, 64), meta(4, 16, 8))
