@@ -83,6 +83,24 @@ static int make_tmap_accum(CUtensorMap* out, float* ptr, uint64_t rows, int D) {
   return FMHA_OK;
 }
 
+// Tensor map of a dense 16-bit [rows, cols] mask with {64 x 128} boxes and 128-byte swizzle.
+static int make_tmap_dense(CUtensorMap* out, const void* ptr, int dtype, uint64_t rows, uint64_t cols) {
+  auto enc = get_encode_fn();
+  if (enc == nullptr) return FMHA_ERR_LAUNCH;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 2};
+  const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(kTileM)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = (dtype == FMHA_DTYPE_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = enc(out, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_cuda_error = static_cast<int>(r);
+    return FMHA_ERR_LAUNCH;
+  }
+  return FMHA_OK;
+}
+
 static bool tensor_ok(const fmha_tensor4& t, int B, int H) {
   if (t.ptr == nullptr) return false;
   if (reinterpret_cast<uintptr_t>(t.ptr) & 15) return false;
@@ -208,7 +226,16 @@ int fmha_sm100_fwd(const fmha_fwd_params* p, void* stream) {
   a.keep_mask_out = p->keep_mask_out;
   a.debug_scores = p->debug_scores;
   a.status = p->status;
-
+  // A dense padding mask whose rows are 16-byte multiples is staged tile by tile through TMA (coalesced, read
+  // once for both softmax passes); otherwise the softmax threads read it directly.  The dense dropout mask is
+  // always read directly: a second 32 KB tile would leave room for one CTA per SM only, which measured slower
+  // (35.6 us against 22.9 us for the train operator at B*H = 512, S = 128, D = 64).
+  a.mask_tiles = 0;
+  const bool dense_mask = p->mask_kind == FMHA_MASK_DENSE_KEEP || p->mask_kind == FMHA_MASK_DENSE_ADDITIVE;
+  if (dense_mask && (p->S_k % 8) == 0 && (reinterpret_cast<uintptr_t>(p->mask) & 15) == 0) {
+    if ((rc = make_tmap_dense(&a.tm_mask, p->mask, p->dtype, static_cast<uint64_t>(p->B) * p->H * p->S_q, p->S_k))) return rc;
+    a.mask_tiles = 1;
+  }
 
   const int e = launch_fwd(a, p->D, p->dtype, legacy, p_via_smem, static_cast<cudaStream_t>(stream));
   if (e != 0) return cuda_fail(static_cast<cudaError_t>(e));

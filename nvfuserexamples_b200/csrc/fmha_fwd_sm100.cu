@@ -41,12 +41,12 @@ constexpr float kMaskedKeep = -10000.0f;  // (1 - amask) * -10000, fmha_manual.c
 
 enum WaitSite {
   kSiteQFull = 101, kSiteKEmpty = 102, kSiteVEmpty = 103, kSiteKFull = 104, kSiteVFull = 105,
-  kSitePFull = 106, kSiteSFull = 107, kSiteOFull = 108
+  kSitePFull = 106, kSiteSFull = 107, kSiteOFull = 108, kSiteMFull = 109, kSiteMEmpty = 110
 };
 
 template <int D, bool PSMEM>
 struct FwdSmem {
-  static constexpr int kStages = (D == 64) ? 2 : 1;
+  static constexpr int kStages = 1;                  // K / V stages (CTAs sharing the SM overlap each other instead)
   static constexpr int kTileBytes = kTileM * D * 2;  // one Q / K / V tile
   static constexpr int kOffQ = 0;
   static constexpr int kOffK = kOffQ + kTileBytes;
@@ -55,10 +55,13 @@ struct FwdSmem {
   static constexpr int kPBytes = PSMEM ? kTileM * kTileN * 2 : 0;
   static constexpr int kOffMask = kOffP + kPBytes;       // 2 x 128 floats
   static constexpr int kOffBar = kOffMask + 2 * kTileN * 4;
-  static constexpr int kNumBars = 4 + 4 * kStages;       // q_full, s_full, p_full, o_full + 4 per stage
+  static constexpr int kNumBars = 6 + 4 * kStages;       // q_full, s_full, p_full, o_full, m_full, m_empty + 4 per stage
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;  // tmem base, abort flag
   static constexpr int kBytes = kOffMisc + 16;
-  static constexpr int kDynBytes = kBytes + 1024;  // slack for the 1024-byte alignment of the base
+  // the dense mask tile (present or not, chosen per launch) follows: 128 x 128 16-bit = two swizzled 16 KB halves
+  static constexpr int kOffMaskTiles = (kBytes + 1023) / 1024 * 1024;
+  static constexpr int kMaskTileBytes = kTileM * kTileN * 2;
+  static constexpr int dyn_bytes(int mask_tiles) { return kOffMaskTiles + mask_tiles * kMaskTileBytes + 1024; }  // + alignment slack
 };
 
 }  // namespace
@@ -85,12 +88,15 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fmha_fwd_kernel(const __grid_c
   uint64_t* s_full = bars + 1;
   uint64_t* p_full = bars + 2;
   uint64_t* o_full = bars + 3;
-  uint64_t* k_full = bars + 4;
+  uint64_t* m_full = bars + 4;    // dense mask tiles of a step have landed
+  uint64_t* m_empty = bars + 5;   // ... and have been consumed (all softmax threads arrive)
+  uint64_t* k_full = bars + 6;
   uint64_t* k_empty = k_full + ST;
   uint64_t* v_full = k_empty + ST;
   uint64_t* v_empty = v_full + ST;
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(smem + L::kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kOffMisc + 4);
+  uint8_t* sMaskT = smem + L::kOffMaskTiles;   // present when a.mask_tiles > 0
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -119,6 +125,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fmha_fwd_kernel(const __grid_c
     mbar_init(s_full, 1);
     mbar_init(p_full, 128);
     mbar_init(o_full, 1);
+    mbar_init(m_full, 1);
+    mbar_init(m_empty, 128);
     for (int s = 0; s < ST; ++s) {
       mbar_init(k_full + s, 1);
       mbar_init(k_empty + s, 1);
@@ -151,6 +159,16 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fmha_fwd_kernel(const __grid_c
       for (int i = 0; i < n_steps; ++i) {
         const bool stats_only = i < n_pre;
         const int j = stats_only ? i : i - n_pre;
+        if constexpr (LEGACY) {
+          if (a.mask_tiles > 0) {
+            // the mask tile of this step: rows of this query tile, key columns [j*128, +128) in two 64-column boxes
+            if (i > 0) mbar_wait(m_empty, (i - 1) & 1, wctx, kSiteMEmpty);
+            mbar_arrive_expect_tx(m_full, L::kMaskTileBytes);
+            const int mrow = bh * a.S_q + q0;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) tma_load_2d(sMaskT + c * 16384, &a.tm_mask, m_full, j * kTileN + c * 64, mrow);
+          }
+        }
         {
           const int s = kcnt % ST;
           if (kcnt >= ST) mbar_wait(k_empty + s, ((kcnt / ST) - 1) & 1, wctx, kSiteKEmpty);
@@ -173,53 +191,64 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fmha_fwd_kernel(const __grid_c
     }
   } else if (warp == 1) {
     // ============================ MMA issuer ========================================
-    if (lane == 0) {
+    // The warp runs the loop convergently and issues the MMAs in bursts from one elected lane with
+    // descriptors prepared beforehand (see umma_ss_x4): a single lane that computes each descriptor
+    // and then issues is starved of issue slots by the softmax warps.
+    {
+      constexpr int KQ = D / 16;
       const uint32_t tS = tmem_base + kColS;
       const uint32_t tO = tmem_base + kColO;
-      const uint32_t sQ_addr = smem_u32(sQ);
+      const uint64_t dq = make_smem_desc_sw128(smem_u32(sQ), 16, 1024);
+      uint64_t aq[KQ];
+#pragma unroll
+      for (int kk = 0; kk < KQ; ++kk) aq[kk] = dq + kmajor_step(kk, 16384);
       mbar_wait(q_full, 0, wctx, kSiteQFull);
       int kcnt = 0, vcnt = 0;
       for (int i = 0; i < n_steps; ++i) {
         const bool stats_only = i < n_pre;
         {
           const int s = kcnt % ST;
+          const uint64_t dk = make_smem_desc_sw128(smem_u32(sK + s * L::kTileBytes), 16, 1024);
+          uint64_t bk[KQ];
+#pragma unroll
+          for (int kk = 0; kk < KQ; ++kk) bk[kk] = dk + kmajor_step(kk, 16384);
           mbar_wait(k_full + s, (kcnt / ST) & 1, wctx, kSiteKFull);
           tc_fence_after_sync();
-          const uint32_t sK_addr = smem_u32(sK + s * L::kTileBytes);
-#pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) {
-            const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
-            umma_ss(tS, make_smem_desc_sw128(sQ_addr + off, 16, 1024), make_smem_desc_sw128(sK_addr + off, 16, 1024),
-                    kIdescQK, kk > 0 ? 1u : 0u);
-          }
-          umma_commit(k_empty + s);
-          umma_commit(s_full);
+          if constexpr (KQ == 4) umma_ss_x4(tS, aq, bk, kIdescQK, 0u);
+          else umma_ss_x8(tS, aq, bk, kIdescQK, 0u);
+          umma_commit_elect(k_empty + s);
+          umma_commit_elect(s_full);
           ++kcnt;
         }
         mbar_wait(p_full, i & 1, wctx, kSitePFull);
         tc_fence_after_sync();
         if (!stats_only) {
           const int s = vcnt % ST;
+          // B = V tile, MN-major: 16 key rows per step (2048 B), 64-wide d chunks 16 KB apart
+          const uint64_t dv = make_smem_desc_sw128(smem_u32(sV + s * L::kTileBytes), 16384, 1024);
+          uint64_t bv[8];
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) bv[kk] = dv + mnmajor_step(kk);
           mbar_wait(v_full + s, (vcnt / ST) & 1, wctx, kSiteVFull);
           tc_fence_after_sync();
-          const uint32_t sV_addr = smem_u32(sV + s * L::kTileBytes);
+          const uint32_t acc0 = (vcnt > 0) ? 1u : 0u;
+          if constexpr (PSMEM) {
+            const uint64_t dp = make_smem_desc_sw128(smem_u32(sP), 16, 1024);
+            uint64_t ap[8];
 #pragma unroll
-          for (int kk = 0; kk < kTileN / 16; ++kk) {
-            // B = V tile, MN-major: 16 key rows per step (2048 B), 64-wide d chunks 16 KB apart
-            const uint64_t vdesc = make_smem_desc_sw128(sV_addr + kk * 2048, 16384, 1024);
-            const uint32_t acc = (vcnt > 0 || kk > 0) ? 1u : 0u;
-            if constexpr (PSMEM) {
-              const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
-              umma_ss(tO, make_smem_desc_sw128(smem_u32(sP) + off, 16, 1024), vdesc, kIdescPV, acc);
-            } else {
-              umma_ts(tO, tS + kk * 8, vdesc, kIdescPV, acc);
-            }
+            for (int kk = 0; kk < 8; ++kk) ap[kk] = dp + kmajor_step(kk, 16384);
+            umma_ss_x8(tO, ap, bv, kIdescPV, acc0);
+          } else {
+            const uint64_t (&b0)[4] = *reinterpret_cast<const uint64_t (*)[4]>(&bv[0]);
+            const uint64_t (&b1)[4] = *reinterpret_cast<const uint64_t (*)[4]>(&bv[4]);
+            umma_ts_x4(tO, tS, 8u, b0, kIdescPV, acc0);
+            umma_ts_x4(tO, tS + 32u, 8u, b1, kIdescPV, 1u);
           }
-          umma_commit(v_empty + s);
+          umma_commit_elect(v_empty + s);
           ++vcnt;
         }
       }
-      umma_commit(o_full);
+      umma_commit_elect(o_full);
     }
   } else {
     // ============================ softmax / epilogue ================================
@@ -253,6 +282,24 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fmha_fwd_kernel(const __grid_c
       }
       mbar_wait(s_full, i & 1, wctx, kSiteSFull);
       tc_fence_after_sync();
+      [[maybe_unused]] const bool mask_staged = LEGACY && a.mask_tiles > 0;
+      if constexpr (LEGACY) {
+        if (mask_staged) mbar_wait(m_full, i & 1, wctx, kSiteMFull);
+      }
+      // 32 staged 16-bit values of this thread's row: chunk c of the mask tile
+      [[maybe_unused]] auto staged_row32 = [&](int c, float (&out)[32]) {
+        const uint32_t tile = smem_u32(sMaskT + (c / 2) * 16384);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint4 w = lds128(tile + sw128_offset(row, (c % 2) * 4 + q));
+          const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            out[q * 8 + 2 * k] = unpack_lo<BF16>(ws[k]);
+            out[q * 8 + 2 * k + 1] = unpack_hi<BF16>(ws[k]);
+          }
+        }
+      };
 
       // Produces chunk c (32 columns) of this row in the log2 domain: t = s*scale*log2e + mask*log2e,
       // -inf for excluded columns.
@@ -270,7 +317,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fmha_fwd_kernel(const __grid_c
           if (a.mask_kind == FMHA_MASK_DENSE_KEEP || a.mask_kind == FMHA_MASK_DENSE_ADDITIVE) {
             float mv[32];
             const int nv = row_ok ? max(0, min(32, n_cols - cbase)) : 0;
-            load_row32<BF16>(a.mask, dense_row + col0 + cbase, nv, a.mask_kind == FMHA_MASK_DENSE_KEEP ? 1.f : 0.f, mv);
+            if (mask_staged) staged_row32(c, mv);   // columns past n_cols are excluded below, rows past S_q are never stored
+            else load_row32<BF16>(a.mask, dense_row + col0 + cbase, nv, a.mask_kind == FMHA_MASK_DENSE_KEEP ? 1.f : 0.f, mv);
 #pragma unroll
             for (int k = 0; k < 32; ++k) {
               const float add = (a.mask_kind == FMHA_MASK_DENSE_KEEP) ? (1.0f - mv[k]) * kMaskedKeep : mv[k];
@@ -438,6 +486,9 @@ __global__ void __launch_bounds__(kFwdThreads, 1) fmha_fwd_kernel(const __grid_c
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(p_full);
+      if constexpr (LEGACY) {
+        if (mask_staged) mbar_arrive(m_empty);
+      }
     }
 
     // ---- epilogue: normalise O, store O and the logsumexp --------------------------
@@ -499,10 +550,16 @@ template <int D, bool BF16, bool LEGACY, bool PSMEM>
 static int launch_fwd_impl(const FwdArgs& a, cudaStream_t stream) {
   using L = FwdSmem<D, PSMEM>;
   auto kfn = fmha_fwd_kernel<D, BF16, LEGACY, PSMEM>;
-  cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynBytes);
-  if (e != cudaSuccess) return static_cast<int>(e);
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, L::dyn_bytes(1));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
   dim3 grid((a.S_q + kTileM - 1) / kTileM, a.H, a.B);
-  kfn<<<grid, kFwdThreads, L::kDynBytes, stream>>>(a);
+  kfn<<<grid, kFwdThreads, L::dyn_bytes(a.mask_tiles), stream>>>(a);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -21,6 +21,9 @@ struct FwdArgs {
   alignas(64) CUtensorMap tm_k;
   alignas(64) CUtensorMap tm_v;
   alignas(64) CUtensorMap tm_o;
+  // general kernel only: the dense [B*H*S_q, S_k] 16-bit padding mask as a 2-D map with {64 x 128} boxes
+  alignas(64) CUtensorMap tm_mask;
+  int mask_tiles;   // 0: the mask is read with plain loads; 1: staged tile by tile through TMA
   int B, H, S_q, S_k;
   float scale_log2;  // softmax scale * log2(e)
   float* lse;
