@@ -61,7 +61,15 @@ enum {
   /* int32 [B] valid key length: keys j >= len[b] get -10000 added (and whole key tiles past
      len[b] are skipped, which is exact in fp32 whenever len[b] >= 1; len[b] == 0 is
      treated as "nothing masked", the value the uniform shift of the composite converges to). */
-  FMHA_MASK_SEQLEN = 4
+  FMHA_MASK_SEQLEN = 4,
+  /* Packed variable-length batch (self-attention): int32 [B+1] cumulative row offsets, cu[0] = 0,
+     cu[B] = total_rows.  q, k, v, o (and d_o, dq, dk, dv) are [total_rows, H, D] views -- stride_s and
+     stride_h are used, stride_b is ignored -- and sequence b owns rows [cu[b], cu[b+1]).  S_q = S_k =
+     an upper bound of the sequence lengths (it sizes the grid).  lse is [H, total_rows].  Rows of a
+     tile past the end of its sequence are read (they belong to the next sequence) but never take
+     part: keys are masked, queries are not written.  The Philox counter uses positions inside the
+     sequence, so a packed batch draws the same bits as the padded batch. */
+  FMHA_MASK_CU_SEQLENS = 5
 };
 
 /* How dropout is applied to the softmax probabilities. */
@@ -110,6 +118,7 @@ typedef struct {
   float* debug_scores;      /* optional [B*H,S_q,S_k] raw Q.K^T accumulators (testing aid) */
   int32_t flags;            /* FMHA_FLAG_* */
   int32_t* status;          /* optional device int32[4]: nonzero word 0 = in-kernel wait ran out */
+  int32_t total_rows;       /* FMHA_MASK_CU_SEQLENS: rows of the packed tensors (= cu[B]) */
 } fmha_fwd_params;
 
 enum {
@@ -130,7 +139,7 @@ typedef struct {
   fmha_tensor4 q, k, v, o, d_o; /* inputs */
   const float* lse;           /* [B*H, S_q] from the forward call */
   fmha_tensor4 dq, dk, dv;    /* outputs */
-  int32_t mask_kind;          /* NONE, KEY_ADDITIVE or SEQLEN */
+  int32_t mask_kind;          /* NONE, KEY_ADDITIVE, SEQLEN or CU_SEQLENS */
   const void* mask;
   int32_t dropout_kind;       /* NONE or PHILOX */
   float p_drop;
@@ -140,6 +149,7 @@ typedef struct {
   size_t workspace_bytes;
   int32_t flags;
   int32_t* status;
+  int32_t total_rows;         /* FMHA_MASK_CU_SEQLENS: rows of the packed tensors (= cu[B]) */
 } fmha_bwd_params;
 
 /* ---- entry points --------------------------------------------------------------- */

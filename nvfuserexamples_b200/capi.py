@@ -23,7 +23,7 @@ FMHA_ERR_NO_DEVICE = 5
 FMHA_ERR_TOO_LARGE = 6
 
 DTYPE_F16, DTYPE_BF16 = 0, 1
-MASK_NONE, MASK_DENSE_KEEP, MASK_DENSE_ADDITIVE, MASK_KEY_ADDITIVE, MASK_SEQLEN = 0, 1, 2, 3, 4
+MASK_NONE, MASK_DENSE_KEEP, MASK_DENSE_ADDITIVE, MASK_KEY_ADDITIVE, MASK_SEQLEN, MASK_CU_SEQLENS = 0, 1, 2, 3, 4, 5
 DROPOUT_NONE, DROPOUT_DENSE, DROPOUT_PHILOX = 0, 1, 2
 FLAG_P_VIA_SMEM = 1
 FLAG_BWD_SKIP_PREPARE = 2
@@ -56,6 +56,7 @@ class FwdParams(C.Structure):
         ("save_softmax", C.c_void_p), ("save_dropout", C.c_void_p),
         ("keep_mask_out", C.c_void_p), ("debug_scores", C.c_void_p),
         ("flags", C.c_int32), ("status", C.c_void_p),
+        ("total_rows", C.c_int32),
     ]
 
 
@@ -72,6 +73,7 @@ class BwdParams(C.Structure):
         ("philox_seed", C.c_uint64), ("philox_offset", C.c_uint64), ("philox_bh_offset", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("flags", C.c_int32), ("status", C.c_void_p),
+        ("total_rows", C.c_int32),
     ]
 
 
@@ -245,6 +247,65 @@ def bwd(d_o, q, k, v, o, lse, *, workspace=None, **kw):
     import torch
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     p = bwd_params(d_o, q, k, v, o, lse, dq, dk, dv, **kw)
+    need = bwd_workspace_bytes(p)
+    if workspace is None:
+        workspace = torch.empty(max(need, 1), dtype=torch.uint8, device=q.device)
+    p.workspace = workspace.data_ptr()
+    p.workspace_bytes = workspace.numel()
+    _check(load().fmha_sm100_bwd(C.byref(p), _stream_ptr(q.device)), "fmha_sm100_bwd")
+    return dq, dk, dv
+
+
+# ---------------------------------------------------------------------------------------
+# packed variable-length batches: q, k, v are [total_rows, H, D]; cu_seqlens int32 [B+1] on the device
+# ---------------------------------------------------------------------------------------
+def _t4_packed(x) -> Tensor4:
+    """[total, H, D] torch tensor -> fmha_tensor4 (the batch stride is not used)."""
+    return Tensor4(x.data_ptr(), 0, x.stride(1), x.stride(0))
+
+
+def fwd_varlen(q, k, v, cu_seqlens, max_seqlen, *, p_drop=0.0, seed=0, offset=0, bh_offset=0, scale=None, status=None,
+               out=None):
+    """Forward over a packed batch.  Returns {'o': [total,H,D], 'lse': [H,total]}."""
+    import torch
+    total, H, D = q.shape
+    o = out if out is not None else torch.empty_like(q)
+    lse = torch.empty((H, total), dtype=torch.float32, device=q.device)
+    p = FwdParams()
+    p.struct_bytes = C.sizeof(FwdParams)
+    p.dtype = _dtype_code(q)
+    p.B, p.H, p.S_q, p.S_k, p.D = cu_seqlens.numel() - 1, H, max_seqlen, max_seqlen, D
+    p.scale = float(scale) if scale is not None else 1.0 / math.sqrt(D)
+    p.q, p.k, p.v, p.o = _t4_packed(q), _t4_packed(k), _t4_packed(v), _t4_packed(o)
+    p.lse = lse.data_ptr()
+    p.mask_kind, p.mask, p.total_rows = MASK_CU_SEQLENS, cu_seqlens.data_ptr(), total
+    if p_drop > 0:
+        p.dropout_kind, p.p_drop = DROPOUT_PHILOX, p_drop
+    p.philox_seed, p.philox_offset, p.philox_bh_offset = seed, offset, bh_offset
+    p.status = _ptr(status)
+    _check(load().fmha_sm100_fwd(C.byref(p), _stream_ptr(q.device)), "fmha_sm100_fwd")
+    return {"o": o, "lse": lse}
+
+
+def bwd_varlen(d_o, q, k, v, o, lse, cu_seqlens, max_seqlen, *, p_drop=0.0, seed=0, offset=0, bh_offset=0, scale=None,
+               status=None, workspace=None):
+    """Backward over a packed batch.  Returns (dq, dk, dv), each [total,H,D]."""
+    import torch
+    total, H, D = q.shape
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    p = BwdParams()
+    p.struct_bytes = C.sizeof(BwdParams)
+    p.dtype = _dtype_code(q)
+    p.B, p.H, p.S_q, p.S_k, p.D = cu_seqlens.numel() - 1, H, max_seqlen, max_seqlen, D
+    p.scale = float(scale) if scale is not None else 1.0 / math.sqrt(D)
+    p.q, p.k, p.v, p.o, p.d_o = (_t4_packed(x) for x in (q, k, v, o, d_o))
+    p.lse = lse.data_ptr()
+    p.dq, p.dk, p.dv = _t4_packed(dq), _t4_packed(dk), _t4_packed(dv)
+    p.mask_kind, p.mask, p.total_rows = MASK_CU_SEQLENS, cu_seqlens.data_ptr(), total
+    p.dropout_kind = DROPOUT_PHILOX if p_drop > 0 else DROPOUT_NONE
+    p.p_drop = p_drop
+    p.philox_seed, p.philox_offset, p.philox_bh_offset = seed, offset, bh_offset
+    p.status = _ptr(status)
     need = bwd_workspace_bytes(p)
     if workspace is None:
         workspace = torch.empty(max(need, 1), dtype=torch.uint8, device=q.device)

@@ -90,6 +90,7 @@ struct PrepArgs {
   float* delta;     // [B*H, S_q]
   float* dq_accum;  // [B*H, S_q_pad, D]
   int* work_counter;  // the main kernel's work-item counter, cleared here
+  const int* cu_seqlens;  // packed batch: row offsets into the [total_rows, H, D] tensors (o_sb / do_sb unused), else null
 };
 
 template <bool BF16>
@@ -108,10 +109,20 @@ __global__ void __launch_bounds__(256) bwd_prepare_kernel(const PrepArgs a) {
     float4* acc = reinterpret_cast<float4*>(a.dq_accum + (static_cast<int64_t>(bh) * a.S_q_pad + r) * a.D + part * per);
     for (int i = 0; i < per / 4; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
+  // packed batch: row r of sequence b is row cu[b] + r of the tensors, and exists for r < cu[b+1] - cu[b]
+  int64_t row_o = static_cast<int64_t>(b) * a.o_sb + static_cast<int64_t>(r) * a.o_ss;
+  int64_t row_do = static_cast<int64_t>(b) * a.do_sb + static_cast<int64_t>(r) * a.do_ss;
+  int q_limit = a.S_q;
+  if (a.cu_seqlens != nullptr) {
+    const int base = a.cu_seqlens[b];
+    q_limit = a.cu_seqlens[b + 1] - base;
+    row_o = static_cast<int64_t>(base + r) * a.o_ss;
+    row_do = static_cast<int64_t>(base + r) * a.do_ss;
+  }
   float sum = 0.f;
-  if (in_range && r < a.S_q) {
-    const unsigned short* po = reinterpret_cast<const unsigned short*>(a.o) + b * a.o_sb + h * a.o_sh + r * a.o_ss + part * per;
-    const unsigned short* pd = reinterpret_cast<const unsigned short*>(a.d_o) + b * a.do_sb + h * a.do_sh + r * a.do_ss + part * per;
+  if (in_range && r < q_limit) {
+    const unsigned short* po = reinterpret_cast<const unsigned short*>(a.o) + row_o + h * a.o_sh + part * per;
+    const unsigned short* pd = reinterpret_cast<const unsigned short*>(a.d_o) + row_do + h * a.do_sh + part * per;
     for (int i = 0; i < per / 8; ++i) {
       const uint4 wo = __ldg(reinterpret_cast<const uint4*>(po) + i);
       const uint4 wd = __ldg(reinterpret_cast<const uint4*>(pd) + i);
@@ -127,7 +138,7 @@ __global__ void __launch_bounds__(256) bwd_prepare_kernel(const PrepArgs a) {
   sum += __shfl_xor_sync(0xffffffffu, sum, 1);
   sum += __shfl_xor_sync(0xffffffffu, sum, 2);
   sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-  if (part == 0 && in_range && r < a.S_q) a.delta[static_cast<int64_t>(bh) * a.S_q + r] = sum;
+  if (part == 0 && in_range && r < q_limit) a.delta[static_cast<int64_t>(bh) * a.S_q + r] = sum;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -139,6 +150,7 @@ struct FinishArgs {
   int64_t sb, sh, ss;
   int B, H, S_q, S_q_pad, D;
   float scale;
+  const int* cu_seqlens;  // packed batch: row offsets into the [total_rows, H, D] dQ (sb unused), else null
 };
 
 template <bool BF16>
@@ -151,6 +163,12 @@ __global__ void __launch_bounds__(256) bwd_finish_kernel(const FinishArgs a) {
   const int bh = blockIdx.x;
   const int h = bh % a.H;
   const int b = bh / a.H;
+  int64_t row_dq = static_cast<int64_t>(b) * a.sb + static_cast<int64_t>(r) * a.ss;
+  if (a.cu_seqlens != nullptr) {
+    const int base = a.cu_seqlens[b];
+    if (r >= a.cu_seqlens[b + 1] - base) return;
+    row_dq = static_cast<int64_t>(base + r) * a.ss;
+  }
   const float4* src = reinterpret_cast<const float4*>(a.dq_accum + (static_cast<int64_t>(bh) * a.S_q_pad + r) * a.D + part * 8);
   const float4 x = src[0], y = src[1];
   uint4 w;
@@ -158,7 +176,7 @@ __global__ void __launch_bounds__(256) bwd_finish_kernel(const FinishArgs a) {
   w.y = pack2<BF16>(x.z * a.scale, x.w * a.scale);
   w.z = pack2<BF16>(y.x * a.scale, y.y * a.scale);
   w.w = pack2<BF16>(y.z * a.scale, y.w * a.scale);
-  unsigned short* dst = reinterpret_cast<unsigned short*>(a.dq) + b * a.sb + h * a.sh + r * a.ss + part * 8;
+  unsigned short* dst = reinterpret_cast<unsigned short*>(a.dq) + row_dq + h * a.sh + part * 8;
   *reinterpret_cast<uint4*>(dst) = w;
 }
 
@@ -182,9 +200,14 @@ __global__ void __launch_bounds__(256) bwd_finish_kernel(const FinishArgs a) {
 struct BwdItem {
   int id;      // < 0: no more work
   int b, h, bh, k0, n_cols;   // n_cols <= 0: key tile wholly masked out
+  int n_q;     // query tiles of this item
+  int q_limit; // query rows [0, q_limit) exist
+  int row_base;  // packed batch: first row of the sequence in the [total_rows, H, D] tensors (else 0)
+  int tb;        // batch coordinate of the tensor maps (0 for a packed batch)
 };
 
-template <int D, bool BF16, bool KEYADD, bool DROP>
+// PACKED: FMHA_MASK_CU_SEQLENS; a template parameter so that the padded kernels carry none of its bookkeeping.
+template <int D, bool BF16, bool KEYADD, bool DROP, bool PACKED = false>
 __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_constant__ BwdArgs a) {
   using L = BwdSmem<D>;
   constexpr int ST = L::kStages;
@@ -229,8 +252,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int kv_tiles = (a.S_k + kTileN - 1) / kTileN;
-  const int n_q = (a.S_q + kTileM - 1) / kTileM;
+  const int n_q_all = (a.S_q + kTileM - 1) / kTileM;
   const int num_items = kv_tiles * a.H * a.B;
+  constexpr bool packed = PACKED;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -286,16 +310,29 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
     it.id = id;
     it.b = it.h = it.bh = it.k0 = 0;
     it.n_cols = 0;
+    it.n_q = n_q_all;
+    it.q_limit = a.S_q;
+    it.row_base = 0;
+    it.tb = 0;
     if (id >= 0) {
       const int kv_tile = id % kv_tiles;
       it.bh = id / kv_tiles;
       it.h = it.bh % a.H;
       it.b = it.bh / a.H;
+      it.tb = it.b;
       it.k0 = kv_tile * kTileN;
       int k_limit = a.S_k;
-      if (a.mask_kind == FMHA_MASK_SEQLEN) {
+      if (!packed && a.mask_kind == FMHA_MASK_SEQLEN) {
         const int len = reinterpret_cast<const int*>(a.mask)[it.b];
         if (len > 0 && len < a.S_k) k_limit = len;
+      } else if (packed) {
+        const int* cu = reinterpret_cast<const int*>(a.mask);
+        it.row_base = cu[it.b];
+        const int len = cu[it.b + 1] - it.row_base;
+        k_limit = len;
+        it.q_limit = len;
+        it.n_q = (len + kTileM - 1) / kTileM;
+        it.tb = 0;
       }
       it.n_cols = min(kTileN, k_limit - it.k0);
     }
@@ -331,17 +368,17 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
         mbar_arrive_expect_tx(kv_full + kvb, 2 * L::kTileBytes);
 #pragma unroll
         for (int c = 0; c < D / 64; ++c) {
-          tma_load_4d(sK + kvb * L::kTileBytes + c * 16384, &a.tm_k, kv_full + kvb, c * 64, it.k0, it.h, it.b);
-          tma_load_4d(sV + kvb * L::kTileBytes + c * 16384, &a.tm_v, kv_full + kvb, c * 64, it.k0, it.h, it.b);
+          tma_load_4d(sK + kvb * L::kTileBytes + c * 16384, &a.tm_k, kv_full + kvb, c * 64, it.row_base + it.k0, it.h, it.tb);
+          tma_load_4d(sV + kvb * L::kTileBytes + c * 16384, &a.tm_v, kv_full + kvb, c * 64, it.row_base + it.k0, it.h, it.tb);
         }
-        for (int i = 0; i < n_q; ++i, ++g) {
+        for (int i = 0; i < it.n_q; ++i, ++g) {
           const int s = g % ST;
           if (g >= ST) mbar_wait(qdo_empty + s, ((g / ST) - 1) & 1, wctx, kSiteQdoEmpty);
           mbar_arrive_expect_tx(qdo_full + s, 2 * L::kTileBytes);
 #pragma unroll
           for (int c = 0; c < D / 64; ++c) {
-            tma_load_4d(sQ + s * L::kTileBytes + c * 16384, &a.tm_q, qdo_full + s, c * 64, i * kTileM, it.h, it.b);
-            tma_load_4d(sdO + s * L::kTileBytes + c * 16384, &a.tm_do, qdo_full + s, c * 64, i * kTileM, it.h, it.b);
+            tma_load_4d(sQ + s * L::kTileBytes + c * 16384, &a.tm_q, qdo_full + s, c * 64, it.row_base + i * kTileM, it.h, it.tb);
+            tma_load_4d(sdO + s * L::kTileBytes + c * 16384, &a.tm_do, qdo_full + s, c * 64, it.row_base + i * kTileM, it.h, it.tb);
           }
         }
         ++w;
@@ -407,6 +444,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
       BwdItem nxt = cur;
       bool have_nxt = false;
       const uint64_t dK_m = make_smem_desc_sw128(smem_u32(sK + kvb * L::kTileBytes), 16384, 1024);   // K as MN-major B (dQ)
+      const int n_q = cur.n_q;
       for (int i = 0; i < n_q; ++i, ++t) {
         TL(t * 16 + 0);
         const int s = t % ST;
@@ -595,10 +633,17 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
     auto store_dkdv = [&](int item_id, bool from_tmem) {
       const BwdItem it = decode(item_id);
       uint8_t* stage = OWNSTAGE ? sDQ + cw * 2048 : sP + cw * 4096;
+      // Packed batch: a slice that reaches past the end of the sequence would overwrite the next sequence's
+      // rows, so its rows are written one by one from registers.
+      const int key = it.k0 + quad * 32 + lane;
+      const bool edge = packed && (it.k0 + quad * 32 + 32 > it.q_limit);
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         const float mul = (which == 0) ? dscale : a.scale * dscale;
         const uint32_t rowaddr = smem_u32(stage) + which * 32 * kDkvRowBytes + lane * kDkvRowBytes;
+        unsigned short* grow = reinterpret_cast<unsigned short*>(which == 0 ? a.dv_ptr : a.dk_ptr) +
+                               static_cast<int64_t>(it.row_base + key) * (which == 0 ? a.dv_ss : a.dk_ss) +
+                               static_cast<int64_t>(it.h) * (which == 0 ? a.dv_sh : a.dk_sh) + cq * DQ;
 #pragma unroll
         for (int c = 0; c < DQ / 16; ++c) {
           uint32_t r[16];
@@ -610,19 +655,25 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
             for (int k = 0; k < 16; ++k) r[k] = 0u;
           }
 #pragma unroll
-          for (int q = 0; q < 2; ++q)
-            sts128(rowaddr + c * 32 + q * 16,
-                   pack2<BF16>(__uint_as_float(r[q * 8 + 0]) * mul, __uint_as_float(r[q * 8 + 1]) * mul),
-                   pack2<BF16>(__uint_as_float(r[q * 8 + 2]) * mul, __uint_as_float(r[q * 8 + 3]) * mul),
-                   pack2<BF16>(__uint_as_float(r[q * 8 + 4]) * mul, __uint_as_float(r[q * 8 + 5]) * mul),
-                   pack2<BF16>(__uint_as_float(r[q * 8 + 6]) * mul, __uint_as_float(r[q * 8 + 7]) * mul));
+          for (int q = 0; q < 2; ++q) {
+            uint4 w;
+            w.x = pack2<BF16>(__uint_as_float(r[q * 8 + 0]) * mul, __uint_as_float(r[q * 8 + 1]) * mul);
+            w.y = pack2<BF16>(__uint_as_float(r[q * 8 + 2]) * mul, __uint_as_float(r[q * 8 + 3]) * mul);
+            w.z = pack2<BF16>(__uint_as_float(r[q * 8 + 4]) * mul, __uint_as_float(r[q * 8 + 5]) * mul);
+            w.w = pack2<BF16>(__uint_as_float(r[q * 8 + 6]) * mul, __uint_as_float(r[q * 8 + 7]) * mul);
+            if (edge) {
+              if (key < it.q_limit) *reinterpret_cast<uint4*>(grow + c * 16 + q * 8) = w;
+            } else {
+              sts128(rowaddr + c * 32 + q * 16, w.x, w.y, w.z, w.w);
+            }
+          }
         }
       }
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0 && *abort_flag == 0) {
-        tma_store_4d(&a.tm_dv, stage, cq * DQ, it.k0 + quad * 32, it.h, it.b);
-        tma_store_4d(&a.tm_dk, stage + 32 * kDkvRowBytes, cq * DQ, it.k0 + quad * 32, it.h, it.b);
+      if (lane == 0 && *abort_flag == 0 && !edge) {
+        tma_store_4d(&a.tm_dv, stage, cq * DQ, it.row_base + it.k0 + quad * 32, it.h, it.tb);
+        tma_store_4d(&a.tm_dk, stage + 32 * kDkvRowBytes, cq * DQ, it.row_base + it.k0 + quad * 32, it.h, it.tb);
         tma_store_commit();
       }
     };
@@ -641,6 +692,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
       const BwdItem cur = fetch_item(n++, kComputeSleepNs);
       if (cur.id < 0) break;
       if (cur.n_cols <= 0) {
+        if (packed) continue;   // a packed sequence has no rows past its length
         // key tile wholly past the valid length: its gradients are zero
         if constexpr (OWNSTAGE) {
           own_stage_free();
@@ -657,8 +709,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
         }
         continue;
       }
-      const int k0 = cur.k0, n_cols = cur.n_cols, bh = cur.bh;
+      const int k0 = cur.k0, n_cols = cur.n_cols, bh = cur.bh, n_q = cur.n_q, q_limit = cur.q_limit;
       const uint32_t gbh = static_cast<uint32_t>(a.philox_bh_offset + bh);
+      // logsumexp rows: [B*H, S_q], or [H, total_rows] for a packed batch; delta is always [B*H, S_q]
+      const int64_t lse_base = packed ? static_cast<int64_t>(cur.h) * a.total_rows + cur.row_base : static_cast<int64_t>(bh) * a.S_q;
+      const int64_t delta_base = static_cast<int64_t>(bh) * a.S_q;
       const float* mask_row = sMask + (w & 1) * kTileN;
       if constexpr (KEYADD) {
         // both barriers are needed: a slower warp may still read the other item's values (first),
@@ -675,9 +730,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
       // Row statistics of the next tile are fetched one iteration ahead and kept RAW: any arithmetic
       // on the loaded value here would make the warp wait for the load at once (~1000 cycles per tile).
       float lse_next = INFINITY, delta_next = 0.f;
-      if (row < a.S_q) {
-        lse_next = a.lse[static_cast<size_t>(bh) * a.S_q + row];
-        delta_next = a.delta[static_cast<size_t>(bh) * a.S_q + row];
+      if (row < q_limit) {
+        lse_next = a.lse[lse_base + row];
+        delta_next = a.delta[delta_base + row];
       }
 
       for (int i = 0; i < n_q; ++i, ++t) {
@@ -687,12 +742,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
         const float delta = delta_next * inv_c;
         {
           const int nr = q_row + kTileM;  // prefetch the statistics of the next tile's row
-          const bool ok = (i + 1 < n_q) && nr < a.S_q;
+          const bool ok = (i + 1 < n_q) && nr < q_limit;
           lse_next = INFINITY;
           delta_next = 0.f;
           if (ok) {
-            lse_next = a.lse[static_cast<size_t>(bh) * a.S_q + nr];
-            delta_next = a.delta[static_cast<size_t>(bh) * a.S_q + nr];
+            lse_next = a.lse[lse_base + nr];
+            delta_next = a.delta[delta_base + nr];
           }
         }
 
@@ -863,10 +918,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
 // ---------------------------------------------------------------------------------------
 // launchers
 // ---------------------------------------------------------------------------------------
-template <int D, bool BF16, bool KEYADD, bool DROP>
+template <int D, bool BF16, bool KEYADD, bool DROP, bool PACKED = false>
 static int launch_bwd_impl(const BwdArgs& a, cudaStream_t stream) {
   using L = BwdSmem<D>;
-  auto kfn = fmha_bwd_kernel<D, BF16, KEYADD, DROP>;
+  auto kfn = fmha_bwd_kernel<D, BF16, KEYADD, DROP, PACKED>;
   static bool configured[64] = {};
   static int sm_count[64] = {};
   int dev = 0;
@@ -894,6 +949,20 @@ int launch_bwd(const BwdArgs& a, int D, int dtype, cudaStream_t stream) {
   const bool bf = dtype == FMHA_DTYPE_BF16;
   const bool keyadd = a.mask_kind == FMHA_MASK_KEY_ADDITIVE;
   const bool drop = a.dropout_kind == FMHA_DROPOUT_PHILOX;
+  if (a.mask_kind == FMHA_MASK_CU_SEQLENS) {
+#define FMHA_BWD_PACKED(DD, BF, DR) \
+  if (D == DD && bf == BF && drop == DR) return launch_bwd_impl<DD, BF, false, DR, true>(a, stream);
+    FMHA_BWD_PACKED(64, false, false)
+    FMHA_BWD_PACKED(64, false, true)
+    FMHA_BWD_PACKED(64, true, false)
+    FMHA_BWD_PACKED(64, true, true)
+    FMHA_BWD_PACKED(128, false, false)
+    FMHA_BWD_PACKED(128, false, true)
+    FMHA_BWD_PACKED(128, true, false)
+    FMHA_BWD_PACKED(128, true, true)
+#undef FMHA_BWD_PACKED
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
 #define FMHA_BWD_CASE(DD, BF, KA, DR) \
   if (D == DD && bf == BF && keyadd == KA && drop == DR) return launch_bwd_impl<DD, BF, KA, DR>(a, stream);
   FMHA_BWD_CASE(64, false, false, false)
@@ -917,14 +986,14 @@ int launch_bwd(const BwdArgs& a, int D, int dtype, cudaStream_t stream) {
 }
 
 int launch_bwd_prepare(const void* o, const fmha_tensor4& ot, const fmha_tensor4& dot, int B, int H, int S_q, int S_q_pad,
-                       int D, int dtype, float* delta, float* dq_accum, int* work_counter, cudaStream_t stream) {
+                       int D, int dtype, float* delta, float* dq_accum, int* work_counter, const int* cu_seqlens, cudaStream_t stream) {
   PrepArgs p;
   p.o = ot.ptr; p.d_o = dot.ptr;
   (void)o;
   p.o_sb = ot.stride_b; p.o_sh = ot.stride_h; p.o_ss = ot.stride_s;
   p.do_sb = dot.stride_b; p.do_sh = dot.stride_h; p.do_ss = dot.stride_s;
   p.B = B; p.H = H; p.S_q = S_q; p.S_q_pad = S_q_pad; p.D = D;
-  p.delta = delta; p.dq_accum = dq_accum; p.work_counter = work_counter;
+  p.delta = delta; p.dq_accum = dq_accum; p.work_counter = work_counter; p.cu_seqlens = cu_seqlens;
   const dim3 grid(static_cast<unsigned>(B) * H, static_cast<unsigned>((S_q_pad + 31) / 32));
   if (dtype == FMHA_DTYPE_BF16) bwd_prepare_kernel<true><<<grid, 256, 0, stream>>>(p);
   else bwd_prepare_kernel<false><<<grid, 256, 0, stream>>>(p);
@@ -932,11 +1001,11 @@ int launch_bwd_prepare(const void* o, const fmha_tensor4& ot, const fmha_tensor4
 }
 
 int launch_bwd_finish(const float* dq_accum, const fmha_tensor4& dq, int B, int H, int S_q, int S_q_pad, int D, int dtype,
-                      float scale, cudaStream_t stream) {
+                      float scale, const int* cu_seqlens, cudaStream_t stream) {
   FinishArgs f;
   f.dq_accum = dq_accum; f.dq = dq.ptr;
   f.sb = dq.stride_b; f.sh = dq.stride_h; f.ss = dq.stride_s;
-  f.B = B; f.H = H; f.S_q = S_q; f.S_q_pad = S_q_pad; f.D = D; f.scale = scale;
+  f.B = B; f.H = H; f.S_q = S_q; f.S_q_pad = S_q_pad; f.D = D; f.scale = scale; f.cu_seqlens = cu_seqlens;
   const int rows_per_block = 256 / (D / 8);
   const dim3 grid(static_cast<unsigned>(B) * H, static_cast<unsigned>((S_q + rows_per_block - 1) / rows_per_block));
   if (dtype == FMHA_DTYPE_BF16) bwd_finish_kernel<true><<<grid, 256, 0, stream>>>(f);

@@ -152,7 +152,7 @@ using namespace fmha;
 
 extern "C" {
 
-int fmha_sm100_abi_version(void) { return 1; }
+int fmha_sm100_abi_version(void) { return 2; }
 
 int fmha_sm100_last_cuda_error(void) { return g_last_cuda_error; }
 
@@ -175,18 +175,20 @@ int fmha_sm100_fwd(const fmha_fwd_params* p, void* stream) {
   if (p == nullptr) return FMHA_ERR_BAD_ARG;
   int rc = validate_common(p->struct_bytes, sizeof(fmha_fwd_params), p->dtype, p->B, p->H, p->S_q, p->S_k, p->D, p->scale);
   if (rc != FMHA_OK) return rc;
-  if (p->mask_kind < FMHA_MASK_NONE || p->mask_kind > FMHA_MASK_SEQLEN) return FMHA_ERR_UNSUPPORTED;
+  if (p->mask_kind < FMHA_MASK_NONE || p->mask_kind > FMHA_MASK_CU_SEQLENS) return FMHA_ERR_UNSUPPORTED;
   if (p->dropout_kind < FMHA_DROPOUT_NONE || p->dropout_kind > FMHA_DROPOUT_PHILOX) return FMHA_ERR_UNSUPPORTED;
   if (p->mask_kind != FMHA_MASK_NONE && p->mask == nullptr) return FMHA_ERR_BAD_ARG;
   if (p->dropout_kind == FMHA_DROPOUT_DENSE && p->dropout_mask == nullptr) return FMHA_ERR_BAD_ARG;
+  const bool packed = p->mask_kind == FMHA_MASK_CU_SEQLENS;
+  if (packed && (p->total_rows <= 0 || p->S_q != p->S_k)) return FMHA_ERR_BAD_ARG;
   if (p->dropout_kind == FMHA_DROPOUT_PHILOX) {
     if (!(p->p_drop >= 0.f && p->p_drop < 1.f)) return FMHA_ERR_BAD_ARG;
     if (p->philox_offset >> 32) return FMHA_ERR_BAD_ARG;
   }
   if (p->B == 0 || p->H == 0 || p->S_q == 0) return FMHA_OK;  // nothing to write
   if (p->S_k == 0) return FMHA_ERR_BAD_ARG;                    // softmax over no keys is undefined
-  if (!tensor_ok(p->q, p->B, p->H) || !tensor_ok(p->k, p->B, p->H) || !tensor_ok(p->v, p->B, p->H) ||
-      !tensor_ok(p->o, p->B, p->H))
+  const int cB = packed ? 1 : p->B;   // the batch stride of packed tensors is not used
+  if (!tensor_ok(p->q, cB, p->H) || !tensor_ok(p->k, cB, p->H) || !tensor_ok(p->v, cB, p->H) || !tensor_ok(p->o, cB, p->H))
     return FMHA_ERR_BAD_ARG;
   rc = check_device();
   if (rc != FMHA_OK) return rc;
@@ -197,11 +199,16 @@ int fmha_sm100_fwd(const fmha_fwd_params* p, void* stream) {
   const bool legacy = p_via_smem || p->mask_kind == FMHA_MASK_DENSE_KEEP || p->mask_kind == FMHA_MASK_DENSE_ADDITIVE ||
                       p->dropout_kind == FMHA_DROPOUT_DENSE || p->save_softmax || p->save_dropout ||
                       p->keep_mask_out || p->debug_scores;
-  if ((rc = make_tmap(&a.tm_q, sanitized(p->q, p->B, p->H, p->S_q, p->D), p->dtype, p->B, p->H, p->S_q, p->D, kTileM))) return rc;
+  if (packed && legacy) return FMHA_ERR_UNSUPPORTED;   // packed batches: production kernel only
+  // tensor-map extents: [B, H, S, D], or one "batch" of total_rows rows for a packed batch
+  const int mB = packed ? 1 : p->B, mSq = packed ? p->total_rows : p->S_q, mSk = packed ? p->total_rows : p->S_k;
+  if ((rc = make_tmap(&a.tm_q, sanitized(p->q, mB, p->H, mSq, p->D), p->dtype, mB, p->H, mSq, p->D, kTileM))) return rc;
   const int kv_rows = fwd_key_tile(p->D, legacy);
-  if ((rc = make_tmap(&a.tm_k, sanitized(p->k, p->B, p->H, p->S_k, p->D), p->dtype, p->B, p->H, p->S_k, p->D, kv_rows))) return rc;
-  if ((rc = make_tmap(&a.tm_v, sanitized(p->v, p->B, p->H, p->S_k, p->D), p->dtype, p->B, p->H, p->S_k, p->D, kv_rows))) return rc;
-  if ((rc = make_tmap(&a.tm_o, sanitized(p->o, p->B, p->H, p->S_q, p->D), p->dtype, p->B, p->H, p->S_q, p->D, kTileM))) return rc;
+  if ((rc = make_tmap(&a.tm_k, sanitized(p->k, mB, p->H, mSk, p->D), p->dtype, mB, p->H, mSk, p->D, kv_rows))) return rc;
+  if ((rc = make_tmap(&a.tm_v, sanitized(p->v, mB, p->H, mSk, p->D), p->dtype, mB, p->H, mSk, p->D, kv_rows))) return rc;
+  if ((rc = make_tmap(&a.tm_o, sanitized(p->o, mB, p->H, mSq, p->D), p->dtype, mB, p->H, mSq, p->D, kTileM))) return rc;
+  a.total_rows = p->total_rows;
+  a.o_ptr = p->o.ptr; a.o_ss = p->o.stride_s; a.o_sh = p->o.stride_h;
   a.B = p->B; a.H = p->H; a.S_q = p->S_q; a.S_k = p->S_k;
   a.scale_log2 = p->scale * 1.4426950408889634f;
   a.lse = p->lse;
@@ -259,8 +266,11 @@ int fmha_sm100_bwd(const fmha_bwd_params* p, void* stream_) {
   if (p == nullptr) return FMHA_ERR_BAD_ARG;
   int rc = validate_common(p->struct_bytes, sizeof(fmha_bwd_params), p->dtype, p->B, p->H, p->S_q, p->S_k, p->D, p->scale);
   if (rc != FMHA_OK) return rc;
-  if (p->mask_kind != FMHA_MASK_NONE && p->mask_kind != FMHA_MASK_KEY_ADDITIVE && p->mask_kind != FMHA_MASK_SEQLEN)
+  if (p->mask_kind != FMHA_MASK_NONE && p->mask_kind != FMHA_MASK_KEY_ADDITIVE && p->mask_kind != FMHA_MASK_SEQLEN &&
+      p->mask_kind != FMHA_MASK_CU_SEQLENS)
     return FMHA_ERR_UNSUPPORTED;
+  const bool packed = p->mask_kind == FMHA_MASK_CU_SEQLENS;
+  if (packed && (p->total_rows <= 0 || p->S_q != p->S_k)) return FMHA_ERR_BAD_ARG;
   if (p->dropout_kind != FMHA_DROPOUT_NONE && p->dropout_kind != FMHA_DROPOUT_PHILOX) return FMHA_ERR_UNSUPPORTED;
   if (p->mask_kind != FMHA_MASK_NONE && p->mask == nullptr) return FMHA_ERR_BAD_ARG;
   if (p->dropout_kind == FMHA_DROPOUT_PHILOX) {
@@ -270,9 +280,10 @@ int fmha_sm100_bwd(const fmha_bwd_params* p, void* stream_) {
   if (p->B == 0 || p->H == 0) return FMHA_OK;
   if (p->S_q == 0 && p->S_k == 0) return FMHA_OK;
   if (p->S_k == 0 || p->S_q == 0) return FMHA_ERR_BAD_ARG;
-  if (!tensor_ok(p->q, p->B, p->H) || !tensor_ok(p->k, p->B, p->H) || !tensor_ok(p->v, p->B, p->H) ||
-      !tensor_ok(p->o, p->B, p->H) || !tensor_ok(p->d_o, p->B, p->H) || !tensor_ok(p->dq, p->B, p->H) ||
-      !tensor_ok(p->dk, p->B, p->H) || !tensor_ok(p->dv, p->B, p->H) || p->lse == nullptr)
+  const int cB = packed ? 1 : p->B;   // the batch stride of packed tensors is not used
+  if (!tensor_ok(p->q, cB, p->H) || !tensor_ok(p->k, cB, p->H) || !tensor_ok(p->v, cB, p->H) || !tensor_ok(p->o, cB, p->H) ||
+      !tensor_ok(p->d_o, cB, p->H) || !tensor_ok(p->dq, cB, p->H) || !tensor_ok(p->dk, cB, p->H) || !tensor_ok(p->dv, cB, p->H) ||
+      p->lse == nullptr)
     return FMHA_ERR_BAD_ARG;
   size_t need = 0;
   rc = fmha_sm100_bwd_workspace_bytes(p, &need);
@@ -291,18 +302,24 @@ int fmha_sm100_bwd(const fmha_bwd_params* p, void* stream_) {
 
   BwdArgs a;
   std::memset(&a, 0, sizeof(a));
-  const fmha_tensor4 tq = sanitized(p->q, p->B, p->H, p->S_q, p->D), tk = sanitized(p->k, p->B, p->H, p->S_k, p->D),
-                     tv = sanitized(p->v, p->B, p->H, p->S_k, p->D), to = sanitized(p->o, p->B, p->H, p->S_q, p->D),
-                     tdo = sanitized(p->d_o, p->B, p->H, p->S_q, p->D), tdq = sanitized(p->dq, p->B, p->H, p->S_q, p->D),
-                     tdk = sanitized(p->dk, p->B, p->H, p->S_k, p->D), tdv = sanitized(p->dv, p->B, p->H, p->S_k, p->D);
-  if ((rc = make_tmap(&a.tm_q, tq, p->dtype, p->B, p->H, p->S_q, p->D, kTileM))) return rc;
-  if ((rc = make_tmap(&a.tm_k, tk, p->dtype, p->B, p->H, p->S_k, p->D, kTileN))) return rc;
-  if ((rc = make_tmap(&a.tm_v, tv, p->dtype, p->B, p->H, p->S_k, p->D, kTileN))) return rc;
-  if ((rc = make_tmap(&a.tm_do, tdo, p->dtype, p->B, p->H, p->S_q, p->D, kTileM))) return rc;
+  // tensor-map extents: [B, H, S, D], or one "batch" of total_rows rows for a packed batch
+  const int mB = packed ? 1 : p->B, mSq = packed ? p->total_rows : p->S_q, mSk = packed ? p->total_rows : p->S_k;
+  const fmha_tensor4 tq = sanitized(p->q, mB, p->H, mSq, p->D), tk = sanitized(p->k, mB, p->H, mSk, p->D),
+                     tv = sanitized(p->v, mB, p->H, mSk, p->D), to = sanitized(p->o, mB, p->H, mSq, p->D),
+                     tdo = sanitized(p->d_o, mB, p->H, mSq, p->D), tdq = sanitized(p->dq, mB, p->H, mSq, p->D),
+                     tdk = sanitized(p->dk, mB, p->H, mSk, p->D), tdv = sanitized(p->dv, mB, p->H, mSk, p->D);
+  if ((rc = make_tmap(&a.tm_q, tq, p->dtype, mB, p->H, mSq, p->D, kTileM))) return rc;
+  if ((rc = make_tmap(&a.tm_k, tk, p->dtype, mB, p->H, mSk, p->D, kTileN))) return rc;
+  if ((rc = make_tmap(&a.tm_v, tv, p->dtype, mB, p->H, mSk, p->D, kTileN))) return rc;
+  if ((rc = make_tmap(&a.tm_do, tdo, p->dtype, mB, p->H, mSq, p->D, kTileM))) return rc;
   // dK and dV leave in per-warp slices of 32 key rows x D/4 columns
-  if ((rc = make_tmap(&a.tm_dk, tdk, p->dtype, p->B, p->H, p->S_k, p->D, 32, p->D / 4))) return rc;
-  if ((rc = make_tmap(&a.tm_dv, tdv, p->dtype, p->B, p->H, p->S_k, p->D, 32, p->D / 4))) return rc;
+  if ((rc = make_tmap(&a.tm_dk, tdk, p->dtype, mB, p->H, mSk, p->D, 32, p->D / 4))) return rc;
+  if ((rc = make_tmap(&a.tm_dv, tdv, p->dtype, mB, p->H, mSk, p->D, 32, p->D / 4))) return rc;
   a.work_counter = work_counter;
+  a.total_rows = p->total_rows;
+  a.dk_ptr = tdk.ptr; a.dk_ss = tdk.stride_s; a.dk_sh = tdk.stride_h;
+  a.dv_ptr = tdv.ptr; a.dv_ss = tdv.stride_s; a.dv_sh = tdv.stride_h;
+  const int* cu_seqlens = packed ? reinterpret_cast<const int*>(p->mask) : nullptr;
   if ((rc = make_tmap_accum(&a.tm_dq, dq_accum, static_cast<uint64_t>(bh) * s_q_pad, p->D))) return rc;
   a.B = p->B; a.H = p->H; a.S_q = p->S_q; a.S_k = p->S_k;
   a.scale = p->scale;
@@ -329,7 +346,8 @@ int fmha_sm100_bwd(const fmha_bwd_params* p, void* stream_) {
 
   int e = 0;
   if (!(p->flags & FMHA_FLAG_BWD_SKIP_PREPARE)) {
-    e = launch_bwd_prepare(nullptr, to, tdo, p->B, p->H, p->S_q, s_q_pad, p->D, p->dtype, delta, dq_accum, work_counter, stream);
+    e = launch_bwd_prepare(nullptr, to, tdo, p->B, p->H, p->S_q, s_q_pad, p->D, p->dtype, delta, dq_accum, work_counter, cu_seqlens,
+                           stream);
     if (e != 0) return cuda_fail(static_cast<cudaError_t>(e));
   } else {
     // the caller prepared delta and the accumulator itself; the work counter is still ours to clear
@@ -340,7 +358,8 @@ int fmha_sm100_bwd(const fmha_bwd_params* p, void* stream_) {
   if (e != 0) return cuda_fail(static_cast<cudaError_t>(e));
   if (!(p->flags & FMHA_FLAG_BWD_SKIP_FINISH)) {
     // the main kernel leaves the dropout factor 1/(1-p) out of dS; it is applied here (and to dK, dV in its epilogue)
-    e = launch_bwd_finish(dq_accum, tdq, p->B, p->H, p->S_q, s_q_pad, p->D, p->dtype, p->scale * a.dropout_scale, stream);
+    e = launch_bwd_finish(dq_accum, tdq, p->B, p->H, p->S_q, s_q_pad, p->D, p->dtype, p->scale * a.dropout_scale, cu_seqlens,
+                          stream);
     if (e != 0) return cuda_fail(static_cast<cudaError_t>(e));
   }
   return FMHA_OK;

@@ -100,7 +100,9 @@ __device__ __forceinline__ void softmax_chunk(const uint32_t (&r)[32], int cbase
 
 }  // namespace
 
-template <int D, bool BF16, bool KEYADD, bool DROP>
+// PACKED: the batch is one [total_rows, H, D] tensor per operand with row offsets (FMHA_MASK_CU_SEQLENS); a
+// template parameter so that the padded kernels carry none of its bookkeeping in registers.
+template <int D, bool BF16, bool KEYADD, bool DROP, bool PACKED = false>
 __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_fwd_fast_kernel(const __grid_constant__ FwdArgs a) {
   using L = FastSmem<D>;
   constexpr int ST = L::kStages;
@@ -137,9 +139,21 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
   const int bh = b * a.H + h;
 
   int k_limit = a.S_k;
-  if (a.mask_kind == FMHA_MASK_SEQLEN) {
+  int q_limit = a.S_q;     // query rows [0, q_limit) of this (b, h) exist
+  int row_base = 0;        // packed batch: first row of sequence b in the [total_rows, H, D] tensors
+  int tb = b;              // batch coordinate of the tensor maps (0 for a packed batch)
+  constexpr bool packed = PACKED;
+  if (!packed && a.mask_kind == FMHA_MASK_SEQLEN) {
     const int len = reinterpret_cast<const int*>(a.mask)[b];
     if (len > 0 && len < a.S_k) k_limit = len;
+  } else if (packed) {
+    const int* cu = reinterpret_cast<const int*>(a.mask);
+    row_base = cu[b];
+    const int len = cu[b + 1] - row_base;
+    k_limit = len;
+    q_limit = len;
+    tb = 0;
+    if (q0 >= len) return;   // this sequence has no such query tile (whole CTA, before any barrier)
   }
   const int n_kv = (k_limit + TN - 1) / TN;
 
@@ -176,19 +190,19 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
     if (lane == 0) {
       mbar_arrive_expect_tx(q_full, L::kQBytes);
 #pragma unroll
-      for (int c = 0; c < D / 64; ++c) tma_load_4d(sQ + c * 16384, &a.tm_q, q_full, c * 64, q0, h, b);
+      for (int c = 0; c < D / 64; ++c) tma_load_4d(sQ + c * 16384, &a.tm_q, q_full, c * 64, row_base + q0, h, tb);
       for (int j = 0; j < n_kv; ++j) {
         const int s = j % ST;
         if (j >= ST) mbar_wait(k_empty + s, ((j / ST) - 1) & 1, wctx, kFKEmpty);
         mbar_arrive_expect_tx(k_full + s, L::kTileBytes);
 #pragma unroll
         for (int c = 0; c < D / 64; ++c)
-          tma_load_4d(sK + s * L::kTileBytes + c * L::kSubTile, &a.tm_k, k_full + s, c * 64, j * TN, h, b);
+          tma_load_4d(sK + s * L::kTileBytes + c * L::kSubTile, &a.tm_k, k_full + s, c * 64, row_base + j * TN, h, tb);
         if (j >= ST) mbar_wait(v_empty + s, ((j / ST) - 1) & 1, wctx, kFVEmpty);
         mbar_arrive_expect_tx(v_full + s, L::kTileBytes);
 #pragma unroll
         for (int c = 0; c < D / 64; ++c)
-          tma_load_4d(sV + s * L::kTileBytes + c * L::kSubTile, &a.tm_v, v_full + s, c * 64, j * TN, h, b);
+          tma_load_4d(sV + s * L::kTileBytes + c * L::kSubTile, &a.tm_v, v_full + s, c * 64, row_base + j * TN, h, tb);
       }
     }
   } else if (warp == 1) {
@@ -244,7 +258,7 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
     const int row = quad * 32 + lane;
     const int tid = threadIdx.x - 64;
     const int q_row = q0 + row;
-    const bool row_ok = q_row < a.S_q;
+    const bool row_ok = q_row < q_limit;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t tS = tmem_base + lane_addr + kColS;
     const uint32_t tO = tmem_base + lane_addr + kColO;
@@ -370,13 +384,22 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
     tc_fence_after_sync();
     const float l_sum = sum2.x + sum2.y;
     const float out_scale = (DROP ? a.dropout_scale : 1.0f) / l_sum;
-    if (a.lse != nullptr && row_ok) a.lse[static_cast<size_t>(bh) * a.S_q + q_row] = (m_ref + fast_log2(l_sum)) * kLn2F;
+    if (a.lse != nullptr && row_ok) {
+      const size_t li = packed ? static_cast<size_t>(h) * a.total_rows + row_base + q_row   // [H, total_rows]
+                               : static_cast<size_t>(bh) * a.S_q + q_row;                   // [B*H, S_q]
+      a.lse[li] = (m_ref + fast_log2(l_sum)) * kLn2F;
+    }
+    // A packed batch's last query tile of a sequence holds rows of the NEXT sequence past q_limit: its rows
+    // are written one by one from registers instead of through the tile store.
+    const bool partial_rows = packed && (q0 + kTileM > q_limit);
 #pragma unroll
     for (int c = 0; c < D / 32; ++c) {
       uint32_t r[32];
       tmem_ld32(tO + c * 32, r);
       tmem_wait_ld_dep(r);
       uint8_t* tile = sQ + (c / 2) * 16384;  // Q is no longer needed: every QK^T has completed
+      unsigned short* grow = reinterpret_cast<unsigned short*>(a.o_ptr) + static_cast<int64_t>(row_base + q_row) * a.o_ss +
+                             static_cast<int64_t>(h) * a.o_sh + c * 32;
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
         uint4 w;
@@ -384,15 +407,19 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
         w.y = pack2<BF16>(__uint_as_float(r[q * 8 + 2]) * out_scale, __uint_as_float(r[q * 8 + 3]) * out_scale);
         w.z = pack2<BF16>(__uint_as_float(r[q * 8 + 4]) * out_scale, __uint_as_float(r[q * 8 + 5]) * out_scale);
         w.w = pack2<BF16>(__uint_as_float(r[q * 8 + 6]) * out_scale, __uint_as_float(r[q * 8 + 7]) * out_scale);
-        *reinterpret_cast<uint4*>(tile + sw128_offset(row, (c % 2) * 4 + q)) = w;
+        if (partial_rows) {
+          if (row_ok) *reinterpret_cast<uint4*>(grow + q * 8) = w;
+        } else {
+          *reinterpret_cast<uint4*>(tile + sw128_offset(row, (c % 2) * 4 + q)) = w;
+        }
       }
     }
     fence_proxy_async_smem();
     named_bar_sync(1, 128);
     if (tid == 0) {
-      if (*abort_flag == 0) {
+      if (*abort_flag == 0 && !partial_rows) {
 #pragma unroll
-        for (int c = 0; c < D / 64; ++c) tma_store_4d(&a.tm_o, sQ + c * 16384, c * 64, q0, h, b);
+        for (int c = 0; c < D / 64; ++c) tma_store_4d(&a.tm_o, sQ + c * 16384, c * 64, row_base + q0, h, tb);
         tma_store_commit();
       }
       tma_store_wait_read();  // the shared-memory source must outlive the copy; the writes finish on their own
@@ -411,10 +438,10 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
   }
 }
 
-template <int D, bool BF16, bool KEYADD, bool DROP>
+template <int D, bool BF16, bool KEYADD, bool DROP, bool PACKED = false>
 static int launch_fast_impl(const FwdArgs& a, cudaStream_t stream) {
   using L = FastSmem<D>;
-  auto kfn = fmha_fwd_fast_kernel<D, BF16, KEYADD, DROP>;
+  auto kfn = fmha_fwd_fast_kernel<D, BF16, KEYADD, DROP, PACKED>;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -432,6 +459,20 @@ int launch_fwd_fast(const FwdArgs& a, int D, int dtype, cudaStream_t stream) {
   const bool bf = dtype == FMHA_DTYPE_BF16;
   const bool keyadd = a.mask_kind == FMHA_MASK_KEY_ADDITIVE;
   const bool drop = a.dropout_kind == FMHA_DROPOUT_PHILOX;
+  if (a.mask_kind == FMHA_MASK_CU_SEQLENS) {
+#define FMHA_FAST_PACKED(DD, BF, DR) \
+  if (D == DD && bf == BF && drop == DR) return launch_fast_impl<DD, BF, false, DR, true>(a, stream);
+    FMHA_FAST_PACKED(64, false, false)
+    FMHA_FAST_PACKED(64, false, true)
+    FMHA_FAST_PACKED(64, true, false)
+    FMHA_FAST_PACKED(64, true, true)
+    FMHA_FAST_PACKED(128, false, false)
+    FMHA_FAST_PACKED(128, false, true)
+    FMHA_FAST_PACKED(128, true, false)
+    FMHA_FAST_PACKED(128, true, true)
+#undef FMHA_FAST_PACKED
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
 #define FMHA_FAST_CASE(DD, BF, KA, DR) \
   if (D == DD && bf == BF && keyadd == KA && drop == DR) return launch_fast_impl<DD, BF, KA, DR>(a, stream);
   FMHA_FAST_CASE(64, false, false, false)

@@ -24,6 +24,11 @@ struct FwdArgs {
   // general kernel only: the dense [B*H*S_q, S_k] 16-bit padding mask as a 2-D map with {64 x 128} boxes
   alignas(64) CUtensorMap tm_mask;
   int mask_tiles;   // 0: the mask is read with plain loads; 1: staged tile by tile through TMA
+  // FMHA_MASK_CU_SEQLENS (production kernel): mask = int32 [B+1] row offsets into the packed [total_rows, H, D]
+  // tensors; o_ptr / strides serve the row-wise stores of a sequence's last, partial query tile
+  int total_rows;
+  void* o_ptr;
+  int64_t o_ss, o_sh;
   int B, H, S_q, S_k;
   float scale_log2;  // softmax scale * log2(e)
   float* lse;
@@ -59,6 +64,12 @@ struct BwdArgs {
   const float* delta;  // [B*H, S_q] rowsum(dO * O)
   float* dq_accum;     // [B*H, S_q_pad, D] fp32, zero on entry
   int* work_counter;   // zero on entry; the persistent CTAs draw their work items from it
+  // FMHA_MASK_CU_SEQLENS: mask = int32 [B+1] row offsets into the packed [total_rows, H, D] tensors; the raw
+  // dK / dV pointers serve the row-wise stores of a sequence's last, partial key tile
+  int total_rows;
+  void* dk_ptr;
+  void* dv_ptr;
+  int64_t dk_ss, dk_sh, dv_ss, dv_sh;
   int S_q_pad;         // S_q rounded up to the tile
   int mask_kind;
   const void* mask;
@@ -77,8 +88,8 @@ int launch_fwd(const FwdArgs& a, int D, int dtype, bool legacy, bool p_via_smem,
 int launch_fwd_fast(const FwdArgs& a, int D, int dtype, cudaStream_t stream);
 int launch_bwd(const BwdArgs& a, int D, int dtype, cudaStream_t stream);
 int launch_bwd_prepare(const void* o, const fmha_tensor4& ot, const fmha_tensor4& dot, int B, int H, int S_q, int S_q_pad,
-                       int D, int dtype, float* delta, float* dq_accum, int* work_counter, cudaStream_t stream);
+                       int D, int dtype, float* delta, float* dq_accum, int* work_counter, const int* cu_seqlens, cudaStream_t stream);
 int launch_bwd_finish(const float* dq_accum, const fmha_tensor4& dq, int B, int H, int S_q, int S_q_pad, int D, int dtype,
-                      float scale, cudaStream_t stream);
+                      float scale, const int* cu_seqlens, cudaStream_t stream);
 
 }  // namespace fmha

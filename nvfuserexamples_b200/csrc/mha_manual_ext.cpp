@@ -296,6 +296,123 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_bwd(const at::Tensor& d_o, c
   return {dq, dk, dv};
 }
 
+// ---------------------------------------------------------------------------------------
+// packed variable-length batches: q, k, v [total, H, D]; cu_seqlens int32 [B+1] on the device
+// ---------------------------------------------------------------------------------------
+struct Packed {
+  fmha_tensor4 t;
+  int64_t total, H, D;
+};
+Packed packed3(const at::Tensor& x, const char* name) {
+  TORCH_CHECK(x.is_cuda(), "mha_manual: ", name, " must be a CUDA tensor");
+  TORCH_CHECK(x.dim() == 3, "mha_manual: ", name, " must be [total_rows, H, D]");
+  TORCH_CHECK(x.scalar_type() == at::kHalf || x.scalar_type() == at::kBFloat16, "mha_manual: ", name,
+              " must be float16 or bfloat16");
+  TORCH_CHECK(x.stride(-1) == 1, "mha_manual: ", name, " must be contiguous along the head dimension");
+  Packed v;
+  v.total = x.size(0); v.H = x.size(1); v.D = x.size(2);
+  v.t.ptr = x.data_ptr();
+  v.t.stride_b = 0; v.t.stride_h = x.stride(1); v.t.stride_s = x.stride(0);
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(v.t.ptr) & 15) == 0, "mha_manual: ", name, " must be 16-byte aligned");
+  TORCH_CHECK(v.t.stride_s % 8 == 0 && (v.H == 1 || v.t.stride_h % 8 == 0), "mha_manual: strides of ", name,
+              " must be multiples of 8 elements");
+  return v;
+}
+at::Tensor check_cu_seqlens(const at::Tensor& cu, const at::Tensor& q) {
+  TORCH_CHECK(cu.device() == q.device(), "mha_manual: cu_seqlens is on a different device");
+  TORCH_CHECK(cu.dim() == 1 && cu.numel() >= 2, "mha_manual: cu_seqlens must be [B+1]");
+  return cu.to(at::kInt).contiguous();
+}
+void check_packed_qkv(const Packed& q, const Packed& k, const Packed& v, int64_t max_seqlen) {
+  TORCH_CHECK(q.D == 64 || q.D == 128, "mha_manual: head dimension must be 64 or 128, got ", q.D);
+  TORCH_CHECK(k.D == q.D && v.D == q.D && k.H == q.H && v.H == q.H && k.total == q.total && v.total == q.total,
+              "mha_manual: packed q, k, v must have the same [total_rows, H, D] shape");
+  TORCH_CHECK(max_seqlen > 0, "mha_manual: max_seqlen must be positive");
+}
+
+std::tuple<at::Tensor, at::Tensor> fmha_varlen_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                                                   const at::Tensor& cu_seqlens, int64_t max_seqlen, double p_drop,
+                                                   int64_t seed, int64_t offset, c10::optional<double> scale) {
+  const Packed vq = packed3(q, "q"), vk = packed3(k, "k"), vv = packed3(v, "v");
+  check_same(q, k, "k");
+  check_same(q, v, "v");
+  check_packed_qkv(vq, vk, vv, max_seqlen);
+  const c10::cuda::CUDAGuard guard(q.device());
+  const int dev = q.get_device();
+  const at::Tensor cu = check_cu_seqlens(cu_seqlens, q);
+  at::Tensor o = at::empty(q.sizes(), q.options());
+  at::Tensor lse = at::empty({vq.H, vq.total}, q.options().dtype(at::kFloat));
+  if (vq.total == 0) return {o, lse};
+  fmha_fwd_params p{};
+  p.struct_bytes = sizeof(p);
+  p.dtype = dtype_code(q);
+  p.B = static_cast<int32_t>(cu.numel() - 1); p.H = static_cast<int32_t>(vq.H);
+  p.S_q = p.S_k = static_cast<int32_t>(max_seqlen); p.D = static_cast<int32_t>(vq.D);
+  p.scale = scale.has_value() ? static_cast<float>(*scale) : 1.0f / std::sqrt(static_cast<float>(vq.D));
+  p.q = vq.t; p.k = vk.t; p.v = vv.t; p.o = packed3(o, "o").t;
+  p.lse = lse.data_ptr<float>();
+  p.mask_kind = FMHA_MASK_CU_SEQLENS;
+  p.mask = cu.data_ptr();
+  p.total_rows = static_cast<int32_t>(vq.total);
+  if (p_drop > 0.0) {
+    p.dropout_kind = FMHA_DROPOUT_PHILOX;
+    p.p_drop = static_cast<float>(p_drop);
+    p.philox_seed = static_cast<uint64_t>(seed);
+    p.philox_offset = static_cast<uint64_t>(offset);
+  }
+  p.status = status_block(dev).data_ptr<int32_t>();
+  finish_call(fmha_sm100_fwd(&p, at::cuda::getCurrentCUDAStream(dev).stream()), "fmha_varlen_fwd", dev);
+  return {o, lse};
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_varlen_bwd(const at::Tensor& d_o, const at::Tensor& q, const at::Tensor& k,
+                                                               const at::Tensor& v, const at::Tensor& o, const at::Tensor& lse,
+                                                               const at::Tensor& cu_seqlens, int64_t max_seqlen, double p_drop,
+                                                               int64_t seed, int64_t offset, c10::optional<double> scale) {
+  const Packed vq = packed3(q, "q"), vk = packed3(k, "k"), vv = packed3(v, "v"), vo = packed3(o, "o");
+  at::Tensor d_o_c = d_o.stride(-1) == 1 ? d_o : d_o.contiguous();
+  const Packed vdo = packed3(d_o_c, "d_o");
+  check_same(q, k, "k"); check_same(q, v, "v"); check_same(q, o, "o"); check_same(q, d_o_c, "d_o");
+  check_packed_qkv(vq, vk, vv, max_seqlen);
+  TORCH_CHECK(o.sizes() == q.sizes() && d_o_c.sizes() == q.sizes(), "mha_manual: o and d_o must have the shape of q");
+  TORCH_CHECK(lse.device() == q.device() && lse.scalar_type() == at::kFloat && lse.numel() == vq.H * vq.total,
+              "mha_manual: lse must be float32 [H, total_rows] on the device of q");
+  const c10::cuda::CUDAGuard guard(q.device());
+  const int dev = q.get_device();
+  const at::Tensor cu = check_cu_seqlens(cu_seqlens, q);
+  at::Tensor lse_c = lse.contiguous();
+  at::Tensor dq = at::empty(q.sizes(), q.options());
+  at::Tensor dk = at::empty(k.sizes(), k.options());
+  at::Tensor dv = at::empty(v.sizes(), v.options());
+  if (vq.total == 0) return {dq, dk, dv};
+  fmha_bwd_params p{};
+  p.struct_bytes = sizeof(p);
+  p.dtype = dtype_code(q);
+  p.B = static_cast<int32_t>(cu.numel() - 1); p.H = static_cast<int32_t>(vq.H);
+  p.S_q = p.S_k = static_cast<int32_t>(max_seqlen); p.D = static_cast<int32_t>(vq.D);
+  p.scale = scale.has_value() ? static_cast<float>(*scale) : 1.0f / std::sqrt(static_cast<float>(vq.D));
+  p.q = vq.t; p.k = vk.t; p.v = vv.t; p.o = vo.t; p.d_o = vdo.t;
+  p.lse = lse_c.data_ptr<float>();
+  p.dq = packed3(dq, "dq").t; p.dk = packed3(dk, "dk").t; p.dv = packed3(dv, "dv").t;
+  p.mask_kind = FMHA_MASK_CU_SEQLENS;
+  p.mask = cu.data_ptr();
+  p.total_rows = static_cast<int32_t>(vq.total);
+  if (p_drop > 0.0) {
+    p.dropout_kind = FMHA_DROPOUT_PHILOX;
+    p.p_drop = static_cast<float>(p_drop);
+    p.philox_seed = static_cast<uint64_t>(seed);
+    p.philox_offset = static_cast<uint64_t>(offset);
+  }
+  size_t ws = 0;
+  raise_if(fmha_sm100_bwd_workspace_bytes(&p, &ws), "fmha_bwd_workspace_bytes");
+  at::Tensor workspace = at::empty({static_cast<int64_t>(ws)}, q.options().dtype(at::kByte));
+  p.workspace = workspace.data_ptr();
+  p.workspace_bytes = ws;
+  p.status = status_block(dev).data_ptr<int32_t>();
+  finish_call(fmha_sm100_bwd(&p, at::cuda::getCurrentCUDAStream(dev).stream()), "fmha_varlen_bwd", dev);
+  return {dq, dk, dv};
+}
+
 at::Tensor philox_dropout_mask(int64_t B, int64_t H, int64_t S_q, int64_t S_k, double p, int64_t seed, int64_t offset,
                                int64_t bh_offset, bool on_device) {
   TORCH_CHECK(B >= 0 && H >= 0 && S_q >= 0 && S_k >= 0, "mha_manual: negative size");
@@ -374,6 +491,49 @@ class FmhaFunction : public torch::autograd::Function<FmhaFunction> {
     return {dq, dk, dv, at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor()};
   }
 };
+
+class FmhaVarlenFunction : public torch::autograd::Function<FmhaVarlenFunction> {
+ public:
+  static at::Tensor forward(torch::autograd::AutogradContext* ctx, const at::Tensor& q, const at::Tensor& k,
+                            const at::Tensor& v, const at::Tensor& cu_seqlens, int64_t max_seqlen, double p_drop,
+                            int64_t seed, int64_t offset, c10::optional<double> scale) {
+    at::AutoDispatchBelowADInplaceOrView guard;
+    static auto op = c10::Dispatcher::singleton()
+                         .findSchemaOrThrow("mha_manual::fmha_varlen_fwd", "")
+                         .typed<std::tuple<at::Tensor, at::Tensor>(const at::Tensor&, const at::Tensor&, const at::Tensor&,
+                                                                   const at::Tensor&, int64_t, double, int64_t, int64_t,
+                                                                   c10::optional<double>)>();
+    auto [o, lse] = op.call(q, k, v, cu_seqlens, max_seqlen, p_drop, seed, offset, scale);
+    ctx->save_for_backward({q, k, v, o, lse, cu_seqlens});
+    ctx->saved_data["max_seqlen"] = max_seqlen;
+    ctx->saved_data["p_drop"] = p_drop;
+    ctx->saved_data["seed"] = seed;
+    ctx->saved_data["offset"] = offset;
+    ctx->saved_data["has_scale"] = scale.has_value();
+    ctx->saved_data["scale"] = scale.has_value() ? *scale : 0.0;
+    return o;
+  }
+  static torch::autograd::variable_list backward(torch::autograd::AutogradContext* ctx,
+                                                 torch::autograd::variable_list grads) {
+    const auto saved = ctx->get_saved_variables();
+    c10::optional<double> scale;
+    if (ctx->saved_data["has_scale"].toBool()) scale = ctx->saved_data["scale"].toDouble();
+    static auto op = c10::Dispatcher::singleton()
+                         .findSchemaOrThrow("mha_manual::fmha_varlen_bwd", "")
+                         .typed<std::tuple<at::Tensor, at::Tensor, at::Tensor>(
+                             const at::Tensor&, const at::Tensor&, const at::Tensor&, const at::Tensor&, const at::Tensor&,
+                             const at::Tensor&, const at::Tensor&, int64_t, double, int64_t, int64_t, c10::optional<double>)>();
+    auto [dq, dk, dv] = op.call(grads[0], saved[0], saved[1], saved[2], saved[3], saved[4], saved[5],
+                                ctx->saved_data["max_seqlen"].toInt(), ctx->saved_data["p_drop"].toDouble(),
+                                ctx->saved_data["seed"].toInt(), ctx->saved_data["offset"].toInt(), scale);
+    return {dq, dk, dv, at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor()};
+  }
+};
+
+at::Tensor fmha_varlen_autograd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& cu_seqlens,
+                                int64_t max_seqlen, double p_drop, int64_t seed, int64_t offset, c10::optional<double> scale) {
+  return FmhaVarlenFunction::apply(q, k, v, cu_seqlens, max_seqlen, p_drop, seed, offset, scale);
+}
 
 at::Tensor fmha_autograd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
                          const c10::optional<at::Tensor>& mask, const c10::optional<at::Tensor>& seqlens, double p_drop,
@@ -454,6 +614,32 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_bwd_meta(const at::Tensor& d
   return {at::empty(q.sizes(), q.options()), at::empty(k.sizes(), k.options()), at::empty(v.sizes(), v.options())};
 }
 
+void meta_check_packed(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& cu, int64_t max_seqlen) {
+  TORCH_CHECK(q.dim() == 3, "mha_manual: q must be [total_rows, H, D]");
+  TORCH_CHECK(q.scalar_type() == at::kHalf || q.scalar_type() == at::kBFloat16, "mha_manual: q must be float16 or bfloat16");
+  TORCH_CHECK(k.sizes() == q.sizes() && v.sizes() == q.sizes() && k.scalar_type() == q.scalar_type() &&
+                  v.scalar_type() == q.scalar_type(),
+              "mha_manual: packed q, k, v must have the same [total_rows, H, D] shape and dtype");
+  TORCH_CHECK(q.size(2) == 64 || q.size(2) == 128, "mha_manual: head dimension must be 64 or 128, got ", q.size(2));
+  TORCH_CHECK(cu.dim() == 1 && cu.numel() >= 2, "mha_manual: cu_seqlens must be [B+1]");
+  TORCH_CHECK(max_seqlen > 0, "mha_manual: max_seqlen must be positive");
+}
+std::tuple<at::Tensor, at::Tensor> fmha_varlen_fwd_meta(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                                                        const at::Tensor& cu_seqlens, int64_t max_seqlen, double, int64_t, int64_t,
+                                                        c10::optional<double>) {
+  meta_check_packed(q, k, v, cu_seqlens, max_seqlen);
+  return {at::empty(q.sizes(), q.options()), at::empty({q.size(1), q.size(0)}, q.options().dtype(at::kFloat))};
+}
+std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_varlen_bwd_meta(const at::Tensor& d_o, const at::Tensor& q, const at::Tensor& k,
+                                                                    const at::Tensor& v, const at::Tensor& o, const at::Tensor& lse,
+                                                                    const at::Tensor& cu_seqlens, int64_t max_seqlen, double, int64_t,
+                                                                    int64_t, c10::optional<double>) {
+  meta_check_packed(q, k, v, cu_seqlens, max_seqlen);
+  TORCH_CHECK(o.sizes() == q.sizes() && d_o.sizes() == q.sizes(), "mha_manual: o and d_o must have the shape of q");
+  TORCH_CHECK(lse.scalar_type() == at::kFloat && lse.numel() == q.size(0) * q.size(1), "mha_manual: lse must be float32 [H, total_rows]");
+  return {at::empty(q.sizes(), q.options()), at::empty(k.sizes(), k.options()), at::empty(v.sizes(), v.options())};
+}
+
 }  // namespace
 
 TORCH_LIBRARY(mha_manual, m) {
@@ -467,6 +653,12 @@ TORCH_LIBRARY(mha_manual, m) {
         "-> (Tensor, Tensor, Tensor)");
   m.def("fmha(Tensor q, Tensor k, Tensor v, Tensor? mask=None, Tensor? seqlens=None, float p_drop=0.0, int seed=0, "
         "int offset=0, float? scale=None) -> Tensor");
+  m.def("fmha_varlen_fwd(Tensor q, Tensor k, Tensor v, Tensor cu_seqlens, int max_seqlen, float p_drop=0.0, int seed=0, "
+        "int offset=0, float? scale=None) -> (Tensor, Tensor)");
+  m.def("fmha_varlen_bwd(Tensor d_o, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, Tensor cu_seqlens, int max_seqlen, "
+        "float p_drop=0.0, int seed=0, int offset=0, float? scale=None) -> (Tensor, Tensor, Tensor)");
+  m.def("fmha_varlen(Tensor q, Tensor k, Tensor v, Tensor cu_seqlens, int max_seqlen, float p_drop=0.0, int seed=0, "
+        "int offset=0, float? scale=None) -> Tensor");
   m.def("philox_dropout_mask(int B, int H, int S_q, int S_k, float p, int seed, int offset, int bh_offset=0, "
         "bool on_device=False) -> Tensor", philox_dropout_mask);
   m.def("check_status() -> ()", check_status);
@@ -478,6 +670,8 @@ TORCH_LIBRARY_IMPL(mha_manual, CUDA, m) {
   m.impl("fmha_train_saveim_nvfuser", fmha_train_saveim_nvfuser);
   m.impl("fmha_fwd", fmha_fwd);
   m.impl("fmha_bwd", fmha_bwd);
+  m.impl("fmha_varlen_fwd", fmha_varlen_fwd);
+  m.impl("fmha_varlen_bwd", fmha_varlen_bwd);
 }
 
 TORCH_LIBRARY_IMPL(mha_manual, Meta, m) {
@@ -486,9 +680,14 @@ TORCH_LIBRARY_IMPL(mha_manual, Meta, m) {
   m.impl("fmha_train_saveim_nvfuser", fmha_train_saveim_nvfuser_meta);
   m.impl("fmha_fwd", fmha_fwd_meta);
   m.impl("fmha_bwd", fmha_bwd_meta);
+  m.impl("fmha_varlen_fwd", fmha_varlen_fwd_meta);
+  m.impl("fmha_varlen_bwd", fmha_varlen_bwd_meta);
 }
 
-TORCH_LIBRARY_IMPL(mha_manual, Autograd, m) { m.impl("fmha", fmha_autograd); }
+TORCH_LIBRARY_IMPL(mha_manual, Autograd, m) {
+  m.impl("fmha", fmha_autograd);
+  m.impl("fmha_varlen", fmha_varlen_autograd);
+}
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "B200 fused multi-head attention operators (torch.ops.mha_manual.*)";

@@ -49,6 +49,21 @@ def test_autograd_operator_traces_on_meta_tensors(ops):
     assert gq.shape == q.shape and gk.shape == k.shape and gv.shape == v.shape
 
 
+def test_packed_batch_operators_infer_shapes(ops):
+    q, k, v = meta(1000, 4, 64), meta(1000, 4, 64), meta(1000, 4, 64)
+    cu = torch.empty(9, dtype=torch.int32, device="meta")
+    o, lse = ops.fmha_varlen_fwd(q, k, v, cu, 384, 0.1, 1, 2)
+    assert o.shape == (1000, 4, 64) and lse.shape == (4, 1000) and lse.dtype == torch.float32
+    dq, dk, dv = ops.fmha_varlen_bwd(torch.empty_like(o), q, k, v, o, lse, cu, 384, 0.1, 1, 2)
+    assert dq.shape == dk.shape == dv.shape == (1000, 4, 64)
+    qg = meta(1000, 4, 64).requires_grad_()
+    out = ops.fmha_varlen(qg, k, v, cu, 384)
+    (g,) = torch.autograd.grad(out, (qg,), torch.empty_like(out))
+    assert g.shape == qg.shape
+    with pytest.raises(RuntimeError, match="same \\[total_rows, H, D\\] shape"):
+        ops.fmha_varlen_fwd(q, meta(999, 4, 64), v, cu, 384)
+
+
 def test_shape_errors_are_raised_without_a_device(ops):
     with pytest.raises(RuntimeError, match="head dimension"):
         ops.fmha_fwd(meta(1, 1, 16, 32), meta(1, 1, 16, 32), meta(1, 1, 16, 32))
