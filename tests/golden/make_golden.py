@@ -64,7 +64,7 @@ def checksum(*tensors) -> np.ndarray:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of shmsong/NvFuserExamples")
     ns = ap.parse_args()
     ref = Path(ns.reference)
 
