@@ -17,7 +17,8 @@
 //                    by the tensor core both as K-major (dQ) and as MN-major (dV, dK) operands;
 //                    dQ tiles are staged in shared memory and added to the fp32 accumulator by TMA
 //                    reduce-add (cp.reduce.async.bulk.tensor ... .add);
-//                    dK and dV are written from registers when the next item is already under way.
+//                    dK and dV leave through per-warp staging tiles and TMA stores when the next item is
+//                    already under way.
 //   3. bwd_finish  : dQ = (scale * accumulator) rounded to the 16-bit dtype
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>

@@ -1,20 +1,26 @@
 // fmha_fwd_fast_sm100.cu — the production forward kernel: compact masks only (none, valid
-// lengths, additive [B,S_k] row), optional Philox dropout, writes O and the row logsumexp.
+// lengths, additive [B,S_k] row, or a packed variable-length batch), optional Philox dropout,
+// writes O and the row logsumexp.
 //
 // Same CTA organisation as the general kernel in fmha_fwd_sm100.cu (TMA producer warp,
 // tcgen05.mma issuer warp, four softmax warps with one thread per query row; S in tensor
-// memory columns [0,128), P written back over it, O in columns [128,128+D); two CTAs per SM),
-// with the softmax written for instruction count, because at head dimension 64 the softmax
-// warps, not the tensor core, set the pace:
-//   * mask kind and dropout are template parameters: no per-chunk branches;
+// memory, P written back over it, O beside it).  Head dimension 64 walks the keys in 64-key
+// steps (S 64 + O 64 = 128 tensor-memory columns, three or four CTAs per SM), head dimension
+// 128 in 128-key steps (two CTAs per SM).  The softmax is written for instruction count and
+// latency, because at head dimension 64 the softmax warps, not the tensor core, set the pace:
+//   * mask kind, dropout and the packed-batch bookkeeping are template parameters: no
+//     per-chunk branches and no registers spent on modes that are off;
 //   * the row maximum is taken over the raw accumulators with 3-input max (the scale is
 //     positive), the exponent argument is one packed fma.rn.f32x2 per two elements, the row
 //     sum one packed add;
 //   * S is read twice from tensor memory (max, then exponentials) instead of being held in
-//     128 registers, which keeps two CTAs resident; in the second sweep the load of the next
-//     32 columns is in flight while the current 32 are processed;
-//   * Philox uses one 32x32->64 multiply per product and the keep decision is applied to the
-//     packed 16-bit pairs with two byte permutes and two ANDs per four elements.
+//     registers; in the second sweep the load of the next 32 columns is in flight while the
+//     current 32 are processed;
+//   * Philox uses one 32x32->64 multiply per product, its keep words for a key step are
+//     computed before the step's scores are awaited (they do not depend on them), and the
+//     keep decision is applied to the packed 16-bit pairs with two byte permutes and two ANDs
+//     per four elements;
+//   * the MMA warp issues in bursts from a converged warp (see umma_ss_x4 in sm100_ptx.cuh).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 

@@ -1,10 +1,13 @@
 // fmha_fwd_sm100.cu — fused multi-head-attention forward for B200 (sm_100a).
 //
-// One CTA owns a 128-row query tile of one (batch, head) and walks the keys in 128-wide
-// tiles with an online softmax:
+// The general kernel: everything the three reference operators need that the production kernel
+// (fmha_fwd_fast_sm100.cu) leaves out -- dense [B*H,S,S] masks, a dense dropout mask, saved
+// intermediates, debug outputs.  One CTA owns a 128-row query tile of one (batch, head) and walks
+// the keys in 128-wide tiles with an online softmax:
 //
-//   warp 0      TMA producer : Q once, then K and V tiles into shared memory (128-byte
-//                              swizzle, zero fill past the tensor edge)
+//   warp 0      TMA producer : Q once, then K and V tiles (and the dense padding-mask tile of
+//                              the step) into shared memory (128-byte swizzle, zero fill past
+//                              the tensor edge)
 //   warp 1      MMA issuer   : S = Q K^T and O += P V as tcgen05.mma with fp32 accumulators
 //                              in tensor memory; also owns the tensor-memory allocation
 //   warps 2-5   softmax      : thread r owns row r of the tile: reads S from tensor memory,
