@@ -51,6 +51,33 @@ def test_backward_with_philox_dropout(cuda_device, D, dtype, p):
     _run(cuda_device, 2, 2, 384, 384, D, dtype, "seqlen", p)
 
 
+def test_more_work_items_than_sms_spot_checked_against_the_oracle(cuda_device):
+    """The persistent kernel draws (key tile, head, batch) items from a counter: with 16*16*4 = 1024 items every
+    CTA processes several, including items whose key tile is wholly masked.  Three heads are checked against the
+    oracle evaluated on those heads alone (the Philox counter uses the global head index)."""
+    B, H, S, D, p = 16, 16, 512, 64, 0.1
+    q, k, v, d_o, _ = helpers.randn_like_config(B, H, S, S, D, torch.float16, seed=31, device=cuda_device)
+    g = torch.Generator().manual_seed(5)
+    lens = torch.randint(100, S + 1, (B,), generator=g, dtype=torch.int32).to(cuda_device)
+    status = torch.zeros(4, dtype=torch.int32, device=cuda_device)
+    o, lse = api.fmha_forward(q, k, v, seqlens=lens, p_drop=p, seed=9, offset=4, status=status)
+    dq, dk, dv = api.fmha_backward(d_o, q, k, v, o, lse, seqlens=lens, p_drop=p, seed=9, offset=4, status=status)
+    assert capi.check_status(status) == [0, 0, 0, 0]
+    for b, h in ((0, 0), (7, 9), (15, 15)):
+        sl = (slice(b, b + 1), slice(h, h + 1))
+        ref, add, keep, ks = helpers.oracle_forward(q[sl], k[sl], v[sl], lens=lens[b:b + 1], p_drop=p, seed=9, offset=4,
+                                                    bh_offset=b * H + h)
+        rdq, rdk, rdv = helpers.oracle_backward(q[sl], k[sl], v[sl], d_o[sl], add=add, keep=keep, ks=ks)
+        helpers.assert_close(o[sl], ref["o"], f"o[{b},{h}]")
+        helpers.assert_close(dq[sl], rdq, f"dq[{b},{h}]")
+        helpers.assert_close(dk[sl], rdk, f"dk[{b},{h}]")
+        helpers.assert_close(dv[sl], rdv, f"dv[{b},{h}]")
+    # a second call on the same workspace-free path gives the same dK, dV bit for bit (work counter reset)
+    dq2, dk2, dv2 = api.fmha_backward(d_o, q, k, v, o, lse, seqlens=lens, p_drop=p, seed=9, offset=4, status=status)
+    assert torch.equal(dk2, dk) and torch.equal(dv2, dv)
+    helpers.assert_close(dq2, dq.float(), "dq repeated")
+
+
 def test_masked_out_key_tiles_get_zero_gradients(cuda_device):
     B, H, S, D = 2, 2, 384, 64
     q, k, v, d_o, _ = helpers.randn_like_config(B, H, S, S, D, torch.float16, seed=3, device=cuda_device)
