@@ -190,6 +190,15 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_slot;
   const WaitCtx wctx{abort_flag, a.status};
+#ifdef FMHA_TIMELINE
+  // Development aid (not compiled into the library): one CTA records clock64() stamps behind its status words.
+  long long* tl_buf = reinterpret_cast<long long*>(a.status + 16);
+  const bool tl_cta = (blockIdx.x == 1 && blockIdx.y == 3 && blockIdx.z == gridDim.z / 2);
+#define FTL(slot) do { if (tl_cta && (threadIdx.x & 31) == 0 && (slot) < 256) tl_buf[slot] = clock64(); } while (0)
+#else
+#define FTL(slot) do { } while (0)
+#endif
+  if (threadIdx.x == 64) FTL(255);
 
   if (warp == 0) {
     // ============================ TMA producer ======================================
@@ -242,7 +251,9 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
         else umma_ss_x8(tS, aq, bk, kIdescQK, 0u);
         umma_commit_elect(k_empty + s);
         umma_commit_elect(s_full);
+        FTL(j * 16 + 0);
         mbar_wait(p_full, j & 1, wctx, kFPFull);
+        FTL(j * 16 + 1);
         mbar_wait(v_full + s, ph, wctx, kFVFull);
         tc_fence_after_sync();
         const uint32_t acc0 = (j > 0) ? 1u : 0u;
@@ -255,6 +266,7 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
           umma_ts_x4(tO, tS + 32u, 8u, b1, kIdescPV, 1u);
         }
         umma_commit_elect(v_empty + s);
+        FTL(j * 16 + 2);
       }
       umma_commit_elect(o_full);
     }
@@ -299,8 +311,10 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
           keepw[d * 4 + 3] = (draw.w & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
         }
       }
+      if (tid == 0) FTL(j * 16 + 7);
       mbar_wait(s_full, j & 1, wctx, kFSFull, 32);
       tc_fence_after_sync();
+      if (tid == 0) FTL(j * 16 + 8);
 
       // ---- sweep 1: row maximum --------------------------------------------------------
       float tile_max = -INFINITY;
@@ -336,6 +350,7 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
         if constexpr (!KEYADD) tile_max *= sl2;  // scale > 0: the maximum commutes with it
       }
 
+      if (tid == 0) FTL(j * 16 + 9);
       // ---- running reference maximum, lazy rescale of O ------------------------------------
       {
         float m_new = fmaxf(m_ref, tile_max);
@@ -358,6 +373,7 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
         m_ref = m_new;
       }
 
+      if (tid == 0) FTL(j * 16 + 10);
       // ---- sweep 2: exponentials, dropout, P (next chunk's load in flight) ----------------------
       {
         const float neg_m = -m_ref;
@@ -383,11 +399,13 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(p_full);
+      if (tid == 0) FTL(j * 16 + 11);
     }
 
     // ---- epilogue ------------------------------------------------------------------------
     mbar_wait(o_full, 0, wctx, kFOFull, 32);
     tc_fence_after_sync();
+    if (tid == 0) FTL(250);
     const float l_sum = sum2.x + sum2.y;
     const float out_scale = (DROP ? a.dropout_scale : 1.0f) / l_sum;
     if (a.lse != nullptr && row_ok) {
@@ -429,6 +447,7 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
         tma_store_commit();
       }
       tma_store_wait_read();  // the shared-memory source must outlive the copy; the writes finish on their own
+      FTL(251);
     }
   }
 
