@@ -119,6 +119,10 @@ typedef struct {
   int32_t flags;            /* FMHA_FLAG_* */
   int32_t* status;          /* optional device int32[4]: nonzero word 0 = in-kernel wait ran out */
   int32_t total_rows;       /* FMHA_MASK_CU_SEQLENS: rows of the packed tensors (= cu[B]) */
+  const int64_t* philox_offset_dev; /* optional device int64: its value (mod 2^32) is added to philox_offset by the
+                               kernel.  A call captured in a CUDA graph can then draw new bits on every replay:
+                               advance the device value between replays (and give forward and backward the
+                               same pointer).  Not supported together with dense masks / saved intermediates. */
 } fmha_fwd_params;
 
 enum {
@@ -150,6 +154,7 @@ typedef struct {
   int32_t flags;
   int32_t* status;
   int32_t total_rows;         /* FMHA_MASK_CU_SEQLENS: rows of the packed tensors (= cu[B]) */
+  const int64_t* philox_offset_dev; /* optional device int64 added to philox_offset, see fmha_fwd_params */
 } fmha_bwd_params;
 
 /* ---- entry points --------------------------------------------------------------- */

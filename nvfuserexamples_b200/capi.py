@@ -57,6 +57,7 @@ class FwdParams(C.Structure):
         ("keep_mask_out", C.c_void_p), ("debug_scores", C.c_void_p),
         ("flags", C.c_int32), ("status", C.c_void_p),
         ("total_rows", C.c_int32),
+        ("philox_offset_dev", C.c_void_p),
     ]
 
 
@@ -74,6 +75,7 @@ class BwdParams(C.Structure):
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("flags", C.c_int32), ("status", C.c_void_p),
         ("total_rows", C.c_int32),
+        ("philox_offset_dev", C.c_void_p),
     ]
 
 

@@ -73,7 +73,7 @@ struct BwdSmem {
   static constexpr int kOffBar = kOffMask + 2 * kTileN * 4;
   static constexpr int kNumBars = 6 + 2 * kKvBufs + 2 * kStages + 4;
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;
-  static constexpr int kBytes = kOffMisc + 16;
+  static constexpr int kBytes = kOffMisc + 32;
   static constexpr int kDynBytes = kBytes + 1024;
   static_assert(kDynBytes <= 232448, "shared memory budget of one CTA exceeded");
 };
@@ -249,6 +249,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(smem + L::kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kOffMisc + 4);
   volatile int* ring = reinterpret_cast<volatile int*>(smem + L::kOffMisc + 8);   // [2]
+  // Philox offset of this launch (launch parameter + optional device-resident value), read where a draw starts
+  volatile uint32_t* philox_off = reinterpret_cast<volatile uint32_t*>(smem + L::kOffMisc + 16);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -259,6 +261,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
+    *philox_off = a.philox_offset + (a.philox_offset_dev != nullptr ? static_cast<uint32_t>(*a.philox_offset_dev) : 0u);
     mbar_init(sdp_full, 1);
     mbar_init(sdp_free, kComputeThreads);
     mbar_init(pds_full, kComputeThreads);
@@ -756,9 +759,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
         // interleave) and before S and dP are needed
         [[maybe_unused]] uint32_t kw8[8];
         if constexpr (DROP) {
+          const uint32_t poff = *philox_off;
 #pragma unroll
           for (int d = 0; d < 2; ++d) {
-            const U4 draw = dropout_draw_keys(a.philox_keys, a.philox_offset, gbh, static_cast<uint32_t>(q_row),
+            const U4 draw = dropout_draw_keys(a.philox_keys, poff, gbh, static_cast<uint32_t>(q_row),
                                          static_cast<uint32_t>((k0 + cbase) / 16 + d));
             kw8[d * 4 + 0] = (draw.x & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
             kw8[d * 4 + 1] = (draw.y & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;

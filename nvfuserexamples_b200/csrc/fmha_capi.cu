@@ -152,7 +152,7 @@ using namespace fmha;
 
 extern "C" {
 
-int fmha_sm100_abi_version(void) { return 2; }
+int fmha_sm100_abi_version(void) { return 3; }
 
 int fmha_sm100_last_cuda_error(void) { return g_last_cuda_error; }
 
@@ -200,6 +200,7 @@ int fmha_sm100_fwd(const fmha_fwd_params* p, void* stream) {
                       p->dropout_kind == FMHA_DROPOUT_DENSE || p->save_softmax || p->save_dropout ||
                       p->keep_mask_out || p->debug_scores;
   if (packed && legacy) return FMHA_ERR_UNSUPPORTED;   // packed batches: production kernel only
+  if (p->philox_offset_dev != nullptr && legacy) return FMHA_ERR_UNSUPPORTED;   // likewise the device-resident offset
   // tensor-map extents: [B, H, S, D], or one "batch" of total_rows rows for a packed batch
   const int mB = packed ? 1 : p->B, mSq = packed ? p->total_rows : p->S_q, mSk = packed ? p->total_rows : p->S_k;
   if ((rc = make_tmap(&a.tm_q, sanitized(p->q, mB, p->H, mSq, p->D), p->dtype, mB, p->H, mSq, p->D, kTileM))) return rc;
@@ -227,6 +228,7 @@ int fmha_sm100_fwd(const fmha_fwd_params* p, void* stream) {
   a.philox_seed = p->philox_seed;
   a.philox_keys = philox_round_keys(p->philox_seed);
   a.philox_offset = static_cast<uint32_t>(p->philox_offset);
+  a.philox_offset_dev = reinterpret_cast<const long long*>(p->philox_offset_dev);
   a.philox_bh_offset = p->philox_bh_offset;
   a.save_softmax = p->save_softmax;
   a.save_dropout = p->save_dropout;
@@ -341,6 +343,7 @@ int fmha_sm100_bwd(const fmha_bwd_params* p, void* stream_) {
   a.philox_seed = p->philox_seed;
   a.philox_keys = philox_round_keys(p->philox_seed);
   a.philox_offset = static_cast<uint32_t>(p->philox_offset);
+  a.philox_offset_dev = reinterpret_cast<const long long*>(p->philox_offset_dev);
   a.philox_bh_offset = p->philox_bh_offset;
   a.status = p->status;
 

@@ -136,6 +136,9 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
   uint64_t* v_empty = v_full + ST;
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(smem + L::kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kOffMisc + 4);
+  // Philox offset of this launch: the launch parameter plus the optional device-resident value.  Kept in shared
+  // memory and read where a draw starts, so that it holds no register in between.
+  volatile uint32_t* philox_off = reinterpret_cast<volatile uint32_t*>(smem + L::kOffMisc + 8);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -165,6 +168,7 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
+    *philox_off = a.philox_offset + (a.philox_offset_dev != nullptr ? static_cast<uint32_t>(*a.philox_offset_dev) : 0u);
     mbar_init(q_full, 1);
     mbar_init(s_full, 1);
     mbar_init(p_full, 128);
@@ -302,9 +306,10 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
       [[maybe_unused]] uint32_t keepw[DROP ? TN / 4 : 1];
       if constexpr (DROP) {
         const uint32_t kb0 = static_cast<uint32_t>(col0 / 16);
+        const uint32_t poff = *philox_off;
 #pragma unroll
         for (int d = 0; d < TN / 16; ++d) {
-          const U4 draw = dropout_draw_keys(a.philox_keys, a.philox_offset, gbh, static_cast<uint32_t>(q_row), kb0 + d);
+          const U4 draw = dropout_draw_keys(a.philox_keys, poff, gbh, static_cast<uint32_t>(q_row), kb0 + d);
           keepw[d * 4 + 0] = (draw.x & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
           keepw[d * 4 + 1] = (draw.y & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
           keepw[d * 4 + 2] = (draw.z & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;

@@ -41,6 +41,7 @@ struct FwdArgs {
   uint64_t philox_seed;
   PhiloxKeys philox_keys;  // round keys of philox_seed
   uint32_t philox_offset;
+  const long long* philox_offset_dev;   // optional device value added to philox_offset (production kernel)
   int philox_bh_offset;
   void* save_softmax;
   void* save_dropout;
@@ -79,6 +80,7 @@ struct BwdArgs {
   uint64_t philox_seed;
   PhiloxKeys philox_keys;  // round keys of philox_seed
   uint32_t philox_offset;
+  const long long* philox_offset_dev;   // optional device value added to philox_offset
   int philox_bh_offset;
   int* status;
 };

@@ -207,10 +207,20 @@ MaskArg resolve_mask(const c10::optional<at::Tensor>& mask, const c10::optional<
   return m;
 }
 
+// Optional device-resident Philox offset: a one-element int64 CUDA tensor whose value the kernels add to
+// `offset`, so that a captured CUDA graph draws new bits whenever the tensor is advanced between replays.
+const int64_t* offset_tensor_ptr(const c10::optional<at::Tensor>& t, const at::Tensor& q) {
+  if (!t.has_value()) return nullptr;
+  TORCH_CHECK(t->device() == q.device(), "mha_manual: offset_tensor is on a different device");
+  TORCH_CHECK(t->scalar_type() == at::kLong && t->numel() == 1, "mha_manual: offset_tensor must hold one int64");
+  return t->data_ptr<int64_t>();
+}
+
 std::tuple<at::Tensor, at::Tensor> fmha_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
                                             const c10::optional<at::Tensor>& mask,
                                             const c10::optional<at::Tensor>& seqlens, double p_drop, int64_t seed,
-                                            int64_t offset, c10::optional<double> scale, int64_t bh_offset) {
+                                            int64_t offset, c10::optional<double> scale, int64_t bh_offset,
+                                            const c10::optional<at::Tensor>& offset_tensor) {
   const View4 vq = view4(q, "q"), vk = view4(k, "k"), vv = view4(v, "v");
   check_same(q, k, "k");
   check_same(q, v, "v");
@@ -238,6 +248,7 @@ std::tuple<at::Tensor, at::Tensor> fmha_fwd(const at::Tensor& q, const at::Tenso
     p.p_drop = static_cast<float>(p_drop);
     p.philox_seed = static_cast<uint64_t>(seed);
     p.philox_offset = static_cast<uint64_t>(offset);
+    p.philox_offset_dev = offset_tensor_ptr(offset_tensor, q);
   }
   p.philox_bh_offset = static_cast<int32_t>(bh_offset);
   p.status = status_block(dev).data_ptr<int32_t>();
@@ -250,7 +261,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_bwd(const at::Tensor& d_o, c
                                                         const c10::optional<at::Tensor>& mask,
                                                         const c10::optional<at::Tensor>& seqlens, double p_drop,
                                                         int64_t seed, int64_t offset, c10::optional<double> scale,
-                                                        int64_t bh_offset) {
+                                                        int64_t bh_offset, const c10::optional<at::Tensor>& offset_tensor) {
   const View4 vq = view4(q, "q"), vk = view4(k, "k"), vv = view4(v, "v"), vo = view4(o, "o");
   at::Tensor d_o_c = d_o.stride(-1) == 1 ? d_o : d_o.contiguous();
   const View4 vdo = view4(d_o_c, "d_o");
@@ -284,6 +295,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_bwd(const at::Tensor& d_o, c
     p.p_drop = static_cast<float>(p_drop);
     p.philox_seed = static_cast<uint64_t>(seed);
     p.philox_offset = static_cast<uint64_t>(offset);
+    p.philox_offset_dev = offset_tensor_ptr(offset_tensor, q);
   }
   p.philox_bh_offset = static_cast<int32_t>(bh_offset);
   size_t ws = 0;
@@ -451,7 +463,7 @@ class FmhaFunction : public torch::autograd::Function<FmhaFunction> {
   static at::Tensor forward(torch::autograd::AutogradContext* ctx, const at::Tensor& q, const at::Tensor& k,
                             const at::Tensor& v, const c10::optional<at::Tensor>& mask,
                             const c10::optional<at::Tensor>& seqlens, double p_drop, int64_t seed, int64_t offset,
-                            c10::optional<double> scale) {
+                            c10::optional<double> scale, const c10::optional<at::Tensor>& offset_tensor) {
     at::AutoDispatchBelowADInplaceOrView guard;
     // through the dispatcher, so that fake / meta tensors reach the shape-only kernels
     static auto op = c10::Dispatcher::singleton()
@@ -459,10 +471,14 @@ class FmhaFunction : public torch::autograd::Function<FmhaFunction> {
                          .typed<std::tuple<at::Tensor, at::Tensor>(const at::Tensor&, const at::Tensor&, const at::Tensor&,
                                                                    const c10::optional<at::Tensor>&,
                                                                    const c10::optional<at::Tensor>&, double, int64_t, int64_t,
-                                                                   c10::optional<double>, int64_t)>();
-    auto [o, lse] = op.call(q, k, v, mask, seqlens, p_drop, seed, offset, scale, 0);
+                                                                   c10::optional<double>, int64_t,
+                                                                   const c10::optional<at::Tensor>&)>();
+    auto [o, lse] = op.call(q, k, v, mask, seqlens, p_drop, seed, offset, scale, 0, offset_tensor);
+    // The backward pass must see the value the forward pass saw, even if the caller advances the tensor in
+    // between: it gets a private copy.
     ctx->save_for_backward({q, k, v, o, lse, mask.has_value() ? *mask : at::Tensor(),
-                            seqlens.has_value() ? *seqlens : at::Tensor()});
+                            seqlens.has_value() ? *seqlens : at::Tensor(),
+                            offset_tensor.has_value() ? offset_tensor->clone() : at::Tensor()});
     ctx->saved_data["p_drop"] = p_drop;
     ctx->saved_data["seed"] = seed;
     ctx->saved_data["offset"] = offset;
@@ -476,6 +492,8 @@ class FmhaFunction : public torch::autograd::Function<FmhaFunction> {
     c10::optional<at::Tensor> mask, seqlens;
     if (saved[5].defined()) mask = saved[5];
     if (saved[6].defined()) seqlens = saved[6];
+    c10::optional<at::Tensor> offset_tensor;
+    if (saved[7].defined()) offset_tensor = saved[7];
     c10::optional<double> scale;
     if (ctx->saved_data["has_scale"].toBool()) scale = ctx->saved_data["scale"].toDouble();
     static auto op =
@@ -484,11 +502,11 @@ class FmhaFunction : public torch::autograd::Function<FmhaFunction> {
             .typed<std::tuple<at::Tensor, at::Tensor, at::Tensor>(
                 const at::Tensor&, const at::Tensor&, const at::Tensor&, const at::Tensor&, const at::Tensor&, const at::Tensor&,
                 const c10::optional<at::Tensor>&, const c10::optional<at::Tensor>&, double, int64_t, int64_t,
-                c10::optional<double>, int64_t)>();
+                c10::optional<double>, int64_t, const c10::optional<at::Tensor>&)>();
     auto [dq, dk, dv] = op.call(grads[0], saved[0], saved[1], saved[2], saved[3], saved[4], mask, seqlens,
                                 ctx->saved_data["p_drop"].toDouble(), ctx->saved_data["seed"].toInt(),
-                                ctx->saved_data["offset"].toInt(), scale, 0);
-    return {dq, dk, dv, at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor()};
+                                ctx->saved_data["offset"].toInt(), scale, 0, offset_tensor);
+    return {dq, dk, dv, at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor()};
   }
 };
 
@@ -537,8 +555,9 @@ at::Tensor fmha_varlen_autograd(const at::Tensor& q, const at::Tensor& k, const 
 
 at::Tensor fmha_autograd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
                          const c10::optional<at::Tensor>& mask, const c10::optional<at::Tensor>& seqlens, double p_drop,
-                         int64_t seed, int64_t offset, c10::optional<double> scale) {
-  return FmhaFunction::apply(q, k, v, mask, seqlens, p_drop, seed, offset, scale);
+                         int64_t seed, int64_t offset, c10::optional<double> scale,
+                         const c10::optional<at::Tensor>& offset_tensor) {
+  return FmhaFunction::apply(q, k, v, mask, seqlens, p_drop, seed, offset, scale, offset_tensor);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -590,7 +609,7 @@ std::vector<at::Tensor> fmha_train_saveim_nvfuser_meta(const at::Tensor& input, 
 std::tuple<at::Tensor, at::Tensor> fmha_fwd_meta(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
                                                  const c10::optional<at::Tensor>& mask,
                                                  const c10::optional<at::Tensor>& seqlens, double p_drop, int64_t, int64_t offset,
-                                                 c10::optional<double>, int64_t) {
+                                                 c10::optional<double>, int64_t, const c10::optional<at::Tensor>&) {
   meta_check_qkv(q, k, v);
   const MetaDims dq = meta_dims(q, "q"), dk = meta_dims(k, "k");
   TORCH_CHECK(!(mask.has_value() && seqlens.has_value()), "mha_manual: pass either mask or seqlens, not both");
@@ -605,7 +624,8 @@ std::tuple<at::Tensor, at::Tensor> fmha_fwd_meta(const at::Tensor& q, const at::
 std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_bwd_meta(const at::Tensor& d_o, const at::Tensor& q, const at::Tensor& k,
                                                              const at::Tensor& v, const at::Tensor& o, const at::Tensor& lse,
                                                              const c10::optional<at::Tensor>&, const c10::optional<at::Tensor>&,
-                                                             double, int64_t, int64_t, c10::optional<double>, int64_t) {
+                                                             double, int64_t, int64_t, c10::optional<double>, int64_t,
+                                                             const c10::optional<at::Tensor>&) {
   meta_check_qkv(q, k, v);
   const MetaDims dq = meta_dims(q, "q");
   TORCH_CHECK(o.sizes() == q.sizes(), "mha_manual: o must have the shape of q");
@@ -647,12 +667,12 @@ TORCH_LIBRARY(mha_manual, m) {
   m.def("fmha_train_nvfuser(Tensor input, Tensor qk, Tensor v, Tensor pad_mask, Tensor dropout_mask) -> Tensor");
   m.def("fmha_train_saveim_nvfuser(Tensor input, Tensor qk, Tensor v, Tensor pad_mask, Tensor dropout_mask) -> Tensor[]");
   m.def("fmha_fwd(Tensor q, Tensor k, Tensor v, Tensor? mask=None, Tensor? seqlens=None, float p_drop=0.0, "
-        "int seed=0, int offset=0, float? scale=None, int bh_offset=0) -> (Tensor, Tensor)");
+        "int seed=0, int offset=0, float? scale=None, int bh_offset=0, Tensor? offset_tensor=None) -> (Tensor, Tensor)");
   m.def("fmha_bwd(Tensor d_o, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, Tensor? mask=None, "
-        "Tensor? seqlens=None, float p_drop=0.0, int seed=0, int offset=0, float? scale=None, int bh_offset=0) "
-        "-> (Tensor, Tensor, Tensor)");
+        "Tensor? seqlens=None, float p_drop=0.0, int seed=0, int offset=0, float? scale=None, int bh_offset=0, "
+        "Tensor? offset_tensor=None) -> (Tensor, Tensor, Tensor)");
   m.def("fmha(Tensor q, Tensor k, Tensor v, Tensor? mask=None, Tensor? seqlens=None, float p_drop=0.0, int seed=0, "
-        "int offset=0, float? scale=None) -> Tensor");
+        "int offset=0, float? scale=None, Tensor? offset_tensor=None) -> Tensor");
   m.def("fmha_varlen_fwd(Tensor q, Tensor k, Tensor v, Tensor cu_seqlens, int max_seqlen, float p_drop=0.0, int seed=0, "
         "int offset=0, float? scale=None) -> (Tensor, Tensor)");
   m.def("fmha_varlen_bwd(Tensor d_o, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, Tensor cu_seqlens, int max_seqlen, "

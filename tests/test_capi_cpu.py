@@ -24,7 +24,7 @@ def test_library_exports_every_declared_symbol():
 
 def test_abi_version_and_strerror():
     lib = capi.load()
-    assert lib.fmha_sm100_abi_version() == 2
+    assert lib.fmha_sm100_abi_version() == 3
     for code in range(0, 8):
         assert isinstance(capi.strerror(code), str) and capi.strerror(code)
     assert capi.strerror(capi.FMHA_OK) == "ok"

@@ -129,6 +129,44 @@ def test_operators_can_be_captured_in_a_cuda_graph(ops, cuda_device):
     ops.check_status()
 
 
+def test_device_resident_philox_offset_gives_new_masks_on_graph_replay(ops, cuda_device):
+    """offset_tensor: the kernels add its value to `offset`, so one captured graph draws the bits of
+    (seed, offset + value) for whatever value the tensor holds at replay time."""
+    B, H, S, D = 2, 4, 256, 64
+    q, k, v, d_o, lens = helpers.randn_like_config(B, H, S, S, D, torch.float16, seed=9, device=cuda_device)
+    off = torch.zeros(1, dtype=torch.int64, device=cuda_device)
+    eager = {}
+    for value in (0, 5):   # what the graph must reproduce: plain calls with offset 10 + value
+        o, lse = ops.fmha_fwd(q, k, v, None, lens, 0.25, 3, 10 + value)
+        eager[value] = (o, lse) + tuple(ops.fmha_bwd(d_o, q, k, v, o, lse, None, lens, 0.25, 3, 10 + value))
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream(device=cuda_device)
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            o, lse = ops.fmha_fwd(q, k, v, None, lens, 0.25, 3, 10, None, 0, off)
+            dq, dk, dv = ops.fmha_bwd(d_o, q, k, v, o, lse, None, lens, 0.25, 3, 10, None, 0, off)
+    torch.cuda.current_stream().wait_stream(side)
+    for value in (0, 5):
+        off.fill_(value)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(o, eager[value][0]) and torch.equal(lse, eager[value][1])
+        assert torch.equal(dk, eager[value][3]) and torch.equal(dv, eager[value][4])
+        helpers.assert_close(dq, eager[value][2].float(), "dq")
+    assert not torch.equal(eager[0][0], eager[5][0])   # the two offsets really drew different masks
+    # the autograd operator keeps the forward's value for its backward pass
+    qg = q.clone().requires_grad_(True)
+    off.fill_(5)
+    out = ops.fmha(qg, k, v, None, lens, 0.25, 3, 10, None, off)
+    off.fill_(99)
+    out.backward(d_o)
+    torch.cuda.synchronize()
+    assert torch.equal(out, eager[5][0])
+    helpers.assert_close(qg.grad, eager[5][2].float(), "dq via autograd")
+
+
 def test_operator_errors(ops, cuda_device):
     x = torch.zeros(2, 128, 64, dtype=torch.half, device=cuda_device)
     with pytest.raises(RuntimeError):
