@@ -344,7 +344,8 @@ void check_packed_qkv(const Packed& q, const Packed& k, const Packed& v, int64_t
 
 std::tuple<at::Tensor, at::Tensor> fmha_varlen_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
                                                    const at::Tensor& cu_seqlens, int64_t max_seqlen, double p_drop,
-                                                   int64_t seed, int64_t offset, c10::optional<double> scale) {
+                                                   int64_t seed, int64_t offset, c10::optional<double> scale,
+                                                   const c10::optional<at::Tensor>& offset_tensor) {
   const Packed vq = packed3(q, "q"), vk = packed3(k, "k"), vv = packed3(v, "v");
   check_same(q, k, "k");
   check_same(q, v, "v");
@@ -371,6 +372,7 @@ std::tuple<at::Tensor, at::Tensor> fmha_varlen_fwd(const at::Tensor& q, const at
     p.p_drop = static_cast<float>(p_drop);
     p.philox_seed = static_cast<uint64_t>(seed);
     p.philox_offset = static_cast<uint64_t>(offset);
+    p.philox_offset_dev = offset_tensor_ptr(offset_tensor, q);
   }
   p.status = status_block(dev).data_ptr<int32_t>();
   finish_call(fmha_sm100_fwd(&p, at::cuda::getCurrentCUDAStream(dev).stream()), "fmha_varlen_fwd", dev);
@@ -380,7 +382,8 @@ std::tuple<at::Tensor, at::Tensor> fmha_varlen_fwd(const at::Tensor& q, const at
 std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_varlen_bwd(const at::Tensor& d_o, const at::Tensor& q, const at::Tensor& k,
                                                                const at::Tensor& v, const at::Tensor& o, const at::Tensor& lse,
                                                                const at::Tensor& cu_seqlens, int64_t max_seqlen, double p_drop,
-                                                               int64_t seed, int64_t offset, c10::optional<double> scale) {
+                                                               int64_t seed, int64_t offset, c10::optional<double> scale,
+                                                               const c10::optional<at::Tensor>& offset_tensor) {
   const Packed vq = packed3(q, "q"), vk = packed3(k, "k"), vv = packed3(v, "v"), vo = packed3(o, "o");
   at::Tensor d_o_c = d_o.stride(-1) == 1 ? d_o : d_o.contiguous();
   const Packed vdo = packed3(d_o_c, "d_o");
@@ -414,6 +417,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_varlen_bwd(const at::Tensor&
     p.p_drop = static_cast<float>(p_drop);
     p.philox_seed = static_cast<uint64_t>(seed);
     p.philox_offset = static_cast<uint64_t>(offset);
+    p.philox_offset_dev = offset_tensor_ptr(offset_tensor, q);
   }
   size_t ws = 0;
   raise_if(fmha_sm100_bwd_workspace_bytes(&p, &ws), "fmha_bwd_workspace_bytes");
@@ -514,15 +518,16 @@ class FmhaVarlenFunction : public torch::autograd::Function<FmhaVarlenFunction> 
  public:
   static at::Tensor forward(torch::autograd::AutogradContext* ctx, const at::Tensor& q, const at::Tensor& k,
                             const at::Tensor& v, const at::Tensor& cu_seqlens, int64_t max_seqlen, double p_drop,
-                            int64_t seed, int64_t offset, c10::optional<double> scale) {
+                            int64_t seed, int64_t offset, c10::optional<double> scale,
+                            const c10::optional<at::Tensor>& offset_tensor) {
     at::AutoDispatchBelowADInplaceOrView guard;
     static auto op = c10::Dispatcher::singleton()
                          .findSchemaOrThrow("mha_manual::fmha_varlen_fwd", "")
                          .typed<std::tuple<at::Tensor, at::Tensor>(const at::Tensor&, const at::Tensor&, const at::Tensor&,
                                                                    const at::Tensor&, int64_t, double, int64_t, int64_t,
-                                                                   c10::optional<double>)>();
-    auto [o, lse] = op.call(q, k, v, cu_seqlens, max_seqlen, p_drop, seed, offset, scale);
-    ctx->save_for_backward({q, k, v, o, lse, cu_seqlens});
+                                                                   c10::optional<double>, const c10::optional<at::Tensor>&)>();
+    auto [o, lse] = op.call(q, k, v, cu_seqlens, max_seqlen, p_drop, seed, offset, scale, offset_tensor);
+    ctx->save_for_backward({q, k, v, o, lse, cu_seqlens, offset_tensor.has_value() ? offset_tensor->clone() : at::Tensor()});
     ctx->saved_data["max_seqlen"] = max_seqlen;
     ctx->saved_data["p_drop"] = p_drop;
     ctx->saved_data["seed"] = seed;
@@ -540,17 +545,21 @@ class FmhaVarlenFunction : public torch::autograd::Function<FmhaVarlenFunction> 
                          .findSchemaOrThrow("mha_manual::fmha_varlen_bwd", "")
                          .typed<std::tuple<at::Tensor, at::Tensor, at::Tensor>(
                              const at::Tensor&, const at::Tensor&, const at::Tensor&, const at::Tensor&, const at::Tensor&,
-                             const at::Tensor&, const at::Tensor&, int64_t, double, int64_t, int64_t, c10::optional<double>)>();
+                             const at::Tensor&, const at::Tensor&, int64_t, double, int64_t, int64_t, c10::optional<double>,
+                             const c10::optional<at::Tensor>&)>();
+    c10::optional<at::Tensor> offset_tensor;
+    if (saved[6].defined()) offset_tensor = saved[6];
     auto [dq, dk, dv] = op.call(grads[0], saved[0], saved[1], saved[2], saved[3], saved[4], saved[5],
                                 ctx->saved_data["max_seqlen"].toInt(), ctx->saved_data["p_drop"].toDouble(),
-                                ctx->saved_data["seed"].toInt(), ctx->saved_data["offset"].toInt(), scale);
-    return {dq, dk, dv, at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor()};
+                                ctx->saved_data["seed"].toInt(), ctx->saved_data["offset"].toInt(), scale, offset_tensor);
+    return {dq, dk, dv, at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor()};
   }
 };
 
 at::Tensor fmha_varlen_autograd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& cu_seqlens,
-                                int64_t max_seqlen, double p_drop, int64_t seed, int64_t offset, c10::optional<double> scale) {
-  return FmhaVarlenFunction::apply(q, k, v, cu_seqlens, max_seqlen, p_drop, seed, offset, scale);
+                                int64_t max_seqlen, double p_drop, int64_t seed, int64_t offset, c10::optional<double> scale,
+                                const c10::optional<at::Tensor>& offset_tensor) {
+  return FmhaVarlenFunction::apply(q, k, v, cu_seqlens, max_seqlen, p_drop, seed, offset, scale, offset_tensor);
 }
 
 at::Tensor fmha_autograd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
@@ -646,14 +655,14 @@ void meta_check_packed(const at::Tensor& q, const at::Tensor& k, const at::Tenso
 }
 std::tuple<at::Tensor, at::Tensor> fmha_varlen_fwd_meta(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
                                                         const at::Tensor& cu_seqlens, int64_t max_seqlen, double, int64_t, int64_t,
-                                                        c10::optional<double>) {
+                                                        c10::optional<double>, const c10::optional<at::Tensor>&) {
   meta_check_packed(q, k, v, cu_seqlens, max_seqlen);
   return {at::empty(q.sizes(), q.options()), at::empty({q.size(1), q.size(0)}, q.options().dtype(at::kFloat))};
 }
 std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_varlen_bwd_meta(const at::Tensor& d_o, const at::Tensor& q, const at::Tensor& k,
                                                                     const at::Tensor& v, const at::Tensor& o, const at::Tensor& lse,
                                                                     const at::Tensor& cu_seqlens, int64_t max_seqlen, double, int64_t,
-                                                                    int64_t, c10::optional<double>) {
+                                                                    int64_t, c10::optional<double>, const c10::optional<at::Tensor>&) {
   meta_check_packed(q, k, v, cu_seqlens, max_seqlen);
   TORCH_CHECK(o.sizes() == q.sizes() && d_o.sizes() == q.sizes(), "mha_manual: o and d_o must have the shape of q");
   TORCH_CHECK(lse.scalar_type() == at::kFloat && lse.numel() == q.size(0) * q.size(1), "mha_manual: lse must be float32 [H, total_rows]");
@@ -674,11 +683,11 @@ TORCH_LIBRARY(mha_manual, m) {
   m.def("fmha(Tensor q, Tensor k, Tensor v, Tensor? mask=None, Tensor? seqlens=None, float p_drop=0.0, int seed=0, "
         "int offset=0, float? scale=None, Tensor? offset_tensor=None) -> Tensor");
   m.def("fmha_varlen_fwd(Tensor q, Tensor k, Tensor v, Tensor cu_seqlens, int max_seqlen, float p_drop=0.0, int seed=0, "
-        "int offset=0, float? scale=None) -> (Tensor, Tensor)");
+        "int offset=0, float? scale=None, Tensor? offset_tensor=None) -> (Tensor, Tensor)");
   m.def("fmha_varlen_bwd(Tensor d_o, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, Tensor cu_seqlens, int max_seqlen, "
-        "float p_drop=0.0, int seed=0, int offset=0, float? scale=None) -> (Tensor, Tensor, Tensor)");
+        "float p_drop=0.0, int seed=0, int offset=0, float? scale=None, Tensor? offset_tensor=None) -> (Tensor, Tensor, Tensor)");
   m.def("fmha_varlen(Tensor q, Tensor k, Tensor v, Tensor cu_seqlens, int max_seqlen, float p_drop=0.0, int seed=0, "
-        "int offset=0, float? scale=None) -> Tensor");
+        "int offset=0, float? scale=None, Tensor? offset_tensor=None) -> Tensor");
   m.def("philox_dropout_mask(int B, int H, int S_q, int S_k, float p, int seed, int offset, int bh_offset=0, "
         "bool on_device=False) -> Tensor", philox_dropout_mask);
   m.def("check_status() -> ()", check_status);

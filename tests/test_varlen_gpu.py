@@ -140,4 +140,8 @@ def test_packed_autograd_operator(cuda_device):
     helpers.assert_close(q.grad, ref["dq"], "dq")
     helpers.assert_close(k.grad, ref["dk"], "dk")
     helpers.assert_close(v.grad, ref["dv"], "dv")
+    # the device-resident offset is added to the launch parameter: 1 + 3 draws the bits of offset 4
+    off = torch.full((1,), 3, dtype=torch.int64, device=cuda_device)
+    o2, _ = ops.fmha_varlen_fwd(q.detach(), k.detach(), v.detach(), cu, 384, 0.1, 77, 1, None, off)
+    assert torch.equal(o2, o.detach())
     ops.check_status()
