@@ -41,9 +41,9 @@ LEN_RANGE = (256, 512)
 P_DROP = 0.1
 METRIC = "fused MHA fwd+bwd TFLOP/s at BERT-large shape (executed flops)"
 # ncu capture of fmha_bwd_kernel<64,fp16,dropout> (profiles/bwd_kernel_b16_h16_s512_d64.md): at B=16 of this
-# workload dram__bytes_read.sum + dram__bytes_write.sum = 97.60 MB + 22.15 MB per launch; DRAM traffic of
+# workload dram__bytes_read.sum + dram__bytes_write.sum = 97.62 MB + 22.36 MB per launch; DRAM traffic of
 # the kernel is proportional to the batch (every CTA touches only its own head), so B=32 is twice that.
-BWD_KERNEL_DRAM_TRAFFIC_B16 = 97.60e6 + 22.15e6
+BWD_KERNEL_DRAM_TRAFFIC_B16 = 97.62e6 + 22.36e6
 
 
 def executed_flops(lens, h, s_q, d, mult, granule=128):
