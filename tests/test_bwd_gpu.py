@@ -78,6 +78,15 @@ def test_more_work_items_than_sms_spot_checked_against_the_oracle(cuda_device):
     helpers.assert_close(dq2, dq.float(), "dq repeated")
 
 
+@pytest.mark.parametrize("B,H,S_q,S_k,D", [(1, 1, 1, 1, 64), (1, 1, 5, 130, 64), (3, 1, 129, 1, 128), (1, 2, 1, 257, 128)])
+def test_backward_tiny_and_ragged_shapes(cuda_device, B, H, S_q, S_k, D):
+    _run(cuda_device, B, H, S_q, S_k, D, torch.float16, "none", 0.0, seed=14)
+    if S_k > 1:
+        # With a single key dQ is an exact cancellation (dS = dP - delta = 0); with dropout delta comes from O
+        # rounded to 16 bits, so the kernel's dQ is |dP| * 2^-11 instead of 0: outside a bar anchored at ref = 0.
+        _run(cuda_device, B, H, S_q, S_k, D, torch.float16, "seqlen", 0.25, seed=15)
+
+
 def test_masked_out_key_tiles_get_zero_gradients(cuda_device):
     B, H, S, D = 2, 2, 384, 64
     q, k, v, d_o, _ = helpers.randn_like_config(B, H, S, S, D, torch.float16, seed=3, device=cuda_device)

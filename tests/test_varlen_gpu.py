@@ -28,6 +28,8 @@ def per_sequence_oracle(q, k, v, d_o, lens, p_drop, seed, offset, max_len):
     ks = helpers.philox.keep_scale(p_drop) if p_drop > 0 else 1.0
     r0 = 0
     for b, n in enumerate(lens):
+        if n == 0:
+            continue
         sl = slice(r0, r0 + n)
         qb, kb, vb, dob = (x[sl].permute(1, 0, 2).unsqueeze(0).cpu() for x in (q, k, v, d_o))   # [1,H,n,D]
         keep = keep_all[b:b + 1, :, :n, :n] if keep_all is not None else None
@@ -109,6 +111,23 @@ def test_packed_batch_equals_the_padded_batch_on_its_valid_rows(cuda_device):
         assert torch.equal(res["o"][r0:r0 + n].permute(1, 0, 2), pad["o"][b, :, :n])
         assert torch.equal(res["lse"][:, r0:r0 + n], pad["lse"][b, :, :n])
         r0 += n
+
+
+def test_packed_batch_with_empty_sequences(cuda_device):
+    """Sequences of length zero own no rows and produce nothing; their neighbours are unaffected."""
+    lens = [0, 130, 0, 0, 40, 0]
+    H, D = 2, 64
+    q, k, v, d_o, cu = packed_batch(lens, H, D, torch.float16, seed=8, device=cuda_device)
+    status = torch.zeros(4, dtype=torch.int32, device=cuda_device)
+    res = capi.fwd_varlen(q, k, v, cu, 256, p_drop=0.1, seed=2, offset=1, status=status)
+    dq, dk, dv = capi.bwd_varlen(d_o, q, k, v, res["o"], res["lse"], cu, 256, p_drop=0.1, seed=2, offset=1, status=status)
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0, 0, 0]
+    ref = per_sequence_oracle(q, k, v, d_o, lens, 0.1, 2, 1, 256)
+    helpers.assert_close(res["o"], ref["o"], "o")
+    helpers.assert_close(dq, ref["dq"], "dq")
+    helpers.assert_close(dk, ref["dk"], "dk")
+    helpers.assert_close(dv, ref["dv"], "dv")
 
 
 def test_packed_batch_leaves_neighbouring_rows_alone(cuda_device):
