@@ -568,36 +568,29 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
       tc_fence_after_sync();
     };
 
-    // D = 128: dQ tile `tt` (rows from `row0` of the accumulator) -> shared memory (the idle P/dS
-    // buffers) -> one TMA reduce-add per 32-column group.  The additions are performed line by line
-    // by the TMA unit instead of 2048 scattered 16-byte atomics per tile, which occupied the
-    // compute warps for ~1500 cycles per tile.
+    // D = 128: every warp stages its own 32 rows x 32 columns of dQ tile `tt` (4 KB, 128-byte swizzle)
+    // in the idle P/dS buffers and its lane 0 issues one TMA reduce-add for it.  The additions are
+    // performed line by line by the TMA unit instead of 2048 scattered 16-byte atomics per tile, which
+    // occupied the compute warps for ~1500 cycles per tile, and no warp waits for another one here.
     auto dq_readout_tma = [&](int tt, int row0) {
       wait_all(dq_full, tt & 1, kSiteDqFull);
       uint32_t r[DQ];
 #pragma unroll
-      for (int c = 0; c < DQ / 16; ++c) {
-        uint32_t t16[16];
-        tmem_ld16(tmem_base + lane_addr + kColdQ + cq * DQ + c * 16, t16);
-        tmem_wait_ld();
-#pragma unroll
-        for (int k = 0; k < 16; ++k) r[c * 16 + k] = t16[k];
-      }
+      for (int c = 0; c < DQ / 16; ++c)
+        tmem_ld16(tmem_base + lane_addr + kColdQ + cq * DQ + c * 16, *reinterpret_cast<uint32_t(*)[16]>(r + c * 16));
+      tmem_wait_ld();
       tc_fence_before_sync();
       mbar_arrive(dq_free);                          // the dQ columns may be overwritten
-      {
-        // this thread's DQ floats of row `row`: sub-tile (cq*DQ)/32, 16-byte chunks from ((cq*DQ)%32)/4
-        const uint32_t tile = smem_u32(sDQ + ((cq * DQ) / 32) * 16384);
-        const int chunk0 = ((cq * DQ) % 32) / 4;
+      uint8_t* stage = sDQ + cw * 4096;
+      const uint32_t rowaddr = smem_u32(stage) + lane * 128;
+      const uint32_t sw = lane & 7;                  // 128-byte swizzle: 16-byte chunk ^= row mod 8
 #pragma unroll
-        for (int q = 0; q < DQ / 4; ++q)
-          sts128(tile + sw128_offset(row, chunk0 + q), r[q * 4], r[q * 4 + 1], r[q * 4 + 2], r[q * 4 + 3]);
-      }
+      for (int q = 0; q < DQ / 4; ++q)
+        sts128(rowaddr + ((q ^ sw) << 4), r[q * 4], r[q * 4 + 1], r[q * 4 + 2], r[q * 4 + 3]);
       fence_proxy_async_smem();
-      named_bar_sync(3, kComputeThreads);
-      if (tid == 0 && *abort_flag == 0) {
-#pragma unroll
-        for (int g = 0; g < D / 32; ++g) tma_reduce_add_2d(&a.tm_dq, sDQ + g * 16384, g * 32, row0);
+      __syncwarp();
+      if (lane == 0 && *abort_flag == 0) {
+        tma_reduce_add_2d(&a.tm_dq, stage, cq * DQ, row0 + quad * 32);
         tma_store_commit();
       }
     };
@@ -704,7 +697,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
         } else {
           // the P/dS buffers may still be read by the previous tile's MMAs and dQ reduce
           if (t > 0) {
-            if (tid == 0) tma_store_wait_read();
+            if (lane == 0) tma_store_wait_read();
             named_bar_sync(2, kComputeThreads);
           }
           store_dkdv(cur.id, false);
@@ -844,7 +837,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
         } else {
           // D = 128: the previous tile's dQ was staged in the P/dS buffers; the reduce must have read them.
           if (t > 0) {
-            if (tid == 0) tma_store_wait_read();
+            if (lane == 0) tma_store_wait_read();
             named_bar_sync(2, kComputeThreads);
           }
         }
@@ -898,7 +891,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
       if constexpr (OWNSTAGE) {
         own_stage_free();
       } else {
-        if (tid == 0) tma_store_wait_read();   // the last dQ reduce has read the P/dS buffers
+        if (lane == 0) tma_store_wait_read();  // the last dQ reduces have read the P/dS buffers
         named_bar_sync(2, kComputeThreads);
       }
       store_dkdv(prev_id, true);

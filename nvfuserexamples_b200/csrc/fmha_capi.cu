@@ -62,16 +62,16 @@ static int make_tmap(CUtensorMap* out, const fmha_tensor4& t, int dtype, int B, 
   return FMHA_OK;
 }
 
-// Tensor map of the fp32 dQ accumulator [rows, D].  D = 128: {32 x 128} boxes with 128-byte swizzle (one
-// reduce per 32-column group of a whole tile).  D = 64: {16 x 32} boxes with 64-byte swizzle, one per compute
-// warp (its 32 rows x 16 columns), so that no CTA-wide barrier is needed around the staging buffer.
+// Tensor map of the fp32 dQ accumulator [rows, D].  One box per compute warp, so that no CTA-wide barrier is
+// needed around the staging buffer: its 32 rows x 16 columns with 64-byte swizzle at D = 64, its 32 rows x
+// 32 columns with 128-byte swizzle at D = 128.
 static int make_tmap_accum(CUtensorMap* out, float* ptr, uint64_t rows, int D) {
   auto enc = get_encode_fn();
   if (enc == nullptr) return FMHA_ERR_LAUNCH;
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(rows)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(D) * 4};
-  const bool per_warp = (D == 64);
-  const cuuint32_t box[2] = {per_warp ? 16u : 32u, per_warp ? 32u : static_cast<cuuint32_t>(kTileM)};
+  const bool per_warp = (D == 64);   // box = one warp's slice: 32 rows x 16 columns (D = 64) or x 32 (D = 128)
+  const cuuint32_t box[2] = {per_warp ? 16u : 32u, 32u};
   const cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    per_warp ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
