@@ -302,7 +302,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
   // Development aid (not compiled into the library): CTA 0 records clock64() stamps after its
   // status words; TL(slot) is issued by the MMA warp and by the first compute thread.
   long long* tl_buf = reinterpret_cast<long long*>(a.status + 16);
-  const bool tl_cta = (blockIdx.x == 0);
+  const bool tl_cta = (a.status != nullptr && blockIdx.x == 0);
 #define TL(slot) do { if (tl_cta && lane == 0 && (slot) < 256) tl_buf[slot] = clock64(); } while (0)
 #else
 #define TL(slot) do { } while (0)

@@ -197,7 +197,7 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
 #ifdef FMHA_TIMELINE
   // Development aid (not compiled into the library): one CTA records clock64() stamps behind its status words.
   long long* tl_buf = reinterpret_cast<long long*>(a.status + 16);
-  const bool tl_cta = (blockIdx.x == 1 && blockIdx.y == 3 && blockIdx.z == gridDim.z / 2);
+  const bool tl_cta = (a.status != nullptr && blockIdx.x == 1 && blockIdx.y == 3 && blockIdx.z == gridDim.z / 2);
 #define FTL(slot) do { if (tl_cta && (threadIdx.x & 31) == 0 && (slot) < 256) tl_buf[slot] = clock64(); } while (0)
 #else
 #define FTL(slot) do { } while (0)
