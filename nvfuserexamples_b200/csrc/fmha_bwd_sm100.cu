@@ -96,6 +96,7 @@ struct PrepArgs {
 
 template <bool BF16>
 __global__ void __launch_bounds__(256) bwd_prepare_kernel(const PrepArgs a) {
+  griddep_wait();
   // grid = (B*H, blocks of 32 rows); 8 threads per row (D = 64: 8 elements each; D = 128: 16 each).
   // The head index comes from the grid, so no thread divides 64-bit indices.
   const int per = a.D / 8;
@@ -156,6 +157,7 @@ struct FinishArgs {
 
 template <bool BF16>
 __global__ void __launch_bounds__(256) bwd_finish_kernel(const FinishArgs a) {
+  griddep_wait();
   // grid = (B*H, row blocks); one thread converts 8 consecutive elements, D/8 threads per row
   const int per_row = a.D / 8;
   const int part = threadIdx.x % per_row;
@@ -210,6 +212,7 @@ struct BwdItem {
 // PACKED: FMHA_MASK_CU_SEQLENS; a template parameter so that the padded kernels carry none of its bookkeeping.
 template <int D, bool BF16, bool KEYADD, bool DROP, bool PACKED = false>
 __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_constant__ BwdArgs a) {
+  griddep_wait();
   using L = BwdSmem<D>;
   constexpr int ST = L::kStages;
   constexpr int KV = L::kKvBufs;
@@ -939,8 +942,8 @@ static int launch_bwd_impl(const BwdArgs& a, cudaStream_t stream) {
   }
   const int64_t items = static_cast<int64_t>((a.S_k + kTileN - 1) / kTileN) * a.H * a.B;
   const int grid = static_cast<int>(items < sms ? items : sms);   // one persistent CTA per SM
-  kfn<<<grid, kBwdThreads, L::kDynBytes, stream>>>(a);
-  return static_cast<int>(cudaGetLastError());
+  const cudaError_t e = launch_overlapped(kfn, dim3(grid), dim3(kBwdThreads), L::kDynBytes, stream, a);
+  return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
 }
 
 int launch_bwd(const BwdArgs& a, int D, int dtype, cudaStream_t stream) {
@@ -993,9 +996,9 @@ int launch_bwd_prepare(const void* o, const fmha_tensor4& ot, const fmha_tensor4
   p.B = B; p.H = H; p.S_q = S_q; p.S_q_pad = S_q_pad; p.D = D;
   p.delta = delta; p.dq_accum = dq_accum; p.work_counter = work_counter; p.cu_seqlens = cu_seqlens;
   const dim3 grid(static_cast<unsigned>(B) * H, static_cast<unsigned>((S_q_pad + 31) / 32));
-  if (dtype == FMHA_DTYPE_BF16) bwd_prepare_kernel<true><<<grid, 256, 0, stream>>>(p);
-  else bwd_prepare_kernel<false><<<grid, 256, 0, stream>>>(p);
-  return static_cast<int>(cudaGetLastError());
+  const cudaError_t e = launch_overlapped(dtype == FMHA_DTYPE_BF16 ? bwd_prepare_kernel<true> : bwd_prepare_kernel<false>, grid,
+                                          dim3(256), 0, stream, p);
+  return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
 }
 
 int launch_bwd_finish(const float* dq_accum, const fmha_tensor4& dq, int B, int H, int S_q, int S_q_pad, int D, int dtype,
@@ -1006,9 +1009,9 @@ int launch_bwd_finish(const float* dq_accum, const fmha_tensor4& dq, int B, int 
   f.B = B; f.H = H; f.S_q = S_q; f.S_q_pad = S_q_pad; f.D = D; f.scale = scale; f.cu_seqlens = cu_seqlens;
   const int rows_per_block = 256 / (D / 8);
   const dim3 grid(static_cast<unsigned>(B) * H, static_cast<unsigned>((S_q + rows_per_block - 1) / rows_per_block));
-  if (dtype == FMHA_DTYPE_BF16) bwd_finish_kernel<true><<<grid, 256, 0, stream>>>(f);
-  else bwd_finish_kernel<false><<<grid, 256, 0, stream>>>(f);
-  return static_cast<int>(cudaGetLastError());
+  const cudaError_t e = launch_overlapped(dtype == FMHA_DTYPE_BF16 ? bwd_finish_kernel<true> : bwd_finish_kernel<false>, grid,
+                                          dim3(256), 0, stream, f);
+  return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
 }
 
 }  // namespace fmha

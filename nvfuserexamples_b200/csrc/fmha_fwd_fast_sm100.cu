@@ -110,6 +110,7 @@ __device__ __forceinline__ void softmax_chunk(const uint32_t (&r)[32], int cbase
 // template parameter so that the padded kernels carry none of its bookkeeping in registers.
 template <int D, bool BF16, bool KEYADD, bool DROP, bool PACKED = false>
 __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_fwd_fast_kernel(const __grid_constant__ FwdArgs a) {
+  griddep_wait();
   using L = FastSmem<D>;
   constexpr int ST = L::kStages;
   constexpr int TN = L::TN;
@@ -481,8 +482,8 @@ static int launch_fast_impl(const FwdArgs& a, cudaStream_t stream) {
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   dim3 grid((a.S_q + kTileM - 1) / kTileM, a.H, a.B);
-  kfn<<<grid, kThreads, L::kDynBytes, stream>>>(a);
-  return static_cast<int>(cudaGetLastError());
+  const cudaError_t e = launch_overlapped(kfn, grid, dim3(kThreads), L::kDynBytes, stream, a);
+  return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
 }
 
 int launch_fwd_fast(const FwdArgs& a, int D, int dtype, cudaStream_t stream) {

@@ -71,6 +71,7 @@ struct FwdSmem {
 
 template <int D, bool BF16, bool LEGACY, bool PSMEM>
 __global__ void __launch_bounds__(kFwdThreads, 1) fmha_fwd_kernel(const __grid_constant__ FwdArgs a) {
+  griddep_wait();
   using L = FwdSmem<D, PSMEM>;
   constexpr int ST = L::kStages;
   constexpr int kTmemCols = 256;
@@ -562,8 +563,8 @@ static int launch_fwd_impl(const FwdArgs& a, cudaStream_t stream) {
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   dim3 grid((a.S_q + kTileM - 1) / kTileM, a.H, a.B);
-  kfn<<<grid, kFwdThreads, L::dyn_bytes(a.mask_tiles), stream>>>(a);
-  return static_cast<int>(cudaGetLastError());
+  const cudaError_t e = launch_overlapped(kfn, grid, dim3(kFwdThreads), L::dyn_bytes(a.mask_tiles), stream, a);
+  return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
 }
 
 int launch_fwd(const FwdArgs& a, int D, int dtype, bool legacy, bool p_via_smem, cudaStream_t stream) {

@@ -94,4 +94,23 @@ int launch_bwd_prepare(const void* o, const fmha_tensor4& ot, const fmha_tensor4
 int launch_bwd_finish(const float* dq_accum, const fmha_tensor4& dq, int B, int H, int S_q, int S_q_pad, int D, int dtype,
                       float scale, const int* cu_seqlens, cudaStream_t stream);
 
+// Launches `kernel` with programmatic stream serialization: its CTAs may be scheduled while the previous
+// kernel of the stream drains (which hides the launch latency between the kernels of a training step); the
+// kernel itself calls griddep_wait() before it touches global memory, so stream order is preserved.
+template <typename Arg>
+inline cudaError_t launch_overlapped(void (*kernel)(Arg), dim3 grid, dim3 block, size_t smem_bytes, cudaStream_t stream,
+                                     const Arg& arg) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, arg);
+}
+
 }  // namespace fmha

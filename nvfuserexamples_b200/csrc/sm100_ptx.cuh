@@ -181,6 +181,12 @@ __device__ __forceinline__ void tma_reduce_add_2d(const void* tmap, const void* 
       ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
       : "memory");
 }
+// First statement of every kernel that is launched with programmatic stream serialization (see
+// launch_overlapped): returns once the preceding kernels of the stream have completed and their
+// writes are visible.  A no-op for a launch without that attribute.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// (An explicit griddepcontrol.launch_dependents at the top of the kernels was measured 2 % slower: the next
+// grid's CTAs then take multiprocessors while this grid's last wave still needs them.)
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Waits until the shared-memory source of every committed store has been read.
 __device__ __forceinline__ void tma_store_wait_read() {
