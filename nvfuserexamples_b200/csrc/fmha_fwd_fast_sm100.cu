@@ -111,6 +111,15 @@ __device__ __forceinline__ void softmax_chunk(const uint32_t (&r)[32], int cbase
 template <int D, bool BF16, bool KEYADD, bool DROP, bool PACKED = false>
 __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_fwd_fast_kernel(const __grid_constant__ FwdArgs a) {
   griddep_wait();
+#ifdef FMHA_TIMELINE
+  // Development aid (not compiled into the library): one CTA records clock64() stamps behind its status words.
+  long long* tl_buf = reinterpret_cast<long long*>(a.status + 16);
+  const bool tl_cta = (a.status != nullptr && blockIdx.x == 1 && blockIdx.y == 3 && blockIdx.z == gridDim.z / 2);
+#define FTL(slot) do { if (tl_cta && (threadIdx.x & 31) == 0 && (slot) < 256) tl_buf[slot] = clock64(); } while (0)
+#else
+#define FTL(slot) do { } while (0)
+#endif
+  if (threadIdx.x == 64) FTL(252);
   using L = FastSmem<D>;
   constexpr int ST = L::kStages;
   constexpr int TN = L::TN;
@@ -195,14 +204,6 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_slot;
   const WaitCtx wctx{abort_flag, a.status};
-#ifdef FMHA_TIMELINE
-  // Development aid (not compiled into the library): one CTA records clock64() stamps behind its status words.
-  long long* tl_buf = reinterpret_cast<long long*>(a.status + 16);
-  const bool tl_cta = (a.status != nullptr && blockIdx.x == 1 && blockIdx.y == 3 && blockIdx.z == gridDim.z / 2);
-#define FTL(slot) do { if (tl_cta && (threadIdx.x & 31) == 0 && (slot) < 256) tl_buf[slot] = clock64(); } while (0)
-#else
-#define FTL(slot) do { } while (0)
-#endif
   if (threadIdx.x == 64) FTL(255);
 
   if (warp == 0) {
@@ -466,6 +467,7 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
+    FTL(253);
   }
 }
 
