@@ -81,12 +81,15 @@ def fmha_forward(q, k, v, *, mask=None, seqlens=None, p_drop: float = 0.0, seed:
 
 
 def fmha_backward(d_o, q, k, v, o, lse, *, mask=None, seqlens=None, p_drop: float = 0.0, seed: int = 0, offset: int = 0,
-                  scale: Optional[float] = None, bh_offset: int = 0, workspace=None, status=None):
-    """dQ, dK, dV of fmha_forward; the probabilities are recomputed from `lse`."""
+                  scale: Optional[float] = None, bh_offset: int = 0, workspace=None, status=None, out=None):
+    """dQ, dK, dV of fmha_forward; the probabilities are recomputed from `lse`.  `out` = (dq, dk, dv) tensors to
+    write into, e.g. three views of one [B,S,3,H,D] gradient buffer of a fused QKV projection."""
     _require_cuda(d_o, q, k, v, o, lse, mask, seqlens)
+    if out is not None:
+        _require_cuda(*out)
     kind, m = _mask_args(mask, seqlens, q.shape[0], k.shape[-2])
     return capi.bwd(d_o, q, k, v, o, lse, mask_kind=kind, mask=m, p_drop=p_drop, seed=seed, offset=offset,
-                    bh_offset=bh_offset, scale=scale, workspace=workspace, status=status)
+                    bh_offset=bh_offset, scale=scale, workspace=workspace, status=status, out=out)
 
 
 def philox_dropout_mask(B: int, H: int, S_q: int, S_k: int, p: float, seed: int, offset: int, bh_offset: int = 0,

@@ -244,10 +244,11 @@ def bwd_workspace_bytes(p: BwdParams) -> int:
     return n.value
 
 
-def bwd(d_o, q, k, v, o, lse, *, workspace=None, **kw):
-    """Calls fmha_sm100_bwd on the current stream. Returns (dq, dk, dv)."""
+def bwd(d_o, q, k, v, o, lse, *, workspace=None, out=None, **kw):
+    """Calls fmha_sm100_bwd on the current stream. Returns (dq, dk, dv); `out` = (dq, dk, dv) to write into
+    (any strides with a contiguous last dimension, e.g. three views of one [B,S,3,H,D] buffer)."""
     import torch
-    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    dq, dk, dv = out if out is not None else (torch.empty_like(q), torch.empty_like(k), torch.empty_like(v))
     p = bwd_params(d_o, q, k, v, o, lse, dq, dk, dv, **kw)
     need = bwd_workspace_bytes(p)
     if workspace is None:

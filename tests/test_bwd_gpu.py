@@ -97,6 +97,34 @@ def test_masked_out_key_tiles_get_zero_gradients(cuda_device):
     assert dk[1].abs().sum() > 0 and dv[0, :, :100].abs().sum() > 0
 
 
+def test_backward_on_fused_qkv_projection_layout(cuda_device):
+    """Q, K, V are views of one [B,S,3,H,D] projection output, dO and O are [B,S,H,D], and the gradients
+    land in one [B,S,3,H,D] buffer: no permute or copy on either side of the operator."""
+    dev = cuda_device
+    B, S, H, D, p = 2, 320, 3, 64, 0.1
+    g = torch.Generator().manual_seed(12)
+    qkv = torch.randn(B, S, 3, H, D, generator=g).half().to(dev)
+    d_o = (torch.randn(B, S, H, D, generator=g).half().to(dev)).permute(0, 2, 1, 3)
+    q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+    lens = torch.tensor([320, 190], dtype=torch.int32, device=dev)
+    out = torch.empty(B, S, H, D, dtype=torch.half, device=dev).permute(0, 2, 1, 3)
+    o, lse = api.fmha_forward(q, k, v, seqlens=lens, p_drop=p, seed=3, offset=1, out=out)
+    assert o.data_ptr() == out.data_ptr()
+    dqkv = torch.full((B, S, 3, H, D), float("nan"), dtype=torch.half, device=dev)
+    dq, dk, dv = (dqkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+    got = api.fmha_backward(d_o, q, k, v, o, lse, seqlens=lens, p_drop=p, seed=3, offset=1, out=(dq, dk, dv))
+    assert [t.data_ptr() for t in got] == [dq.data_ptr(), dk.data_ptr(), dv.data_ptr()]
+    torch.cuda.synchronize()
+    assert not torch.isnan(dqkv).any()
+    qc, kc, vc, doc = q.contiguous(), k.contiguous(), v.contiguous(), d_o.contiguous()
+    ref, add, keep, ks = helpers.oracle_forward(qc, kc, vc, p_drop=p, seed=3, offset=1, lens=lens)
+    rdq, rdk, rdv = helpers.oracle_backward(qc, kc, vc, doc, add=add, keep=keep, ks=ks)
+    helpers.assert_close(o, ref["o"], "o")
+    helpers.assert_close(dq, rdq, "dq")
+    helpers.assert_close(dk, rdk, "dk")
+    helpers.assert_close(dv, rdv, "dv")
+
+
 def test_sharded_backward_equals_unsharded(cuda_device):
     B, H, S, D, p = 4, 2, 256, 64, 0.1
     q, k, v, d_o, lens = helpers.randn_like_config(B, H, S, S, D, torch.float16, seed=4, device=cuda_device)
