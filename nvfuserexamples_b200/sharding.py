@@ -3,7 +3,7 @@
 Every (batch, head) pair is an independent attention problem (the reference already maps
 B*H to blockIdx.y, shmsong/NvFuserExamples fmha/fmha_manual.cpp:279), so rank r of W takes a
 contiguous slice of the flattened B*H axis and no data crosses NVLink: inputs live on the
-shard's device and outputs stay sharded.  The only shared state is the Philox counter, which
+shard's device and outputs stay sharded (gather_outputs() is there for a caller that wants them whole).  The only shared state is the Philox counter, which
 uses the GLOBAL (b*H + h) index — `bh_offset` below — so a sharded run draws exactly the
 bits of the unsharded one.
 """
@@ -67,3 +67,21 @@ def shard_per_batch(v, shard: Shard):
     import torch
     idx = torch.arange(shard.bh_start, shard.bh_start + shard.bh_count, device=v.device) // H
     return v.index_select(0, idx)
+
+
+def gather_outputs(part, shard: Shard, B: int, group=None):
+    """Optional: the sharded outputs of every rank (what shard_tensor() would slice from the full tensor)
+    -> the full [B,H,...] tensor on every rank, by one all-gather over `group` (NCCL on GPUs, over
+    NVLink/NVSwitch; gloo on CPU).  The attention path itself never needs this exchange.  Shards may
+    differ by one (batch, head) pair, so every rank contributes a buffer padded to the largest shard."""
+    import torch
+    import torch.distributed as dist
+    n = B * shard.H
+    flat = part.reshape(shard.bh_count, *part.shape[2:])
+    width = -(-n // shard.world)
+    buf = flat.new_zeros((width,) + tuple(flat.shape[1:]))
+    buf[:shard.bh_count] = flat
+    bufs = [torch.empty_like(buf) for _ in range(shard.world)]
+    dist.all_gather(bufs, buf, group=group)
+    pieces = [b[:shard_bounds(n, shard.world, r)[1]] for r, b in enumerate(bufs)]
+    return torch.cat(pieces).reshape(B, shard.H, *flat.shape[1:])

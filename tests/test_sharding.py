@@ -65,11 +65,9 @@ def _rank_main(rank: int, world: int, port: int, ragged: bool, out_q):
         keep = keep.reshape(q.shape[0], q.shape[1], S, S)
         o = composite.attention_fp32(q, k, v, add_mask=composite.padding_add_mask(lens, S), keep=keep,
                                      keep_scale=philox.keep_scale(0.2))["o"].reshape(sh.bh_count, S, D)
-        # the only "collective" is the test's own gather of results; the data path has none
-        bufs = [None] * world
-        dist.all_gather_object(bufs, o)
+        # the only collective is the optional gather of results; the data path has none
+        full = sharding.gather_outputs(o.reshape(sh.bh_count, 1, S, D), sh, B).reshape(B * H, S, D)
         if rank == 0:
-            full = torch.cat(list(bufs))
             keep_all = torch.from_numpy(philox.dropout_keep_mask(5, 2, 0, B * H, S, S, 0.2).astype(np.float32)).reshape(B, H, S, S)
             ref = composite.attention_fp32(x["q"], x["k"], x["v"], add_mask=composite.padding_add_mask(x["lens"], S),
                                            keep=keep_all, keep_scale=philox.keep_scale(0.2))["o"].reshape(B * H, S, D)
