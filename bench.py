@@ -3,6 +3,7 @@
 BERT-large shape, on N GPUs of one node.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--scaling weak|strong]
+    python bench.py --configs      (kernel times of the other named configurations, one line each)
 
 One "step" is one forward and one backward pass of the hot path over one batch of synthetic
 input (B=32, H=16, S=512, D=64, fp16, valid lengths uniform in [256,512], Philox dropout 0.1).
@@ -409,6 +410,76 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+# The other named configurations (device-resident inputs, kernel time only): one line each with `--configs`.
+# The long-sequence case is the per-GPU shard (B=256 over 8 GPUs).
+NAMED_CONFIGS = [
+    ("bert_base_fwd", 32, 12, 512, 64, "float16", (256, 512), 0.1, False),
+    ("bert_large_fwd", 64, 16, 384, 64, "float16", (128, 384), 0.1, False),
+    ("bert_large_train", 32, 16, 512, 64, "float16", (256, 512), 0.1, True),
+    ("long_seq_train_shard_of_8", 32, 16, 2048, 128, "bfloat16", (1024, 2048), 0.0, True),
+]
+
+
+def run_configs(args):
+    """Times the forward (and backward) library calls of every named configuration on cuda:0 with CUDA
+    events and prints one JSON line per configuration: dense-equivalent and executed TFLOP/s."""
+    import ctypes as C
+
+    import torch
+
+    from nvfuserexamples_b200 import capi
+    from oracle import composite  # input recipe only
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device (the kernels have no CPU fallback)")
+    lib = capi.load()
+    sp = torch.cuda.current_stream().cuda_stream
+
+    def timed(fn, n):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / n
+
+    for name, b, h, s, d, dt, len_range, p, train in NAMED_CONFIGS:
+        dtype = getattr(torch, dt)
+        x = composite.make_inputs(b, h, s, d, dtype, len_range, 7, with_do=True)
+        q, k, v, d_o, lens = (x[n].cuda() for n in ("q", "k", "v", "d_o", "lens"))
+        kw = dict(mask_kind=capi.MASK_SEQLEN, mask=lens)
+        fkw = dict(kw)
+        if p > 0:
+            fkw.update(dropout_kind=capi.DROPOUT_PHILOX, p_drop=p, seed=1, offset=0)
+            kw.update(p_drop=p, seed=1, offset=0)
+        o = torch.empty_like(q)
+        res = capi.fwd(q, k, v, out=o, **fkw)
+        n = 30 if s <= 512 else 5     # every configuration's tensors exceed the L2 capacity
+        step_f = 64 if d == 64 else 128
+        f_ms = timed(lambda: capi.fwd(q, k, v, out=o, **fkw), n)
+        exe_f = executed_flops(lens.tolist(), h, s, d, 4.0, step_f)
+        line = {"config": name, "B": b, "H": h, "S": s, "D": d, "dtype": dt, "p_drop": p, "fwd_ms": round(f_ms, 4),
+                "fwd_dense_tflops": round(4.0 * b * h * s * s * d / f_ms / 1e9, 1),
+                "fwd_executed_tflops": round(exe_f / f_ms / 1e9, 1)}
+        if train:
+            dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+            bp = capi.bwd_params(d_o, q, k, v, res["o"], res["lse"], dq, dk, dv, **kw)
+            ws = torch.empty(capi.bwd_workspace_bytes(bp), dtype=torch.uint8, device="cuda")
+            bp.workspace, bp.workspace_bytes = ws.data_ptr(), ws.numel()
+            b_ms = timed(lambda: lib.fmha_sm100_bwd(C.byref(bp), sp), n)
+            exe_b = executed_flops(lens.tolist(), h, s, d, 10.0, 128)
+            line.update({"bwd_ms": round(b_ms, 4), "step_ms": round(f_ms + b_ms, 4),
+                         "step_dense_tflops": round(14.0 * b * h * s * s * d / (f_ms + b_ms) / 1e9, 1),
+                         "step_executed_tflops": round((exe_f + exe_b) / (f_ms + b_ms) / 1e9, 1)})
+        print(json.dumps(line), flush=True)
+        del x, q, k, v, d_o, o, res
+        torch.cuda.empty_cache()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -419,7 +490,11 @@ def main():
     ap.add_argument("--profile", choices=["fwd", "bwd"], default=None,
                     help="run three launches of one kernel path on a reduced batch and exit (for ncu)")
     ap.add_argument("--profile-batch", type=int, default=16)
+    ap.add_argument("--configs", action="store_true",
+                    help="kernel times of every named configuration on one GPU, one JSON line each (not the benchmark line)")
     args = ap.parse_args()
+    if args.configs:
+        return run_configs(args)
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
