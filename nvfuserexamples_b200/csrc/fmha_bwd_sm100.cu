@@ -58,8 +58,8 @@ struct BwdSmem {
   static constexpr int kStages = (D == 64) ? 2 : 1;   // Q / dO stages
   static constexpr int kPdsBufs = 1;                  // P / dS buffers
   // dQ tiles leave through shared memory + TMA reduce-add.  D = 64 has a dedicated 32 KB staging area
-  // (2 KB per compute warp); at D = 128 the 64 KB fp32 tile is staged in the P/dS buffers, which are
-  // idle between the completion of a tile's MMAs and the next tile's P/dS write.
+  // (2 KB per compute warp); at D = 128 the 64 KB fp32 tile is staged in the P/dS buffers (4 KB per
+  // compute warp), which are idle between the completion of a tile's MMAs and the next tile's P/dS write.
   static constexpr bool kDqStageOwn = (D == 64);
   static constexpr int kTileBytes = kTileM * D * 2;
   static constexpr int kOffK = 0;
