@@ -216,11 +216,11 @@ const int64_t* offset_tensor_ptr(const c10::optional<at::Tensor>& t, const at::T
   return t->data_ptr<int64_t>();
 }
 
-std::tuple<at::Tensor, at::Tensor> fmha_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
-                                            const c10::optional<at::Tensor>& mask,
-                                            const c10::optional<at::Tensor>& seqlens, double p_drop, int64_t seed,
-                                            int64_t offset, c10::optional<double> scale, int64_t bh_offset,
-                                            const c10::optional<at::Tensor>& offset_tensor) {
+// Forward into a caller-allocated `o` (any strides with a contiguous last axis); returns lse.
+at::Tensor fwd_into(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& o,
+                    const c10::optional<at::Tensor>& mask, const c10::optional<at::Tensor>& seqlens, double p_drop,
+                    int64_t seed, int64_t offset, c10::optional<double> scale, int64_t bh_offset,
+                    const c10::optional<at::Tensor>& offset_tensor, const char* what) {
   const View4 vq = view4(q, "q"), vk = view4(k, "k"), vv = view4(v, "v");
   check_same(q, k, "k");
   check_same(q, v, "v");
@@ -228,7 +228,6 @@ std::tuple<at::Tensor, at::Tensor> fmha_fwd(const at::Tensor& q, const at::Tenso
   const c10::cuda::CUDAGuard guard(q.device());
   const int dev = q.get_device();
   const MaskArg m = resolve_mask(mask, seqlens, vq.B, vk.S, q);
-  at::Tensor o = at::empty(q.sizes(), q.options());
   std::vector<int64_t> lse_shape{vq.B, vq.S};
   if (q.dim() == 4) lse_shape = {vq.B, vq.H, vq.S};
   at::Tensor lse = at::empty(lse_shape, q.options().dtype(at::kFloat));
@@ -252,16 +251,27 @@ std::tuple<at::Tensor, at::Tensor> fmha_fwd(const at::Tensor& q, const at::Tenso
   }
   p.philox_bh_offset = static_cast<int32_t>(bh_offset);
   p.status = status_block(dev).data_ptr<int32_t>();
-  finish_call(fmha_sm100_fwd(&p, at::cuda::getCurrentCUDAStream(dev).stream()), "fmha_fwd", dev);
+  finish_call(fmha_sm100_fwd(&p, at::cuda::getCurrentCUDAStream(dev).stream()), what, dev);
+  return lse;
+}
+
+std::tuple<at::Tensor, at::Tensor> fmha_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                                            const c10::optional<at::Tensor>& mask,
+                                            const c10::optional<at::Tensor>& seqlens, double p_drop, int64_t seed,
+                                            int64_t offset, c10::optional<double> scale, int64_t bh_offset,
+                                            const c10::optional<at::Tensor>& offset_tensor) {
+  TORCH_CHECK(q.is_cuda(), "mha_manual: q must be a CUDA tensor");
+  at::Tensor o = at::empty(q.sizes(), q.options());
+  at::Tensor lse = fwd_into(q, k, v, o, mask, seqlens, p_drop, seed, offset, scale, bh_offset, offset_tensor, "fmha_fwd");
   return {o, lse};
 }
 
-std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_bwd(const at::Tensor& d_o, const at::Tensor& q, const at::Tensor& k,
-                                                        const at::Tensor& v, const at::Tensor& o, const at::Tensor& lse,
-                                                        const c10::optional<at::Tensor>& mask,
-                                                        const c10::optional<at::Tensor>& seqlens, double p_drop,
-                                                        int64_t seed, int64_t offset, c10::optional<double> scale,
-                                                        int64_t bh_offset, const c10::optional<at::Tensor>& offset_tensor) {
+// Backward into caller-allocated dq, dk, dv (any strides with a contiguous last axis).
+void bwd_into(const at::Tensor& d_o, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& o,
+              const at::Tensor& lse, const at::Tensor& dq, const at::Tensor& dk, const at::Tensor& dv,
+              const c10::optional<at::Tensor>& mask, const c10::optional<at::Tensor>& seqlens, double p_drop, int64_t seed,
+              int64_t offset, c10::optional<double> scale, int64_t bh_offset,
+              const c10::optional<at::Tensor>& offset_tensor, const char* what) {
   const View4 vq = view4(q, "q"), vk = view4(k, "k"), vv = view4(v, "v"), vo = view4(o, "o");
   at::Tensor d_o_c = d_o.stride(-1) == 1 ? d_o : d_o.contiguous();
   const View4 vdo = view4(d_o_c, "d_o");
@@ -275,9 +285,6 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_bwd(const at::Tensor& d_o, c
   const int dev = q.get_device();
   const MaskArg m = resolve_mask(mask, seqlens, vq.B, vk.S, q);
   at::Tensor lse_c = lse.contiguous();
-  at::Tensor dq = at::empty(q.sizes(), q.options());
-  at::Tensor dk = at::empty(k.sizes(), k.options());
-  at::Tensor dv = at::empty(v.sizes(), v.options());
   const View4 vdq = view4(dq, "dq"), vdk = view4(dk, "dk"), vdv = view4(dv, "dv");
   fmha_bwd_params p{};
   p.struct_bytes = sizeof(p);
@@ -304,8 +311,60 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_bwd(const at::Tensor& d_o, c
   p.workspace = workspace.data_ptr();
   p.workspace_bytes = ws;
   p.status = status_block(dev).data_ptr<int32_t>();
-  finish_call(fmha_sm100_bwd(&p, at::cuda::getCurrentCUDAStream(dev).stream()), "fmha_bwd", dev);
+  finish_call(fmha_sm100_bwd(&p, at::cuda::getCurrentCUDAStream(dev).stream()), what, dev);
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_bwd(const at::Tensor& d_o, const at::Tensor& q, const at::Tensor& k,
+                                                        const at::Tensor& v, const at::Tensor& o, const at::Tensor& lse,
+                                                        const c10::optional<at::Tensor>& mask,
+                                                        const c10::optional<at::Tensor>& seqlens, double p_drop,
+                                                        int64_t seed, int64_t offset, c10::optional<double> scale,
+                                                        int64_t bh_offset, const c10::optional<at::Tensor>& offset_tensor) {
+  TORCH_CHECK(q.is_cuda() && k.is_cuda() && v.is_cuda(), "mha_manual: q, k, v must be CUDA tensors");
+  at::Tensor dq = at::empty(q.sizes(), q.options());
+  at::Tensor dk = at::empty(k.sizes(), k.options());
+  at::Tensor dv = at::empty(v.sizes(), v.options());
+  bwd_into(d_o, q, k, v, o, lse, dq, dk, dv, mask, seqlens, p_drop, seed, offset, scale, bh_offset, offset_tensor, "fmha_bwd");
   return {dq, dk, dv};
+}
+
+// ---------------------------------------------------------------------------------------
+// fused QKV projection layout: qkv [B,S,3,H,D] in, o [B,S,H,D] out, gradients in one [B,S,3,H,D] tensor.
+// The kernels read and write these layouts through their tensor-map strides: the permutes and copies
+// that the reference leaves to the caller ("no permute" in its perf scripts) do not exist here.
+// ---------------------------------------------------------------------------------------
+void check_qkvpacked(const at::Tensor& qkv) {
+  TORCH_CHECK(qkv.is_cuda(), "mha_manual: qkv must be a CUDA tensor");
+  TORCH_CHECK(qkv.dim() == 5 && qkv.size(2) == 3, "mha_manual: qkv must be [B,S,3,H,D]");
+  TORCH_CHECK(qkv.is_contiguous(), "mha_manual: qkv must be contiguous");
+}
+// [B,S,3,H,D] -> the [B,H,S,D] view of slice i
+at::Tensor qkv_slice(const at::Tensor& qkv, int64_t i) { return qkv.select(2, i).permute({0, 2, 1, 3}); }
+
+std::tuple<at::Tensor, at::Tensor> fmha_qkvpacked_fwd(const at::Tensor& qkv, const c10::optional<at::Tensor>& mask,
+                                                      const c10::optional<at::Tensor>& seqlens, double p_drop, int64_t seed,
+                                                      int64_t offset, c10::optional<double> scale, int64_t bh_offset,
+                                                      const c10::optional<at::Tensor>& offset_tensor) {
+  check_qkvpacked(qkv);
+  at::Tensor o = at::empty({qkv.size(0), qkv.size(1), qkv.size(3), qkv.size(4)}, qkv.options());   // [B,S,H,D]
+  at::Tensor lse = fwd_into(qkv_slice(qkv, 0), qkv_slice(qkv, 1), qkv_slice(qkv, 2), o.permute({0, 2, 1, 3}), mask, seqlens,
+                            p_drop, seed, offset, scale, bh_offset, offset_tensor, "fmha_qkvpacked_fwd");
+  return {o, lse};
+}
+
+at::Tensor fmha_qkvpacked_bwd(const at::Tensor& d_o, const at::Tensor& qkv, const at::Tensor& o, const at::Tensor& lse,
+                              const c10::optional<at::Tensor>& mask, const c10::optional<at::Tensor>& seqlens, double p_drop,
+                              int64_t seed, int64_t offset, c10::optional<double> scale, int64_t bh_offset,
+                              const c10::optional<at::Tensor>& offset_tensor) {
+  check_qkvpacked(qkv);
+  TORCH_CHECK(d_o.dim() == 4 && o.dim() == 4 && d_o.sizes() == o.sizes() && o.size(0) == qkv.size(0) &&
+                  o.size(1) == qkv.size(1) && o.size(2) == qkv.size(3) && o.size(3) == qkv.size(4),
+              "mha_manual: o and d_o must be [B,S,H,D]");
+  at::Tensor dqkv = at::empty(qkv.sizes(), qkv.options());
+  bwd_into(d_o.permute({0, 2, 1, 3}), qkv_slice(qkv, 0), qkv_slice(qkv, 1), qkv_slice(qkv, 2), o.permute({0, 2, 1, 3}), lse,
+           qkv_slice(dqkv, 0), qkv_slice(dqkv, 1), qkv_slice(dqkv, 2), mask, seqlens, p_drop, seed, offset, scale, bh_offset,
+           offset_tensor, "fmha_qkvpacked_bwd");
+  return dqkv;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -562,6 +621,57 @@ at::Tensor fmha_varlen_autograd(const at::Tensor& q, const at::Tensor& k, const 
   return FmhaVarlenFunction::apply(q, k, v, cu_seqlens, max_seqlen, p_drop, seed, offset, scale, offset_tensor);
 }
 
+class FmhaQkvPackedFunction : public torch::autograd::Function<FmhaQkvPackedFunction> {
+ public:
+  static at::Tensor forward(torch::autograd::AutogradContext* ctx, const at::Tensor& qkv,
+                            const c10::optional<at::Tensor>& mask, const c10::optional<at::Tensor>& seqlens, double p_drop,
+                            int64_t seed, int64_t offset, c10::optional<double> scale,
+                            const c10::optional<at::Tensor>& offset_tensor) {
+    at::AutoDispatchBelowADInplaceOrView guard;
+    static auto op = c10::Dispatcher::singleton()
+                         .findSchemaOrThrow("mha_manual::fmha_qkvpacked_fwd", "")
+                         .typed<std::tuple<at::Tensor, at::Tensor>(const at::Tensor&, const c10::optional<at::Tensor>&,
+                                                                   const c10::optional<at::Tensor>&, double, int64_t, int64_t,
+                                                                   c10::optional<double>, int64_t,
+                                                                   const c10::optional<at::Tensor>&)>();
+    auto [o, lse] = op.call(qkv, mask, seqlens, p_drop, seed, offset, scale, 0, offset_tensor);
+    ctx->save_for_backward({qkv, o, lse, mask.has_value() ? *mask : at::Tensor(),
+                            seqlens.has_value() ? *seqlens : at::Tensor(),
+                            offset_tensor.has_value() ? offset_tensor->clone() : at::Tensor()});
+    ctx->saved_data["p_drop"] = p_drop;
+    ctx->saved_data["seed"] = seed;
+    ctx->saved_data["offset"] = offset;
+    ctx->saved_data["has_scale"] = scale.has_value();
+    ctx->saved_data["scale"] = scale.has_value() ? *scale : 0.0;
+    return o;
+  }
+  static torch::autograd::variable_list backward(torch::autograd::AutogradContext* ctx,
+                                                 torch::autograd::variable_list grads) {
+    const auto saved = ctx->get_saved_variables();
+    c10::optional<at::Tensor> mask, seqlens, offset_tensor;
+    if (saved[3].defined()) mask = saved[3];
+    if (saved[4].defined()) seqlens = saved[4];
+    if (saved[5].defined()) offset_tensor = saved[5];
+    c10::optional<double> scale;
+    if (ctx->saved_data["has_scale"].toBool()) scale = ctx->saved_data["scale"].toDouble();
+    static auto op = c10::Dispatcher::singleton()
+                         .findSchemaOrThrow("mha_manual::fmha_qkvpacked_bwd", "")
+                         .typed<at::Tensor(const at::Tensor&, const at::Tensor&, const at::Tensor&, const at::Tensor&,
+                                           const c10::optional<at::Tensor>&, const c10::optional<at::Tensor>&, double, int64_t,
+                                           int64_t, c10::optional<double>, int64_t, const c10::optional<at::Tensor>&)>();
+    at::Tensor dqkv = op.call(grads[0].contiguous(), saved[0], saved[1], saved[2], mask, seqlens,
+                              ctx->saved_data["p_drop"].toDouble(), ctx->saved_data["seed"].toInt(),
+                              ctx->saved_data["offset"].toInt(), scale, 0, offset_tensor);
+    return {dqkv, at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor()};
+  }
+};
+
+at::Tensor fmha_qkvpacked_autograd(const at::Tensor& qkv, const c10::optional<at::Tensor>& mask,
+                                   const c10::optional<at::Tensor>& seqlens, double p_drop, int64_t seed, int64_t offset,
+                                   c10::optional<double> scale, const c10::optional<at::Tensor>& offset_tensor) {
+  return FmhaQkvPackedFunction::apply(qkv, mask, seqlens, p_drop, seed, offset, scale, offset_tensor);
+}
+
 at::Tensor fmha_autograd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
                          const c10::optional<at::Tensor>& mask, const c10::optional<at::Tensor>& seqlens, double p_drop,
                          int64_t seed, int64_t offset, c10::optional<double> scale,
@@ -643,6 +753,36 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_bwd_meta(const at::Tensor& d
   return {at::empty(q.sizes(), q.options()), at::empty(k.sizes(), k.options()), at::empty(v.sizes(), v.options())};
 }
 
+void meta_check_qkvpacked(const at::Tensor& qkv, const c10::optional<at::Tensor>& mask, const c10::optional<at::Tensor>& seqlens) {
+  TORCH_CHECK(qkv.dim() == 5 && qkv.size(2) == 3, "mha_manual: qkv must be [B,S,3,H,D]");
+  TORCH_CHECK(qkv.scalar_type() == at::kHalf || qkv.scalar_type() == at::kBFloat16, "mha_manual: qkv must be float16 or bfloat16");
+  TORCH_CHECK(qkv.size(4) == 64 || qkv.size(4) == 128, "mha_manual: head dimension must be 64 or 128, got ", qkv.size(4));
+  TORCH_CHECK(!(mask.has_value() && seqlens.has_value()), "mha_manual: pass either mask or seqlens, not both");
+  if (mask.has_value()) TORCH_CHECK(mask->numel() == qkv.size(0) * qkv.size(1), "mha_manual: mask must hold B*S_k additive values");
+  if (seqlens.has_value()) TORCH_CHECK(seqlens->numel() == qkv.size(0), "mha_manual: seqlens must be [B]");
+}
+std::tuple<at::Tensor, at::Tensor> fmha_qkvpacked_fwd_meta(const at::Tensor& qkv, const c10::optional<at::Tensor>& mask,
+                                                           const c10::optional<at::Tensor>& seqlens, double p_drop, int64_t,
+                                                           int64_t offset, c10::optional<double>, int64_t,
+                                                           const c10::optional<at::Tensor>&) {
+  meta_check_qkvpacked(qkv, mask, seqlens);
+  TORCH_CHECK(p_drop >= 0.0 && p_drop < 1.0, "mha_manual: p_drop must be in [0, 1)");
+  TORCH_CHECK(offset >= 0 && offset < (int64_t(1) << 32), "mha_manual: offset must be in [0, 2^32)");
+  return {at::empty({qkv.size(0), qkv.size(1), qkv.size(3), qkv.size(4)}, qkv.options()),
+          at::empty({qkv.size(0), qkv.size(3), qkv.size(1)}, qkv.options().dtype(at::kFloat))};
+}
+at::Tensor fmha_qkvpacked_bwd_meta(const at::Tensor& d_o, const at::Tensor& qkv, const at::Tensor& o, const at::Tensor& lse,
+                                   const c10::optional<at::Tensor>& mask, const c10::optional<at::Tensor>& seqlens, double,
+                                   int64_t, int64_t, c10::optional<double>, int64_t, const c10::optional<at::Tensor>&) {
+  meta_check_qkvpacked(qkv, mask, seqlens);
+  TORCH_CHECK(o.dim() == 4 && d_o.sizes() == o.sizes() && o.size(0) == qkv.size(0) && o.size(1) == qkv.size(1) &&
+                  o.size(2) == qkv.size(3) && o.size(3) == qkv.size(4),
+              "mha_manual: o and d_o must be [B,S,H,D]");
+  TORCH_CHECK(lse.scalar_type() == at::kFloat && lse.numel() == qkv.size(0) * qkv.size(3) * qkv.size(1),
+              "mha_manual: lse must be float32 [B,H,S]");
+  return at::empty(qkv.sizes(), qkv.options());
+}
+
 void meta_check_packed(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& cu, int64_t max_seqlen) {
   TORCH_CHECK(q.dim() == 3, "mha_manual: q must be [total_rows, H, D]");
   TORCH_CHECK(q.scalar_type() == at::kHalf || q.scalar_type() == at::kBFloat16, "mha_manual: q must be float16 or bfloat16");
@@ -688,6 +828,12 @@ TORCH_LIBRARY(mha_manual, m) {
         "float p_drop=0.0, int seed=0, int offset=0, float? scale=None, Tensor? offset_tensor=None) -> (Tensor, Tensor, Tensor)");
   m.def("fmha_varlen(Tensor q, Tensor k, Tensor v, Tensor cu_seqlens, int max_seqlen, float p_drop=0.0, int seed=0, "
         "int offset=0, float? scale=None, Tensor? offset_tensor=None) -> Tensor");
+  m.def("fmha_qkvpacked_fwd(Tensor qkv, Tensor? mask=None, Tensor? seqlens=None, float p_drop=0.0, int seed=0, "
+        "int offset=0, float? scale=None, int bh_offset=0, Tensor? offset_tensor=None) -> (Tensor, Tensor)");
+  m.def("fmha_qkvpacked_bwd(Tensor d_o, Tensor qkv, Tensor o, Tensor lse, Tensor? mask=None, Tensor? seqlens=None, "
+        "float p_drop=0.0, int seed=0, int offset=0, float? scale=None, int bh_offset=0, Tensor? offset_tensor=None) -> Tensor");
+  m.def("fmha_qkvpacked(Tensor qkv, Tensor? mask=None, Tensor? seqlens=None, float p_drop=0.0, int seed=0, "
+        "int offset=0, float? scale=None, Tensor? offset_tensor=None) -> Tensor");
   m.def("philox_dropout_mask(int B, int H, int S_q, int S_k, float p, int seed, int offset, int bh_offset=0, "
         "bool on_device=False) -> Tensor", philox_dropout_mask);
   m.def("check_status() -> ()", check_status);
@@ -701,6 +847,8 @@ TORCH_LIBRARY_IMPL(mha_manual, CUDA, m) {
   m.impl("fmha_bwd", fmha_bwd);
   m.impl("fmha_varlen_fwd", fmha_varlen_fwd);
   m.impl("fmha_varlen_bwd", fmha_varlen_bwd);
+  m.impl("fmha_qkvpacked_fwd", fmha_qkvpacked_fwd);
+  m.impl("fmha_qkvpacked_bwd", fmha_qkvpacked_bwd);
 }
 
 TORCH_LIBRARY_IMPL(mha_manual, Meta, m) {
@@ -711,11 +859,14 @@ TORCH_LIBRARY_IMPL(mha_manual, Meta, m) {
   m.impl("fmha_bwd", fmha_bwd_meta);
   m.impl("fmha_varlen_fwd", fmha_varlen_fwd_meta);
   m.impl("fmha_varlen_bwd", fmha_varlen_bwd_meta);
+  m.impl("fmha_qkvpacked_fwd", fmha_qkvpacked_fwd_meta);
+  m.impl("fmha_qkvpacked_bwd", fmha_qkvpacked_bwd_meta);
 }
 
 TORCH_LIBRARY_IMPL(mha_manual, Autograd, m) {
   m.impl("fmha", fmha_autograd);
   m.impl("fmha_varlen", fmha_varlen_autograd);
+  m.impl("fmha_qkvpacked", fmha_qkvpacked_autograd);
 }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {

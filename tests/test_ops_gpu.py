@@ -167,6 +167,31 @@ def test_device_resident_philox_offset_gives_new_masks_on_graph_replay(ops, cuda
     helpers.assert_close(qg.grad, eager[5][2].float(), "dq via autograd")
 
 
+def test_fused_projection_layout_operator(ops, cuda_device):
+    """qkv [B,S,3,H,D] -> o [B,S,H,D], and autograd returns one [B,S,3,H,D] gradient: the layouts on both sides
+    of a fused QKV projection, with no permute or copy around the kernels."""
+    dev = cuda_device
+    B, S, H, D, p = 2, 200, 3, 64, 0.1
+    g = torch.Generator().manual_seed(8)
+    qkv = torch.randn(B, S, 3, H, D, generator=g).half().to(dev).requires_grad_()
+    d_o = torch.randn(B, S, H, D, generator=g).half().to(dev)
+    lens = torch.tensor([200, 131], dtype=torch.int32, device=dev)
+    o = ops.fmha_qkvpacked(qkv, None, lens, p, 11, 4)
+    assert o.shape == (B, S, H, D) and o.is_contiguous()
+    (dqkv,) = torch.autograd.grad(o, (qkv,), d_o)
+    assert dqkv.shape == qkv.shape and dqkv.is_contiguous()
+    ops.check_status()
+    q, k, v = (qkv.detach()[:, :, i].permute(0, 2, 1, 3).contiguous() for i in range(3))
+    ref, add, keep, ks = helpers.oracle_forward(q, k, v, p_drop=p, seed=11, offset=4, lens=lens)
+    rdq, rdk, rdv = helpers.oracle_backward(q, k, v, d_o.permute(0, 2, 1, 3).contiguous(), add=add, keep=keep, ks=ks)
+    helpers.assert_close(o.permute(0, 2, 1, 3), ref["o"], "o")
+    for i, (name, want) in enumerate((("dq", rdq), ("dk", rdk), ("dv", rdv))):
+        helpers.assert_close(dqkv[:, :, i].permute(0, 2, 1, 3), want, name)
+    # the same numbers as the [B,H,S,D] operator on permuted views, bit for bit in the forward direction
+    o2, _ = ops.fmha_fwd(q, k, v, None, lens, p, 11, 4)
+    assert torch.equal(o2, o.permute(0, 2, 1, 3))
+
+
 def test_operator_errors(ops, cuda_device):
     x = torch.zeros(2, 128, 64, dtype=torch.half, device=cuda_device)
     with pytest.raises(RuntimeError):

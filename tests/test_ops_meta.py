@@ -73,3 +73,17 @@ def test_shape_errors_are_raised_without_a_device(ops):
         ops.fmha_fwd(meta(1, 1, 16, 64, dtype=torch.float32), meta(1, 1, 16, 64, dtype=torch.float32), meta(1, 1, 16, 64, dtype=torch.float32))
     with pytest.raises(RuntimeError, match="B\\*H\\*S_q\\*S_k"):
         ops.fmha_nvfuser(meta(4, 16, 64), meta(4, 16, 64), meta(4, 16, 64), meta(4, 16, 8))
+
+
+def test_fused_projection_layout_operators_infer_shapes(ops):
+    qkv = meta(2, 300, 3, 4, 64)
+    lens = torch.empty(2, dtype=torch.int32, device="meta")
+    o, lse = ops.fmha_qkvpacked_fwd(qkv, None, lens, 0.1, 1, 2)
+    assert o.shape == (2, 300, 4, 64) and lse.shape == (2, 4, 300) and lse.dtype == torch.float32
+    assert ops.fmha_qkvpacked_bwd(torch.empty_like(o), qkv, o, lse, None, lens, 0.1, 1, 2).shape == qkv.shape
+    qg = meta(2, 300, 3, 4, 64).requires_grad_()
+    out = ops.fmha_qkvpacked(qg, None, lens, 0.1, 1, 2)
+    (g,) = torch.autograd.grad(out, (qg,), torch.empty_like(out))
+    assert out.shape == (2, 300, 4, 64) and g.shape == qg.shape
+    with pytest.raises(RuntimeError):
+        ops.fmha_qkvpacked_fwd(meta(2, 300, 2, 4, 64))
