@@ -401,10 +401,10 @@ void check_packed_qkv(const Packed& q, const Packed& k, const Packed& v, int64_t
   TORCH_CHECK(max_seqlen > 0, "mha_manual: max_seqlen must be positive");
 }
 
-std::tuple<at::Tensor, at::Tensor> fmha_varlen_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
-                                                   const at::Tensor& cu_seqlens, int64_t max_seqlen, double p_drop,
-                                                   int64_t seed, int64_t offset, c10::optional<double> scale,
-                                                   const c10::optional<at::Tensor>& offset_tensor) {
+// Packed forward into a caller-allocated `o` ([total_rows, H, D] with any row / head strides); returns lse.
+at::Tensor varlen_fwd_into(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& o,
+                           const at::Tensor& cu_seqlens, int64_t max_seqlen, double p_drop, int64_t seed, int64_t offset,
+                           c10::optional<double> scale, const c10::optional<at::Tensor>& offset_tensor, const char* what) {
   const Packed vq = packed3(q, "q"), vk = packed3(k, "k"), vv = packed3(v, "v");
   check_same(q, k, "k");
   check_same(q, v, "v");
@@ -412,9 +412,8 @@ std::tuple<at::Tensor, at::Tensor> fmha_varlen_fwd(const at::Tensor& q, const at
   const c10::cuda::CUDAGuard guard(q.device());
   const int dev = q.get_device();
   const at::Tensor cu = check_cu_seqlens(cu_seqlens, q);
-  at::Tensor o = at::empty(q.sizes(), q.options());
   at::Tensor lse = at::empty({vq.H, vq.total}, q.options().dtype(at::kFloat));
-  if (vq.total == 0) return {o, lse};
+  if (vq.total == 0) return lse;
   fmha_fwd_params p{};
   p.struct_bytes = sizeof(p);
   p.dtype = dtype_code(q);
@@ -434,15 +433,25 @@ std::tuple<at::Tensor, at::Tensor> fmha_varlen_fwd(const at::Tensor& q, const at
     p.philox_offset_dev = offset_tensor_ptr(offset_tensor, q);
   }
   p.status = status_block(dev).data_ptr<int32_t>();
-  finish_call(fmha_sm100_fwd(&p, at::cuda::getCurrentCUDAStream(dev).stream()), "fmha_varlen_fwd", dev);
+  finish_call(fmha_sm100_fwd(&p, at::cuda::getCurrentCUDAStream(dev).stream()), what, dev);
+  return lse;
+}
+
+std::tuple<at::Tensor, at::Tensor> fmha_varlen_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                                                   const at::Tensor& cu_seqlens, int64_t max_seqlen, double p_drop,
+                                                   int64_t seed, int64_t offset, c10::optional<double> scale,
+                                                   const c10::optional<at::Tensor>& offset_tensor) {
+  TORCH_CHECK(q.is_cuda(), "mha_manual: q must be a CUDA tensor");
+  at::Tensor o = at::empty(q.sizes(), q.options());
+  at::Tensor lse = varlen_fwd_into(q, k, v, o, cu_seqlens, max_seqlen, p_drop, seed, offset, scale, offset_tensor, "fmha_varlen_fwd");
   return {o, lse};
 }
 
-std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_varlen_bwd(const at::Tensor& d_o, const at::Tensor& q, const at::Tensor& k,
-                                                               const at::Tensor& v, const at::Tensor& o, const at::Tensor& lse,
-                                                               const at::Tensor& cu_seqlens, int64_t max_seqlen, double p_drop,
-                                                               int64_t seed, int64_t offset, c10::optional<double> scale,
-                                                               const c10::optional<at::Tensor>& offset_tensor) {
+// Packed backward into caller-allocated dq, dk, dv ([total_rows, H, D] with any row / head strides).
+void varlen_bwd_into(const at::Tensor& d_o, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& o,
+                     const at::Tensor& lse, const at::Tensor& dq, const at::Tensor& dk, const at::Tensor& dv,
+                     const at::Tensor& cu_seqlens, int64_t max_seqlen, double p_drop, int64_t seed, int64_t offset,
+                     c10::optional<double> scale, const c10::optional<at::Tensor>& offset_tensor, const char* what) {
   const Packed vq = packed3(q, "q"), vk = packed3(k, "k"), vv = packed3(v, "v"), vo = packed3(o, "o");
   at::Tensor d_o_c = d_o.stride(-1) == 1 ? d_o : d_o.contiguous();
   const Packed vdo = packed3(d_o_c, "d_o");
@@ -455,10 +464,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_varlen_bwd(const at::Tensor&
   const int dev = q.get_device();
   const at::Tensor cu = check_cu_seqlens(cu_seqlens, q);
   at::Tensor lse_c = lse.contiguous();
-  at::Tensor dq = at::empty(q.sizes(), q.options());
-  at::Tensor dk = at::empty(k.sizes(), k.options());
-  at::Tensor dv = at::empty(v.sizes(), v.options());
-  if (vq.total == 0) return {dq, dk, dv};
+  if (vq.total == 0) return;
   fmha_bwd_params p{};
   p.struct_bytes = sizeof(p);
   p.dtype = dtype_code(q);
@@ -484,8 +490,50 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_varlen_bwd(const at::Tensor&
   p.workspace = workspace.data_ptr();
   p.workspace_bytes = ws;
   p.status = status_block(dev).data_ptr<int32_t>();
-  finish_call(fmha_sm100_bwd(&p, at::cuda::getCurrentCUDAStream(dev).stream()), "fmha_varlen_bwd", dev);
+  finish_call(fmha_sm100_bwd(&p, at::cuda::getCurrentCUDAStream(dev).stream()), what, dev);
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_varlen_bwd(const at::Tensor& d_o, const at::Tensor& q, const at::Tensor& k,
+                                                               const at::Tensor& v, const at::Tensor& o, const at::Tensor& lse,
+                                                               const at::Tensor& cu_seqlens, int64_t max_seqlen, double p_drop,
+                                                               int64_t seed, int64_t offset, c10::optional<double> scale,
+                                                               const c10::optional<at::Tensor>& offset_tensor) {
+  TORCH_CHECK(q.is_cuda() && k.is_cuda() && v.is_cuda(), "mha_manual: q, k, v must be CUDA tensors");
+  at::Tensor dq = at::empty(q.sizes(), q.options());
+  at::Tensor dk = at::empty(k.sizes(), k.options());
+  at::Tensor dv = at::empty(v.sizes(), v.options());
+  varlen_bwd_into(d_o, q, k, v, o, lse, dq, dk, dv, cu_seqlens, max_seqlen, p_drop, seed, offset, scale, offset_tensor,
+                  "fmha_varlen_bwd");
   return {dq, dk, dv};
+}
+
+// Packed batch AND fused projection layout: qkv [total_rows, 3, H, D] in, o [total_rows, H, D] out, one
+// [total_rows, 3, H, D] gradient back (the form an unpadded BERT layer keeps its activations in).
+void check_varlen_qkvpacked(const at::Tensor& qkv) {
+  TORCH_CHECK(qkv.is_cuda(), "mha_manual: qkv must be a CUDA tensor");
+  TORCH_CHECK(qkv.dim() == 4 && qkv.size(1) == 3, "mha_manual: qkv must be [total_rows, 3, H, D]");
+  TORCH_CHECK(qkv.is_contiguous(), "mha_manual: qkv must be contiguous");
+}
+std::tuple<at::Tensor, at::Tensor> fmha_varlen_qkvpacked_fwd(const at::Tensor& qkv, const at::Tensor& cu_seqlens,
+                                                             int64_t max_seqlen, double p_drop, int64_t seed, int64_t offset,
+                                                             c10::optional<double> scale,
+                                                             const c10::optional<at::Tensor>& offset_tensor) {
+  check_varlen_qkvpacked(qkv);
+  at::Tensor o = at::empty({qkv.size(0), qkv.size(2), qkv.size(3)}, qkv.options());
+  at::Tensor lse = varlen_fwd_into(qkv.select(1, 0), qkv.select(1, 1), qkv.select(1, 2), o, cu_seqlens, max_seqlen, p_drop, seed,
+                                   offset, scale, offset_tensor, "fmha_varlen_qkvpacked_fwd");
+  return {o, lse};
+}
+at::Tensor fmha_varlen_qkvpacked_bwd(const at::Tensor& d_o, const at::Tensor& qkv, const at::Tensor& o, const at::Tensor& lse,
+                                     const at::Tensor& cu_seqlens, int64_t max_seqlen, double p_drop, int64_t seed,
+                                     int64_t offset, c10::optional<double> scale,
+                                     const c10::optional<at::Tensor>& offset_tensor) {
+  check_varlen_qkvpacked(qkv);
+  at::Tensor dqkv = at::empty(qkv.sizes(), qkv.options());
+  varlen_bwd_into(d_o, qkv.select(1, 0), qkv.select(1, 1), qkv.select(1, 2), o, lse, dqkv.select(1, 0), dqkv.select(1, 1),
+                  dqkv.select(1, 2), cu_seqlens, max_seqlen, p_drop, seed, offset, scale, offset_tensor,
+                  "fmha_varlen_qkvpacked_bwd");
+  return dqkv;
 }
 
 at::Tensor philox_dropout_mask(int64_t B, int64_t H, int64_t S_q, int64_t S_k, double p, int64_t seed, int64_t offset,
@@ -614,6 +662,52 @@ class FmhaVarlenFunction : public torch::autograd::Function<FmhaVarlenFunction> 
     return {dq, dk, dv, at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor()};
   }
 };
+
+class FmhaVarlenQkvPackedFunction : public torch::autograd::Function<FmhaVarlenQkvPackedFunction> {
+ public:
+  static at::Tensor forward(torch::autograd::AutogradContext* ctx, const at::Tensor& qkv, const at::Tensor& cu_seqlens,
+                            int64_t max_seqlen, double p_drop, int64_t seed, int64_t offset, c10::optional<double> scale,
+                            const c10::optional<at::Tensor>& offset_tensor) {
+    at::AutoDispatchBelowADInplaceOrView guard;
+    static auto op = c10::Dispatcher::singleton()
+                         .findSchemaOrThrow("mha_manual::fmha_varlen_qkvpacked_fwd", "")
+                         .typed<std::tuple<at::Tensor, at::Tensor>(const at::Tensor&, const at::Tensor&, int64_t, double, int64_t,
+                                                                   int64_t, c10::optional<double>,
+                                                                   const c10::optional<at::Tensor>&)>();
+    auto [o, lse] = op.call(qkv, cu_seqlens, max_seqlen, p_drop, seed, offset, scale, offset_tensor);
+    ctx->save_for_backward({qkv, o, lse, cu_seqlens, offset_tensor.has_value() ? offset_tensor->clone() : at::Tensor()});
+    ctx->saved_data["max_seqlen"] = max_seqlen;
+    ctx->saved_data["p_drop"] = p_drop;
+    ctx->saved_data["seed"] = seed;
+    ctx->saved_data["offset"] = offset;
+    ctx->saved_data["has_scale"] = scale.has_value();
+    ctx->saved_data["scale"] = scale.has_value() ? *scale : 0.0;
+    return o;
+  }
+  static torch::autograd::variable_list backward(torch::autograd::AutogradContext* ctx,
+                                                 torch::autograd::variable_list grads) {
+    const auto saved = ctx->get_saved_variables();
+    c10::optional<double> scale;
+    if (ctx->saved_data["has_scale"].toBool()) scale = ctx->saved_data["scale"].toDouble();
+    c10::optional<at::Tensor> offset_tensor;
+    if (saved[4].defined()) offset_tensor = saved[4];
+    static auto op = c10::Dispatcher::singleton()
+                         .findSchemaOrThrow("mha_manual::fmha_varlen_qkvpacked_bwd", "")
+                         .typed<at::Tensor(const at::Tensor&, const at::Tensor&, const at::Tensor&, const at::Tensor&,
+                                           const at::Tensor&, int64_t, double, int64_t, int64_t, c10::optional<double>,
+                                           const c10::optional<at::Tensor>&)>();
+    at::Tensor dqkv = op.call(grads[0].contiguous(), saved[0], saved[1], saved[2], saved[3],
+                              ctx->saved_data["max_seqlen"].toInt(), ctx->saved_data["p_drop"].toDouble(),
+                              ctx->saved_data["seed"].toInt(), ctx->saved_data["offset"].toInt(), scale, offset_tensor);
+    return {dqkv, at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor()};
+  }
+};
+
+at::Tensor fmha_varlen_qkvpacked_autograd(const at::Tensor& qkv, const at::Tensor& cu_seqlens, int64_t max_seqlen,
+                                          double p_drop, int64_t seed, int64_t offset, c10::optional<double> scale,
+                                          const c10::optional<at::Tensor>& offset_tensor) {
+  return FmhaVarlenQkvPackedFunction::apply(qkv, cu_seqlens, max_seqlen, p_drop, seed, offset, scale, offset_tensor);
+}
 
 at::Tensor fmha_varlen_autograd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& cu_seqlens,
                                 int64_t max_seqlen, double p_drop, int64_t seed, int64_t offset, c10::optional<double> scale,
@@ -809,6 +903,32 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_varlen_bwd_meta(const at::Te
   return {at::empty(q.sizes(), q.options()), at::empty(k.sizes(), k.options()), at::empty(v.sizes(), v.options())};
 }
 
+void meta_check_varlen_qkvpacked(const at::Tensor& qkv, const at::Tensor& cu, int64_t max_seqlen) {
+  TORCH_CHECK(qkv.dim() == 4 && qkv.size(1) == 3, "mha_manual: qkv must be [total_rows, 3, H, D]");
+  TORCH_CHECK(qkv.scalar_type() == at::kHalf || qkv.scalar_type() == at::kBFloat16, "mha_manual: qkv must be float16 or bfloat16");
+  TORCH_CHECK(qkv.size(3) == 64 || qkv.size(3) == 128, "mha_manual: head dimension must be 64 or 128, got ", qkv.size(3));
+  TORCH_CHECK(cu.dim() == 1 && cu.numel() >= 2, "mha_manual: cu_seqlens must be [B+1]");
+  TORCH_CHECK(max_seqlen > 0, "mha_manual: max_seqlen must be positive");
+}
+std::tuple<at::Tensor, at::Tensor> fmha_varlen_qkvpacked_fwd_meta(const at::Tensor& qkv, const at::Tensor& cu_seqlens,
+                                                                  int64_t max_seqlen, double, int64_t, int64_t,
+                                                                  c10::optional<double>, const c10::optional<at::Tensor>&) {
+  meta_check_varlen_qkvpacked(qkv, cu_seqlens, max_seqlen);
+  return {at::empty({qkv.size(0), qkv.size(2), qkv.size(3)}, qkv.options()),
+          at::empty({qkv.size(2), qkv.size(0)}, qkv.options().dtype(at::kFloat))};
+}
+at::Tensor fmha_varlen_qkvpacked_bwd_meta(const at::Tensor& d_o, const at::Tensor& qkv, const at::Tensor& o, const at::Tensor& lse,
+                                          const at::Tensor& cu_seqlens, int64_t max_seqlen, double, int64_t, int64_t,
+                                          c10::optional<double>, const c10::optional<at::Tensor>&) {
+  meta_check_varlen_qkvpacked(qkv, cu_seqlens, max_seqlen);
+  TORCH_CHECK(o.dim() == 3 && d_o.sizes() == o.sizes() && o.size(0) == qkv.size(0) && o.size(1) == qkv.size(2) &&
+                  o.size(2) == qkv.size(3),
+              "mha_manual: o and d_o must be [total_rows, H, D]");
+  TORCH_CHECK(lse.scalar_type() == at::kFloat && lse.numel() == qkv.size(0) * qkv.size(2),
+              "mha_manual: lse must be float32 [H, total_rows]");
+  return at::empty(qkv.sizes(), qkv.options());
+}
+
 }  // namespace
 
 TORCH_LIBRARY(mha_manual, m) {
@@ -834,6 +954,12 @@ TORCH_LIBRARY(mha_manual, m) {
         "float p_drop=0.0, int seed=0, int offset=0, float? scale=None, int bh_offset=0, Tensor? offset_tensor=None) -> Tensor");
   m.def("fmha_qkvpacked(Tensor qkv, Tensor? mask=None, Tensor? seqlens=None, float p_drop=0.0, int seed=0, "
         "int offset=0, float? scale=None, Tensor? offset_tensor=None) -> Tensor");
+  m.def("fmha_varlen_qkvpacked_fwd(Tensor qkv, Tensor cu_seqlens, int max_seqlen, float p_drop=0.0, int seed=0, "
+        "int offset=0, float? scale=None, Tensor? offset_tensor=None) -> (Tensor, Tensor)");
+  m.def("fmha_varlen_qkvpacked_bwd(Tensor d_o, Tensor qkv, Tensor o, Tensor lse, Tensor cu_seqlens, int max_seqlen, "
+        "float p_drop=0.0, int seed=0, int offset=0, float? scale=None, Tensor? offset_tensor=None) -> Tensor");
+  m.def("fmha_varlen_qkvpacked(Tensor qkv, Tensor cu_seqlens, int max_seqlen, float p_drop=0.0, int seed=0, "
+        "int offset=0, float? scale=None, Tensor? offset_tensor=None) -> Tensor");
   m.def("philox_dropout_mask(int B, int H, int S_q, int S_k, float p, int seed, int offset, int bh_offset=0, "
         "bool on_device=False) -> Tensor", philox_dropout_mask);
   m.def("check_status() -> ()", check_status);
@@ -849,6 +975,8 @@ TORCH_LIBRARY_IMPL(mha_manual, CUDA, m) {
   m.impl("fmha_varlen_bwd", fmha_varlen_bwd);
   m.impl("fmha_qkvpacked_fwd", fmha_qkvpacked_fwd);
   m.impl("fmha_qkvpacked_bwd", fmha_qkvpacked_bwd);
+  m.impl("fmha_varlen_qkvpacked_fwd", fmha_varlen_qkvpacked_fwd);
+  m.impl("fmha_varlen_qkvpacked_bwd", fmha_varlen_qkvpacked_bwd);
 }
 
 TORCH_LIBRARY_IMPL(mha_manual, Meta, m) {
@@ -861,12 +989,15 @@ TORCH_LIBRARY_IMPL(mha_manual, Meta, m) {
   m.impl("fmha_varlen_bwd", fmha_varlen_bwd_meta);
   m.impl("fmha_qkvpacked_fwd", fmha_qkvpacked_fwd_meta);
   m.impl("fmha_qkvpacked_bwd", fmha_qkvpacked_bwd_meta);
+  m.impl("fmha_varlen_qkvpacked_fwd", fmha_varlen_qkvpacked_fwd_meta);
+  m.impl("fmha_varlen_qkvpacked_bwd", fmha_varlen_qkvpacked_bwd_meta);
 }
 
 TORCH_LIBRARY_IMPL(mha_manual, Autograd, m) {
   m.impl("fmha", fmha_autograd);
   m.impl("fmha_varlen", fmha_varlen_autograd);
   m.impl("fmha_qkvpacked", fmha_qkvpacked_autograd);
+  m.impl("fmha_varlen_qkvpacked", fmha_varlen_qkvpacked_autograd);
 }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {

@@ -87,3 +87,15 @@ def test_fused_projection_layout_operators_infer_shapes(ops):
     assert out.shape == (2, 300, 4, 64) and g.shape == qg.shape
     with pytest.raises(RuntimeError):
         ops.fmha_qkvpacked_fwd(meta(2, 300, 2, 4, 64))
+
+
+def test_packed_fused_projection_operators_infer_shapes(ops):
+    qkv = meta(1000, 3, 4, 128, dtype=torch.bfloat16)
+    cu = torch.empty(9, dtype=torch.int32, device="meta")
+    o, lse = ops.fmha_varlen_qkvpacked_fwd(qkv, cu, 384, 0.1, 1, 2)
+    assert o.shape == (1000, 4, 128) and lse.shape == (4, 1000) and lse.dtype == torch.float32
+    assert ops.fmha_varlen_qkvpacked_bwd(torch.empty_like(o), qkv, o, lse, cu, 384, 0.1, 1, 2).shape == qkv.shape
+    qg = meta(1000, 3, 4, 128, dtype=torch.bfloat16).requires_grad_()
+    out = ops.fmha_varlen_qkvpacked(qg, cu, 384)
+    (g,) = torch.autograd.grad(out, (qg,), torch.empty_like(out))
+    assert g.shape == qg.shape

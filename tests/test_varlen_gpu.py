@@ -187,3 +187,26 @@ def test_packed_autograd_operator(cuda_device):
     o2, _ = ops.fmha_varlen_fwd(q.detach(), k.detach(), v.detach(), cu, 384, 0.1, 77, 1, None, off)
     assert torch.equal(o2, o.detach())
     ops.check_status()
+
+
+def test_packed_batch_on_the_fused_projection_layout(cuda_device):
+    """qkv [total_rows,3,H,D] in, o [total_rows,H,D] out, one [total_rows,3,H,D] gradient back; sequences that
+    end inside a tile exercise the row-wise edge stores through the strided layout."""
+    import mha_manual  # noqa: F401
+    ops = torch.ops.mha_manual
+    lens = [150, 0, 40, 257, 128]
+    H, D, p = 3, 64, 0.1
+    q, k, v, d_o, cu = packed_batch(lens, H, D, torch.float16, seed=31, device=cuda_device)
+    qkv = torch.stack((q, k, v), dim=1).contiguous().requires_grad_()     # [total, 3, H, D]
+    o = ops.fmha_varlen_qkvpacked(qkv, cu, 384, p, 77, 4)
+    assert o.shape == q.shape and o.is_contiguous()
+    (dqkv,) = torch.autograd.grad(o, (qkv,), d_o)
+    assert dqkv.shape == qkv.shape and dqkv.is_contiguous()
+    ops.check_status()
+    ref = per_sequence_oracle(q, k, v, d_o, lens, p, 77, 4, 384)
+    helpers.assert_close(o, ref["o"], "o")
+    for i, name in enumerate(("dq", "dk", "dv")):
+        helpers.assert_close(dqkv[:, i], ref[name], name)
+    # the same bits as the three-tensor operator
+    o2, _ = ops.fmha_varlen_fwd(q, k, v, cu, 384, p, 77, 4)
+    assert torch.equal(o2, o.detach())
