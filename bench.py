@@ -448,6 +448,10 @@ def run_configs(args):
         return a.elapsed_time(b) / n
 
     for name, b, h, s, d, dt, len_range, p, train in NAMED_CONFIGS:
+        if args.only and name != args.only:
+            continue
+        if args.config_batch:
+            b = args.config_batch      # reduced batch, e.g. for a profiler capture of one configuration
         dtype = getattr(torch, dt)
         x = composite.make_inputs(b, h, s, d, dtype, len_range, 7, with_do=True)
         q, k, v, d_o, lens = (x[n].cuda() for n in ("q", "k", "v", "d_o", "lens"))
@@ -492,6 +496,8 @@ def main():
     ap.add_argument("--profile-batch", type=int, default=16)
     ap.add_argument("--configs", action="store_true",
                     help="kernel times of every named configuration on one GPU, one JSON line each (not the benchmark line)")
+    ap.add_argument("--only", default=None, help="with --configs: run this named configuration alone")
+    ap.add_argument("--config-batch", type=int, default=0, help="with --configs: override the batch size")
     args = ap.parse_args()
     if args.configs:
         return run_configs(args)
