@@ -2,8 +2,8 @@
 """Benchmark of the fused multi-head-attention training step (forward + backward) at the
 BERT-large shape, on N GPUs of one node.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--scaling weak|strong]
-    python bench.py --configs      (kernel times of the other named configurations, one line each)
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --configs      (kernel times of the named configurations, one line each)
 
 One "step" is one forward and one backward pass of the hot path over one batch of synthetic
 input (B=32, H=16, S=512, D=64, fp16, valid lengths uniform in [256,512], Philox dropout 0.1).
@@ -11,11 +11,20 @@ With N > 1 (launched under torchrun, one rank per GPU) every rank works on its o
 batch x heads axis; there is no collective on the data path, only a barrier and a MAX of the
 per-rank device times.  Rank 0 prints ONE JSON line.
 
-What is counted: `value` is EXECUTED TFLOP/s — (4*ceil64(len) + 10*ceil128(len))*H*S_q*D per batch
-element: the key length rounded up to the key steps the kernels actually visit (64 keys in the
-forward kernel, 128 in the backward kernel; steps that lie wholly in the padding are skipped,
-which is exact).  The dense-equivalent figure
-(14*B*H*S^2*D over the same time) is reported beside it.
+`value` is EXECUTED TFLOP/s of exactly K timed steps with every rank holding a full B=32 batch
+("scaling": "weak").  What is counted: (4*ceil64(len) + 10*ceil128(len))*H*S_q*D per batch element,
+the key length rounded up to the key steps the kernels actually visit (64 keys in the forward
+kernel, 128 in the backward kernel; steps that lie wholly in the padding are skipped, which is
+exact).  The dense-equivalent figure (14*B*H*S^2*D over the same time) is reported beside it.
+
+Further legs of the same run, each its own object in the line:
+  strong        the FIXED B=32 batch split N ways over batch x heads (what the configurations state), with the
+                same batch on one GPU timed in the same run, and the efficiency t1 / (N * tN)
+  sustained     the step back to back for >= 2 s: ms per step, SM clock and power under sustained load
+  other_configs the other named configurations (BERT-base forward, BERT-large forward, long-sequence training
+                shard) on this run's ranks
+  roofline / roofline_fwd / kernel_ms, e2e (host buffers in and out through the torch operators), cpu_baseline
+  clocks        NVML samples of the SM clock and throttle reasons over all loaded legs (read-only)
 
 `--impl reference` times the reference's own CPU path for the same step: the eager composite of
 its test scripts (matmul, scale, mask, softmax, dropout, matmul) plus autograd, on the host
@@ -64,42 +73,77 @@ def peaks():
 
 
 class ClockSampler(threading.Thread):
-    """Polls SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+    """Polls SM clock, power and throttle reasons through NVML (read-only) from construction until stop().
+
+    NVML is initialised in the constructor, i.e. BEFORE any timed region, so that even a region of a few
+    milliseconds is covered by samples.  `mark(name)` / `unmark(name)` bracket a leg; summaries can be taken per
+    leg or over everything that ran between marks."""
 
     def __init__(self, index: int):
         super().__init__(daemon=True)
-        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self.index, self.samples, self.reasons, self.max_mhz, self.error = index, [], set(), None, None
         self._stop_evt = threading.Event()
-
-    def run(self):
+        self._legs = {}
+        self._open = {}
+        self._nv = None
+        self._names = {}
         try:
             import pynvml as nv
             nv.nvmlInit()
-            h = nv.nvmlDeviceGetHandleByIndex(self.index)
-            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
-            names = {
+            self._h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(self._h, nv.NVML_CLOCK_SM)
+            self._names = {
                 getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
                 getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
                 getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
                 getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
                 getattr(nv, "nvmlClocksEventReasonHwPowerBrakeSlowdown", 0x80): "hw_power_brake_slowdown",
             }
-            get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
-            while not self._stop_evt.is_set():
-                self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
-                r = get_reasons(h)
-                for bit, name in names.items():
-                    if r & bit:
-                        self.reasons.add(name)
-                time.sleep(0.002)
+            self._get_reasons = (getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None)
+                                 or nv.nvmlDeviceGetCurrentClocksThrottleReasons)
+            self._nv = nv
         except Exception as e:  # NVML missing: report that instead of numbers
-            self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
+            self.error = f"nvml_unavailable:{type(e).__name__}"
+
+    def run(self):
+        nv = self._nv
+        if nv is None:
+            return
+        while not self._stop_evt.is_set():
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)
+                watts = nv.nvmlDeviceGetPowerUsage(self._h) / 1000.0
+                r = self._get_reasons(self._h)
+            except Exception as e:
+                self.error = f"nvml_error:{type(e).__name__}"
+                return
+            self.samples.append((time.perf_counter(), mhz, watts, r))
+            time.sleep(0.001)
+
+    def mark(self, name):
+        self._open[name] = time.perf_counter()
+
+    def unmark(self, name):
+        self._legs.setdefault(name, []).append((self._open.pop(name), time.perf_counter()))
+
+    def summary(self, names=None):
+        """Median SM MHz, max power and the throttle reasons seen inside the marked legs (all legs if None)."""
+        spans = [sp for n, v in self._legs.items() if names is None or n in names for sp in v]
+        inside = [s for s in self.samples if any(a <= s[0] <= b for a, b in spans)]
+        reasons = set()
+        for s in inside:
+            for bit, name in self._names.items():
+                if s[3] & bit:
+                    reasons.add(name)
+        if self.error:
+            reasons.add(self.error)
+        return dict(sm_mhz=statistics.median(s[1] for s in inside) if inside else None, sm_max_mhz=self.max_mhz,
+                    power_w_max=max((s[2] for s in inside), default=None), reasons=sorted(reasons), samples=len(inside))
 
     def stop(self):
         self._stop_evt.set()
-        self.join(2.0)
-        med = statistics.median(self.samples) if self.samples else None
-        return dict(sm_mhz=med, sm_max_mhz=self.max_mhz, reasons=sorted(self.reasons), samples=len(self.samples))
+        if self.is_alive():
+            self.join(2.0)
 
 
 # ------------------------------------------------------------------------------------------
@@ -109,8 +153,9 @@ def cpu_composite_step(sample_b: int, seed: int):
     """Builds a closure running one fwd+bwd of the composite on `sample_b` batch elements of the
     workload on the CPU, and the dense flops of that sample."""
     import torch
+    from nvfuserexamples_b200 import workloads
     from oracle import composite, philox
-    x = composite.make_inputs(sample_b, H, S, D, torch.float16, LEN_RANGE, seed, with_do=True)
+    x = workloads.make_inputs(sample_b, H, S, D, torch.float16, LEN_RANGE, seed, with_do=True)
     add = composite.padding_add_mask(x["lens"], S)
     keep = torch.from_numpy(philox.dropout_keep_mask(1, 0, 0, sample_b * H, S, S, P_DROP)).reshape(sample_b, H, S, S).float()
     ks = philox.keep_scale(P_DROP)
@@ -145,9 +190,10 @@ def run_reference(args, rank):
     sample = f"{sample_b} of {B0} batch elements (x{H} heads, S={S}, D={D}), fp32 composite + autograd, {steps} timed steps"
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": steps,
-        "warmup": warm, "ms_per_step": dt * 1e3 * (B0 / sample_b), "higher_is_better": True, "scaling": args.scaling,
+        "warmup": warm, "ms_per_step": dt * 1e3 * (B0 / sample_b), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "fp16 inputs, fp32 math", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "B": B0, "H": H, "S": S, "D": D, "p_drop": P_DROP,
+        "config": {"workload": WORKLOAD, "B_per_gpu": B0, "global_batch": B0 * args.gpus, "H": H, "S": S, "D": D,
+                   "p_drop": P_DROP, "valid_len": list(LEN_RANGE),
                    "flops_counted": "dense 14*B*H*S^2*D of the sample; ms_per_step scaled to the full batch"},
         "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -158,14 +204,85 @@ def run_reference(args, rank):
 # ------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------
-def run_ours(args, rank, world, local_rank):
-    import ctypes as C
+class Plan:
+    """Device-resident inputs, outputs and parameter blocks of `n_sets` rotating input sets of one shard: no
+    allocation happens inside a timed region."""
 
+    def __init__(self, capi, dev, b_loc, h, s, d, dtype, len_range, p_drop, seeds, bh_offset, status, train=True,
+                 device_inputs=False):
+        import ctypes as C
+
+        import torch
+        from nvfuserexamples_b200 import workloads
+        self.C, self.capi, self.lib = C, capi, capi.load()
+        self.sets, self.plans = [], []
+        for i, seed in enumerate(seeds):
+            if device_inputs:   # large shapes: seeded generation on the device (same distributions)
+                g = torch.Generator(device=dev).manual_seed(seed)
+                x = {n: torch.randn(b_loc, h, s, d, device=dev, generator=g, dtype=torch.float32).to(dtype)
+                     for n in (("q", "k", "v", "d_o") if train else ("q", "k", "v"))}
+                x["lens"] = torch.randint(len_range[0], len_range[1] + 1, (b_loc,), device=dev, generator=g, dtype=torch.int32)
+            else:
+                x = {k: v.to(dev) for k, v in workloads.make_inputs(b_loc, h, s, d, dtype, len_range, seed, with_do=train).items()}
+            self.sets.append(x)
+            o = torch.empty_like(x["q"])
+            lse = torch.empty(b_loc, h, s, dtype=torch.float32, device=dev)
+            fp = capi.FwdParams()
+            fp.struct_bytes = C.sizeof(capi.FwdParams)
+            fp.dtype = capi.DTYPE_F16 if dtype == torch.float16 else capi.DTYPE_BF16
+            fp.B, fp.H, fp.S_q, fp.S_k, fp.D = b_loc, h, s, s, d
+            fp.scale = 1.0 / math.sqrt(d)
+            fp.q, fp.k, fp.v, fp.o = (capi._t4(t) for t in (x["q"], x["k"], x["v"], o))
+            fp.lse = lse.data_ptr()
+            fp.mask_kind, fp.mask = capi.MASK_SEQLEN, x["lens"].data_ptr()
+            if p_drop > 0:
+                fp.dropout_kind, fp.p_drop = capi.DROPOUT_PHILOX, p_drop
+            fp.philox_seed, fp.philox_offset, fp.philox_bh_offset = 0x5EED0004, i, bh_offset
+            fp.status = status.data_ptr()
+            pl = dict(fp=fp, keep=[o, lse])
+            if train:
+                dq, dk, dv = (torch.empty_like(x["q"]) for _ in range(3))
+                bp = capi.bwd_params(x["d_o"], x["q"], x["k"], x["v"], o, lse, dq, dk, dv, mask_kind=capi.MASK_SEQLEN,
+                                     mask=x["lens"], p_drop=p_drop, seed=0x5EED0004, offset=i, bh_offset=bh_offset,
+                                     status=status)
+                ws = torch.empty(capi.bwd_workspace_bytes(bp), dtype=torch.uint8, device=dev)
+                bp.workspace, bp.workspace_bytes = ws.data_ptr(), ws.numel()
+                bpm = capi.BwdParams.from_buffer_copy(bp)   # main backward kernel alone
+                bpm.flags = capi.FLAG_BWD_SKIP_PREPARE | capi.FLAG_BWD_SKIP_FINISH
+                pl.update(bp=bp, bp_main=bpm)
+                pl["keep"] += [dq, dk, dv, ws]
+            self.plans.append(pl)
+        self.lens_host = [x["lens"].cpu().tolist() for x in self.sets]
+        self.n = len(self.plans)
+        self.h, self.s, self.d, self.train = h, s, d, train
+
+    def fwd(self, i, sp):
+        return self.lib.fmha_sm100_fwd(self.C.byref(self.plans[i % self.n]["fp"]), sp)
+
+    def bwd(self, i, sp, which="bp"):
+        return self.lib.fmha_sm100_bwd(self.C.byref(self.plans[i % self.n][which]), sp)
+
+    def step(self, i, sp):
+        rc = self.fwd(i, sp)
+        if self.train:
+            rc |= self.bwd(i, sp)
+        if rc != 0:
+            raise RuntimeError(f"kernel library call failed: {rc} {self.capi.strerror(rc)}")
+
+    def flops(self, fwd_granule):
+        """(executed forward, executed backward, dense forward, dense backward) flops of one step, averaged over the sets."""
+        ef = sum(executed_flops(l, self.h, self.s, self.d, 4.0, fwd_granule) for l in self.lens_host) / self.n
+        eb = sum(executed_flops(l, self.h, self.s, self.d, 10.0, 128) for l in self.lens_host) / self.n if self.train else 0.0
+        b = len(self.lens_host[0])
+        dense_f = 4.0 * b * self.h * self.s * self.s * self.d
+        return ef, eb, dense_f, (2.5 * dense_f if self.train else 0.0)
+
+
+def run_ours(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
 
     from nvfuserexamples_b200 import capi, sharding
-    from oracle import composite  # input recipe only (shapes, seeds); never on the timed path
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device (the kernels have no CPU fallback)")
@@ -173,59 +290,12 @@ def run_ours(args, rank, world, local_rank):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-
-    # ---- this rank's shard ---------------------------------------------------------------
-    if args.profile:
-        b_global = args.profile_batch  # reduced batch for profiler captures (still larger than L2)
-    elif args.scaling == "weak":
-        b_global = B0 * world          # per-GPU work fixed: every rank owns B0 batch elements
-    else:
-        b_global = B0                  # total work fixed
-    shard = sharding.make_shard(b_global, H, world, rank)
-    if not shard.whole_batches or shard.bh_count == 0:
-        raise SystemExit("bench.py: the batch does not split into whole batch elements per rank")
-    b_loc = shard.bh_count // H
-    n_sets = 2
-    sets = []
-    for i in range(n_sets):
-        x = composite.make_inputs(b_loc, H, S, D, torch.float16, LEN_RANGE, 1004 + 17 * rank + i, with_do=True)
-        sets.append({k: v.to(dev) for k, v in x.items()})
-    lens_host = [s["lens"].cpu().tolist() for s in sets]
-    lib = capi.load()
+    sampler = ClockSampler(local_rank)   # NVML is up before anything is timed
+    sampler.start()
     stream = torch.cuda.current_stream(dev)
     sp = stream.cuda_stream
     status = torch.zeros(4, dtype=torch.int32, device=dev)
-
-    # persistent outputs and parameter blocks (no allocation inside the timed region)
-    plans = []
-    for i, x in enumerate(sets):
-        o = torch.empty_like(x["q"])
-        lse = torch.empty(b_loc, H, S, dtype=torch.float32, device=dev)
-        dq, dk, dv = (torch.empty_like(x["q"]) for _ in range(3))
-        fp = capi.FwdParams()
-        fp.struct_bytes = C.sizeof(capi.FwdParams)
-        fp.dtype = capi.DTYPE_F16
-        fp.B, fp.H, fp.S_q, fp.S_k, fp.D = b_loc, H, S, S, D
-        fp.scale = 1.0 / math.sqrt(D)
-        fp.q, fp.k, fp.v, fp.o = (capi._t4(t) for t in (x["q"], x["k"], x["v"], o))
-        fp.lse = lse.data_ptr()
-        fp.mask_kind, fp.mask = capi.MASK_SEQLEN, x["lens"].data_ptr()
-        fp.dropout_kind, fp.p_drop = capi.DROPOUT_PHILOX, P_DROP
-        fp.philox_seed, fp.philox_offset, fp.philox_bh_offset = 0x5EED0004, i, shard.bh_offset
-        fp.status = status.data_ptr()
-        bp = capi.bwd_params(x["d_o"], x["q"], x["k"], x["v"], o, lse, dq, dk, dv, mask_kind=capi.MASK_SEQLEN,
-                             mask=x["lens"], p_drop=P_DROP, seed=0x5EED0004, offset=i, bh_offset=shard.bh_offset,
-                             status=status)
-        ws = torch.empty(capi.bwd_workspace_bytes(bp), dtype=torch.uint8, device=dev)
-        bp.workspace, bp.workspace_bytes = ws.data_ptr(), ws.numel()
-        plans.append(dict(fp=fp, bp=bp, keep=(o, lse, dq, dk, dv, ws)))
-
-    def step(i):
-        pl = plans[i % n_sets]
-        rc = lib.fmha_sm100_fwd(C.byref(pl["fp"]), sp)
-        rc |= lib.fmha_sm100_bwd(C.byref(pl["bp"]), sp)
-        if rc != 0:
-            raise RuntimeError(f"kernel library call failed: {rc} {capi.strerror(rc)}")
+    pk = peaks()
 
     def sync_all():
         torch.cuda.synchronize(dev)
@@ -233,84 +303,163 @@ def run_ours(args, rank, world, local_rank):
             dist.barrier()
             torch.cuda.synchronize(dev)
 
+    def all_max(x):
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    def all_sum(x):
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return t.item()
+
+    def timed(fn, n, leg, collective=True):
+        """n back-to-back calls of fn(i) between two CUDA events on the launching stream, barrier + synchronize on
+        both sides; returns the ms per call, as the MAX over ranks when `collective`."""
+        if collective:
+            sync_all()
+        else:
+            torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sampler.mark(leg)
+        e0.record(stream)
+        for i in range(n):
+            fn(i)
+        e1.record(stream)
+        if collective:
+            sync_all()
+        else:
+            torch.cuda.synchronize(dev)
+        sampler.unmark(leg)
+        ms = e0.elapsed_time(e1) / n
+        return all_max(ms) if collective else ms
+
+    # ---- this rank's shard of the headline workload: every rank owns a full B0 batch (weak scaling) -----------
+    if args.profile:
+        b_global = args.profile_batch  # reduced batch for profiler captures (still larger than L2)
+    else:
+        b_global = B0 * world
+    shard = sharding.make_shard(b_global, H, world, rank)
+    if not shard.whole_batches or shard.bh_count == 0:
+        raise SystemExit("bench.py: the batch does not split into whole batch elements per rank")
+    b_loc = shard.bh_count // H
+    plan = Plan(capi, dev, b_loc, H, S, D, torch.float16, LEN_RANGE, P_DROP, [1004 + 17 * rank + i for i in range(2)],
+                shard.bh_offset, status)
+
     if args.profile:
         # A handful of launches of one kernel for an ncu capture; prints no benchmark line.
-        which = {"fwd": lambda i: lib.fmha_sm100_fwd(C.byref(plans[i % n_sets]["fp"]), sp),
-                 "bwd": lambda i: lib.fmha_sm100_bwd(C.byref(plans[i % n_sets]["bp"]), sp)}[args.profile]
-        step(0)
+        which = {"fwd": lambda i: plan.fwd(i, sp), "bwd": lambda i: plan.bwd(i, sp)}[args.profile]
+        plan.step(0, sp)
         for i in range(3):
             which(i)
         torch.cuda.synchronize(dev)
         capi.check_status(status)
+        sampler.stop()
         print(json.dumps({"profile": args.profile, "B": b_loc, "launches": 3}), flush=True)
         return
 
     for i in range(args.warmup):
-        step(i)
+        plan.step(i, sp)
     capi.check_status(status)
 
-    # ---- timed region: exactly K steps --------------------------------------------------------
-    sampler = ClockSampler(local_rank)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sync_all()
-    sampler.start()
-    e0.record(stream)
-    for i in range(args.steps):
-        step(i)
-    e1.record(stream)
-    sync_all()
-    clocks = sampler.stop()
-    ms_total = e0.elapsed_time(e1)
-    t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_step = t.item() / args.steps
+    # ---- timed region: exactly K steps -------------------------------------------------------------------------
+    ms_step = timed(lambda i: plan.step(i, sp), args.steps, "timed")
     capi.check_status(status)
+    exe_f, exe_b, dense_f, dense_b = plan.flops(64)
+    value = all_sum(exe_f + exe_b) / (ms_step * 1e-3) / 1e12
+    dense_value = (dense_f + dense_b) * world / (ms_step * 1e-3) / 1e12
 
-    exe_step = [executed_flops(l, H, S, D, 4.0, 64) + executed_flops(l, H, S, D, 10.0, 128) for l in lens_host]  # per input set
-    exe_mean = sum(exe_step[i % n_sets] for i in range(args.steps)) / args.steps
-    exe_all = torch.tensor([exe_mean], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(exe_all, op=dist.ReduceOp.SUM)
-    value = exe_all.item() / (ms_step * 1e-3) / 1e12
-    dense_all = 14.0 * b_loc * world * H * S * S * D
-    dense_value = dense_all / (ms_step * 1e-3) / 1e12
+    # ---- sustained leg: the same step back to back for >= 2 s --------------------------------------------------
+    n_sus = max(args.steps, int(math.ceil(2000.0 / max(ms_step, 1e-3))))
+    ms_sus = timed(lambda i: plan.step(i, sp), n_sus, "sustained")
+    sus_clk = sampler.summary({"sustained"})
+    sustained = {"steps": n_sus, "ms_per_step": ms_sus, "value": all_sum(exe_f + exe_b) / (ms_sus * 1e-3) / 1e12,
+                 "unit": "TFLOP/s", "sm_mhz": sus_clk["sm_mhz"], "power_w_max": sus_clk["power_w_max"],
+                 "reasons": sus_clk["reasons"], "samples": sus_clk["samples"],
+                 "pct_of_measured_bf16_sustained_peak": (100.0 * all_sum(exe_f + exe_b) / (ms_sus * 1e-3) / 1e12 /
+                                                         (pk["tflops_sustained"] * world)) if pk["tflops_sustained"] else None}
 
-    # ---- kernel-level numbers (rank 0 only needs them, but every rank runs the same code) ------
-    def time_calls(fn, n):
-        for i in range(3):
-            fn(i)
-        torch.cuda.synchronize(dev)
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record(stream)
-        for i in range(n):
-            fn(i)
-        b.record(stream)
-        torch.cuda.synchronize(dev)
-        return a.elapsed_time(b) / n
-
+    # ---- kernel-level numbers -------------------------------------------------------------------------------------
     kn = max(20, min(args.steps, 200))
-    fwd_ms = time_calls(lambda i: lib.fmha_sm100_fwd(C.byref(plans[i % n_sets]["fp"]), sp), kn)
-    for pl in plans:  # main backward kernel alone: skip the delta/clear and the dQ conversion kernels
-        pl["bp_main"] = capi.BwdParams.from_buffer_copy(pl["bp"])
-        pl["bp_main"].flags = capi.FLAG_BWD_SKIP_PREPARE | capi.FLAG_BWD_SKIP_FINISH
-    bwd_main_ms = time_calls(lambda i: lib.fmha_sm100_bwd(C.byref(plans[i % n_sets]["bp_main"]), sp), kn)
-    bwd_all_ms = time_calls(lambda i: lib.fmha_sm100_bwd(C.byref(plans[i % n_sets]["bp"]), sp), kn)
-    pk = peaks()
-    exe_bwd = sum(executed_flops(l, H, S, D, 10.0) for l in lens_host) / n_sets
-    exe_fwd = sum(executed_flops(l, H, S, D, 4.0, 64) for l in lens_host) / n_sets
-    ach = exe_bwd / (bwd_main_ms * 1e-3) / 1e12
+    for i in range(3):
+        plan.step(i, sp)
+    fwd_ms = timed(lambda i: plan.fwd(i, sp), kn, "kernels", collective=False)
+    bwd_main_ms = timed(lambda i: plan.bwd(i, sp, "bp_main"), kn, "kernels", collective=False)
+    bwd_all_ms = timed(lambda i: plan.bwd(i, sp), kn, "kernels", collective=False)
+    ach = exe_b / (bwd_main_ms * 1e-3) / 1e12
     roofline = {"kernel": "fmha_bwd_kernel<64,fp16,seqlen,dropout>", "bound": "tensor", "achieved": ach, "peak": pk["tflops"],
-                "unit": "TFLOP/s", "frac": ach / pk["tflops"], "traffic": BWD_KERNEL_DRAM_TRAFFIC_B16 * b_loc / 16.0, "traffic_unit": "bytes per launch (ncu at B=16, scaled by batch)",
+                "unit": "TFLOP/s", "frac": ach / pk["tflops"], "traffic": BWD_KERNEL_DRAM_TRAFFIC_B16 * b_loc / 16.0,
+                "traffic_unit": "bytes per launch (ncu at B=16, scaled by batch)",
                 "peak_source": f"{pk['source']} bf16 burst", "ms_per_launch": bwd_main_ms,
-                "algorithmic_flops_per_launch": exe_bwd}
-    ach_f = exe_fwd / (fwd_ms * 1e-3) / 1e12
-    roofline_fwd = {"kernel": "fmha_fwd_fast_kernel<64,fp16,seqlen,dropout>", "bound": "tensor", "achieved": ach_f, "peak": pk["tflops"],
-                    "unit": "TFLOP/s", "frac": ach_f / pk["tflops"], "ms_per_launch": fwd_ms}
+                "algorithmic_flops_per_launch": exe_b}
+    ach_f = exe_f / (fwd_ms * 1e-3) / 1e12
+    roofline_fwd = {"kernel": "fmha_fwd_fast_kernel<64,fp16,seqlen,dropout>", "bound": "tensor", "achieved": ach_f,
+                    "peak": pk["tflops"], "unit": "TFLOP/s", "frac": ach_f / pk["tflops"], "ms_per_launch": fwd_ms,
+                    "dense_equiv_frac": dense_f / (fwd_ms * 1e-3) / 1e12 / pk["tflops"]}
 
-    # ---- end to end through the operator layer, host buffers in and out --------------------------
+    # ---- strong scaling: the FIXED B0 batch split over the ranks, and the same batch on one GPU ----------------
+    strong = None
+    if world > 1:
+        sh = sharding.make_shard(B0, H, world, rank)
+        if sh.whole_batches and sh.bh_count > 0:
+            sb = sh.bh_count // H
+            splan = Plan(capi, dev, sb, H, S, D, torch.float16, LEN_RANGE, P_DROP, [2004 + 31 * rank + i for i in range(2)],
+                         sh.bh_offset, status)
+            n_st = max(50, min(args.steps, 200))
+            for i in range(5):
+                splan.step(i, sp)
+            ms_n = timed(lambda i: splan.step(i, sp), n_st, "strong")
+            sf, sbk, _, _ = splan.flops(64)
+            exe_all = all_sum(sf + sbk)
+            # the whole fixed batch on rank 0 alone (the other ranks wait at the barrier inside timed()): `plan` holds B0
+            ms_1 = timed(lambda i: plan.step(i, sp) if rank == 0 else None, n_st, "strong")
+            n_q, n_kv = S // 128, S // 128
+            strong = {"global_batch": B0, "batch_per_gpu": sb, "ms_per_step": ms_n, "value": exe_all / (ms_n * 1e-3) / 1e12,
+                      "unit": "TFLOP/s", "ms_per_step_1gpu_same_run": ms_1, "efficiency": ms_1 / (world * ms_n),
+                      "steps": n_st,
+                      "work_per_gpu": {"bwd_items": sb * H * n_kv, "bwd_ctas": 148, "fwd_ctas": sb * H * n_q,
+                                       "bwd_waves": round(sb * H * n_kv / 148.0, 2)}}
+            del splan
+            torch.cuda.empty_cache()
+
+    # ---- the other named configurations on this run's ranks ----------------------------------------------------
+    other = {}
+    if not args.no_other_configs:
+        for name, cb, ch, cs, cd, cdt, clr, cp, ctrain, split in OTHER_CONFIGS:
+            dtype = getattr(torch, cdt)
+            if split == "strong":      # the configuration's batch, split over the ranks
+                csh = sharding.make_shard(cb, ch, world, rank)
+                if not csh.whole_batches or csh.bh_count == 0:
+                    continue
+                cb_loc, coff = csh.bh_count // ch, csh.bh_offset
+            else:                      # the configuration's per-GPU shard on every rank
+                cb_loc, coff = cb, rank * cb * ch
+            cplan = Plan(capi, dev, cb_loc, ch, cs, cd, dtype, clr, cp, [7 + rank], coff, status, train=ctrain,
+                         device_inputs=cs * cd >= 2048 * 128)
+            n_c = 30 if cs <= 512 else 5
+            for i in range(3):
+                cplan.step(i, sp)
+            f_ms = timed(lambda i: cplan.fwd(i, sp), n_c, "other")
+            ef, eb, df, db = cplan.flops(64 if cd == 64 else 128)
+            rec = {"B_per_gpu": cb_loc, "global_batch": int(all_sum(cb_loc)), "H": ch, "S": cs, "D": cd, "dtype": cdt, "p_drop": cp,
+                   "fwd_ms": f_ms, "fwd_executed_tflops": all_sum(ef) / f_ms / 1e9, "fwd_dense_tflops": df * world / f_ms / 1e9,
+                   "fwd_frac_of_measured_peak": all_sum(ef) / f_ms / 1e9 / (pk["tflops"] * world)}
+            if ctrain:
+                s_ms = timed(lambda i: cplan.step(i, sp), n_c, "other")
+                rec.update({"step_ms": s_ms, "bwd_ms": s_ms - f_ms, "step_executed_tflops": all_sum(ef + eb) / s_ms / 1e9,
+                            "step_dense_tflops": (df + db) * world / s_ms / 1e9,
+                            "step_frac_of_measured_peak": all_sum(ef + eb) / s_ms / 1e9 / (pk["tflops"] * world)})
+            capi.check_status(status)
+            other[name] = rec
+            del cplan
+            torch.cuda.empty_cache()
+
+    # ---- end to end through the operator layer, host buffers in and out --------------------------------------
     import mha_manual  # noqa: F401
     ops = torch.ops.mha_manual
+    sets = plan.sets
     host = {k: sets[0][k].cpu().pin_memory() for k in ("q", "k", "v", "d_o")}
     host_lens = sets[0]["lens"].cpu().pin_memory()
     host_out = [[torch.empty_like(host["q"]).pin_memory() for _ in range(4)] for _ in range(2)]   # two steps in flight
@@ -354,6 +503,7 @@ def run_ours(args, rank, world, local_rank):
         e2e_step(i)
     sync_all()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.mark("e2e")
     s_in.wait_stream(stream)
     a.record(s_in)
     for i in range(e2e_n):
@@ -361,15 +511,12 @@ def run_ours(args, rank, world, local_rank):
     s_out.wait_stream(stream)
     b.record(s_out)
     sync_all()
-    te = torch.tensor([a.elapsed_time(b) / e2e_n], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(te, op=dist.ReduceOp.MAX)
-    e2e_exe = torch.tensor([exe_step[0]], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(e2e_exe, op=dist.ReduceOp.SUM)
-    e2e_value = e2e_exe.item() / (te.item() * 1e-3) / 1e12
+    sampler.unmark("e2e")
+    te = all_max(a.elapsed_time(b) / e2e_n)
+    exe0 = executed_flops(plan.lens_host[0], H, S, D, 4.0, 64) + executed_flops(plan.lens_host[0], H, S, D, 10.0, 128)
+    e2e_value = all_sum(exe0) / (te * 1e-3) / 1e12
 
-    # ---- CPU baseline (N = 1 only, bounded sample) ---------------------------------------------------
+    # ---- CPU baseline (N = 1 only, bounded sample) ---------------------------------------------------------------
     cpu = None
     if rank == 0 and world == 1:
         torch.set_num_threads(len(os.sched_getaffinity(0)))
@@ -387,10 +534,15 @@ def run_ours(args, rank, world, local_rank):
                "sample": f"2 of {B0} batch elements (x{H} heads, S={S}, D={D}): fp32 eager composite + autograd, "
                          f"{n} iterations, {cdt * 1e3:.1f} ms each; dense flops"}
 
+    sampler.stop()
+    clocks = sampler.summary({"timed", "sustained", "kernels", "strong", "other"})
+    clocks["timed_region"] = sampler.summary({"timed"})
+    clocks["note"] = ("median SM clock over every device-timed leg of this run; the K-step region alone lasts "
+                      f"{ms_step * args.steps:.0f} ms")
     if rank == 0:
         print(json.dumps({
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "fp16 operands, fp32 accumulate", "data": "synthetic",
             "config": {"workload": WORKLOAD, "B_per_gpu": b_loc, "global_batch": b_loc * world, "H": H, "S": S, "D": D,
                        "p_drop": P_DROP, "valid_len": list(LEN_RANGE), "parallelism": f"bh-shard x{world}, no collective",
@@ -398,11 +550,14 @@ def run_ours(args, rank, world, local_rank):
                        "flops_counted": "executed: (4*ceil64(len_b) + 10*ceil128(len_b))*H*S*D per batch element"},
             "dense_equiv_tflops": dense_value,
             "pct_of_measured_bf16_peak": 100.0 * value / (pk["tflops"] * world),
+            "ms_per_step_x_sm_mhz": (ms_step * clocks["timed_region"]["sm_mhz"]) if clocks["timed_region"]["sm_mhz"] else
+                                    ((ms_step * clocks["sm_mhz"]) if clocks["sm_mhz"] else None),
+            "sustained": sustained, "strong": strong, "other_configs": other,
             "roofline": roofline, "roofline_fwd": roofline_fwd,
             "kernel_ms": {"fwd": fwd_ms, "bwd_main": bwd_main_ms, "bwd_all_three": bwd_all_ms},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": te.item(), "api": "torch.ops.mha_manual.fmha_fwd + fmha_bwd on pinned host buffers; copy-in, compute and copy-out of consecutive steps overlap on three streams"},
+                    "ms_per_step": te, "api": "torch.ops.mha_manual.fmha_fwd + fmha_bwd on pinned host buffers; copy-in, compute and copy-out of consecutive steps overlap on three streams"},
             "gpu_launches": 4 * args.steps,
             "clocks": clocks,
         }), flush=True)
@@ -410,8 +565,14 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
-# The other named configurations (device-resident inputs, kernel time only): one line each with `--configs`.
-# The long-sequence case is the per-GPU shard (B=256 over 8 GPUs).
+# The other named configurations: (name, B, H, S, D, dtype, valid lengths, p_drop, train, split).  split = "strong":
+# B is the configuration's whole batch and is divided over the ranks; "shard": B is the per-GPU shard of an 8-GPU
+# configuration (B=256 over 8 GPUs) and every rank runs one.
+OTHER_CONFIGS = [
+    ("bert_base_fwd", 32, 12, 512, 64, "float16", (256, 512), 0.1, False, "strong"),
+    ("bert_large_fwd", 64, 16, 384, 64, "float16", (128, 384), 0.1, False, "strong"),
+    ("long_seq_train_shard_of_8", 32, 16, 2048, 128, "bfloat16", (1024, 2048), 0.0, True, "shard"),
+]
 NAMED_CONFIGS = [
     ("bert_base_fwd", 32, 12, 512, 64, "float16", (256, 512), 0.1, False),
     ("bert_large_fwd", 64, 16, 384, 64, "float16", (128, 384), 0.1, False),
@@ -427,8 +588,7 @@ def run_configs(args):
 
     import torch
 
-    from nvfuserexamples_b200 import capi
-    from oracle import composite  # input recipe only
+    from nvfuserexamples_b200 import capi, workloads
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device (the kernels have no CPU fallback)")
@@ -453,7 +613,7 @@ def run_configs(args):
         if args.config_batch:
             b = args.config_batch      # reduced batch, e.g. for a profiler capture of one configuration
         dtype = getattr(torch, dt)
-        x = composite.make_inputs(b, h, s, d, dtype, len_range, 7, with_do=True)
+        x = workloads.make_inputs(b, h, s, d, dtype, len_range, 7, with_do=True)
         q, k, v, d_o, lens = (x[n].cuda() for n in ("q", "k", "v", "d_o", "lens"))
         kw = dict(mask_kind=capi.MASK_SEQLEN, mask=lens)
         fkw = dict(kw)
@@ -464,12 +624,15 @@ def run_configs(args):
         res = capi.fwd(q, k, v, out=o, **fkw)
         n = 30 if s <= 512 else 5     # every configuration's tensors exceed the L2 capacity
         step_f = 64 if d == 64 else 128
-        f_ms = timed(lambda: capi.fwd(q, k, v, out=o, **fkw), n)
+        if args.which in ("all", "fwd"):
+            f_ms = timed(lambda: capi.fwd(q, k, v, out=o, **fkw), n)
+        else:
+            f_ms = float("nan")
         exe_f = executed_flops(lens.tolist(), h, s, d, 4.0, step_f)
         line = {"config": name, "B": b, "H": h, "S": s, "D": d, "dtype": dt, "p_drop": p, "fwd_ms": round(f_ms, 4),
                 "fwd_dense_tflops": round(4.0 * b * h * s * s * d / f_ms / 1e9, 1),
                 "fwd_executed_tflops": round(exe_f / f_ms / 1e9, 1)}
-        if train:
+        if train and args.which in ("all", "bwd"):
             dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
             bp = capi.bwd_params(d_o, q, k, v, res["o"], res["lse"], dq, dk, dv, **kw)
             ws = torch.empty(capi.bwd_workspace_bytes(bp), dtype=torch.uint8, device="cuda")
@@ -490,13 +653,17 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
+    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak",
+                    help="accepted for compatibility: `value` is always the weak-scaling figure (B=32 per GPU) and the "
+                         "strong split of the fixed batch is always reported as the `strong` object of the same line")
     ap.add_argument("--profile", choices=["fwd", "bwd"], default=None,
                     help="run three launches of one kernel path on a reduced batch and exit (for ncu)")
     ap.add_argument("--profile-batch", type=int, default=16)
+    ap.add_argument("--no-other-configs", action="store_true", help="skip the `other_configs` legs")
     ap.add_argument("--configs", action="store_true",
                     help="kernel times of every named configuration on one GPU, one JSON line each (not the benchmark line)")
     ap.add_argument("--only", default=None, help="with --configs: run this named configuration alone")
+    ap.add_argument("--which", choices=["all", "fwd", "bwd"], default="all", help="with --configs: time only one direction")
     ap.add_argument("--config-batch", type=int, default=0, help="with --configs: override the batch size")
     args = ap.parse_args()
     if args.configs:

@@ -138,8 +138,28 @@ def _check(code: int, what: str) -> None:
 # ---------------------------------------------------------------------------------------
 # helpers that fill the structs from torch tensors
 # ---------------------------------------------------------------------------------------
+def _inner_contiguous(x, what: str) -> None:
+    """The C ABI cannot see the stride of the last axis: it must be 1 (raise instead of computing on the wrong elements)."""
+    if x.dim() < 3 or x.stride(-1) != 1:
+        raise ValueError(f"{what}: the head dimension must be the contiguous last axis (shape {tuple(x.shape)}, "
+                         f"strides {tuple(x.stride())})")
+
+
+def _lse_ok(lse, n: int) -> None:
+    import torch
+    if lse.dtype != torch.float32 or not lse.is_contiguous() or lse.numel() != n:
+        raise ValueError(f"lse must be a contiguous float32 tensor of {n} elements, got {lse.dtype} {tuple(lse.shape)} "
+                         f"strides {tuple(lse.stride())}")
+
+
+def _dense_ok(t, what: str) -> None:
+    if t is not None and hasattr(t, "is_contiguous") and not t.is_contiguous():
+        raise ValueError(f"{what} must be contiguous (strides {tuple(t.stride())})")
+
+
 def _t4(x) -> Tensor4:
     """[B,H,S,D] or [B*H,S,D] torch tensor -> fmha_tensor4 (element strides)."""
+    _inner_contiguous(x, "tensor operand")
     if x.dim() == 4:
         return Tensor4(x.data_ptr(), x.stride(0), x.stride(1), x.stride(2))
     return Tensor4(x.data_ptr(), x.stride(0), x.stride(0), x.stride(1))
@@ -190,6 +210,8 @@ def fwd(q, k, v, *, mask_kind=MASK_NONE, mask=None, dropout_kind=DROPOUT_NONE, d
     if want_lse:
         res["lse"] = torch.empty((B, H, S_q), dtype=torch.float32, device=q.device)
         p.lse = res["lse"].data_ptr()
+    _dense_ok(mask, "mask")
+    _dense_ok(dropout_mask, "dropout_mask")
     p.mask_kind = mask_kind
     p.mask = _ptr(mask)
     p.dropout_kind = dropout_kind
@@ -226,6 +248,8 @@ def bwd_params(d_o, q, k, v, o, lse, dq, dk, dv, *, mask_kind=MASK_NONE, mask=No
     p.B, p.H, p.S_q, p.S_k, p.D = B, H, S_q, S_k, D
     p.scale = float(scale) if scale is not None else 1.0 / math.sqrt(D)
     p.q, p.k, p.v, p.o, p.d_o = _t4(q), _t4(k), _t4(v), _t4(o), _t4(d_o)
+    _lse_ok(lse, B * H * S_q)
+    _dense_ok(mask, "mask")
     p.lse = lse.data_ptr()
     p.dq, p.dk, p.dv = _t4(dq), _t4(dk), _t4(dv)
     p.mask_kind = mask_kind
@@ -264,6 +288,7 @@ def bwd(d_o, q, k, v, o, lse, *, workspace=None, out=None, **kw):
 # ---------------------------------------------------------------------------------------
 def _t4_packed(x) -> Tensor4:
     """[total, H, D] torch tensor -> fmha_tensor4 (the batch stride is not used)."""
+    _inner_contiguous(x, "packed tensor operand")
     return Tensor4(x.data_ptr(), 0, x.stride(1), x.stride(0))
 
 
@@ -302,6 +327,8 @@ def bwd_varlen(d_o, q, k, v, o, lse, cu_seqlens, max_seqlen, *, p_drop=0.0, seed
     p.B, p.H, p.S_q, p.S_k, p.D = cu_seqlens.numel() - 1, H, max_seqlen, max_seqlen, D
     p.scale = float(scale) if scale is not None else 1.0 / math.sqrt(D)
     p.q, p.k, p.v, p.o, p.d_o = (_t4_packed(x) for x in (q, k, v, o, d_o))
+    _lse_ok(lse, H * total)
+    _dense_ok(cu_seqlens, "cu_seqlens")
     p.lse = lse.data_ptr()
     p.dq, p.dk, p.dv = _t4_packed(dq), _t4_packed(dk), _t4_packed(dv)
     p.mask_kind, p.mask, p.total_rows = MASK_CU_SEQLENS, cu_seqlens.data_ptr(), total

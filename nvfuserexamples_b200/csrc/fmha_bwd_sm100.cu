@@ -23,6 +23,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <atomic>
+
 #include <cstring>
 #include <type_traits>
 
@@ -117,7 +119,7 @@ __global__ void __launch_bounds__(256) bwd_prepare_kernel(const PrepArgs a) {
   int q_limit = a.S_q;
   if (a.cu_seqlens != nullptr) {
     const int base = a.cu_seqlens[b];
-    q_limit = a.cu_seqlens[b + 1] - base;
+    q_limit = min(a.cu_seqlens[b + 1] - base, a.S_q);   // rows past the stated maximum length take no part
     row_o = static_cast<int64_t>(base + r) * a.o_ss;
     row_do = static_cast<int64_t>(base + r) * a.do_ss;
   }
@@ -169,7 +171,7 @@ __global__ void __launch_bounds__(256) bwd_finish_kernel(const FinishArgs a) {
   int64_t row_dq = static_cast<int64_t>(b) * a.sb + static_cast<int64_t>(r) * a.ss;
   if (a.cu_seqlens != nullptr) {
     const int base = a.cu_seqlens[b];
-    if (r >= a.cu_seqlens[b + 1] - base) return;
+    if (r >= min(a.cu_seqlens[b + 1] - base, a.S_q)) return;   // rows past the stated maximum length take no part
     row_dq = static_cast<int64_t>(base + r) * a.ss;
   }
   const float4* src = reinterpret_cast<const float4*>(a.dq_accum + (static_cast<int64_t>(bh) * a.S_q_pad + r) * a.D + part * 8);
@@ -301,16 +303,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_slot;
   const WaitCtx wctx{abort_flag, a.status};
-#ifdef FMHA_TIMELINE
-  // Development aid (not compiled into the library): CTA 0 records clock64() stamps after its
-  // status words; TL(slot) is issued by the MMA warp and by the first compute thread.
-  long long* tl_buf = reinterpret_cast<long long*>(a.status + 16);
-  const bool tl_cta = (a.status != nullptr && blockIdx.x == 0);
-#define TL(slot) do { if (tl_cta && lane == 0 && (slot) < 256) tl_buf[slot] = clock64(); } while (0)
-#else
-#define TL(slot) do { } while (0)
-#endif
-  if (threadIdx.x == 0) TL(255);
 
   auto decode = [&](int id) {
     BwdItem it;
@@ -335,7 +327,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
       } else if (packed) {
         const int* cu = reinterpret_cast<const int*>(a.mask);
         it.row_base = cu[it.b];
-        const int len = cu[it.b + 1] - it.row_base;
+        // a sequence longer than the stated maximum is cut there: its tiles would otherwise run into the next
+        // head's rows of the dQ accumulator and of delta
+        const int len = min(cu[it.b + 1] - it.row_base, a.S_q);
         k_limit = len;
         it.q_limit = len;
         it.n_q = (len + kTileM - 1) / kTileM;
@@ -453,14 +447,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
       const uint64_t dK_m = make_smem_desc_sw128(smem_u32(sK + kvb * L::kTileBytes), 16384, 1024);   // K as MN-major B (dQ)
       const int n_q = cur.n_q;
       for (int i = 0; i < n_q; ++i, ++t) {
-        TL(t * 16 + 0);
         const int s = t % ST;
         if constexpr (EARLY) {
           if (i + 1 < n_q) {
             mbar_wait(sdp_free, t & 1, wctx, kSiteSdpFree);
             mbar_wait(qdo_full + ((t + 1) % ST), ((t + 1) / ST) & 1, wctx, kSiteQdoFull);
             tc_fence_after_sync();
-            TL(t * 16 + 1);
             issue_s((t + 1) % ST, kvb);
             issue_dp((t + 1) % ST, kvb);
           } else {
@@ -473,7 +465,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
               mbar_wait(sdp_free, t & 1, wctx, kSiteSdpFree);
               mbar_wait(qdo_full + ((t + 1) % ST), ((t + 1) / ST) & 1, wctx, kSiteQdoFull);
               tc_fence_after_sync();
-              TL(t * 16 + 1);
               issue_s((t + 1) % ST, nkvb);
               issue_dp((t + 1) % ST, nkvb);
               ahead = true;
@@ -486,9 +477,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
         const uint64_t dP_m = make_smem_desc_sw128(smem_u32(sP), 16384, 1024);
         const uint64_t ddS_m = make_smem_desc_sw128(smem_u32(sdS), 16384, 1024);
         const uint64_t ddS_k = make_smem_desc_sw128(smem_u32(sdS), 16, 1024);
-        TL(t * 16 + 2);
         mbar_wait(pds_full, t & 1, wctx, kSitePdsFull);
-        TL(t * 16 + 3);
         tc_fence_after_sync();
         // dV += P^T dO ; dK += dS^T Q : A is the [q x keys] tile read MN-major (keys contiguous),
         // 16 query rows (2048 B) per k-step, the two 64-key halves 16 KB apart.
@@ -513,12 +502,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
         }
         umma_commit_elect(qdo_empty + s);  // Q and dO of this stage are not read again (dQ needs dS and K only)
         if (i == n_q - 1) umma_commit_elect(acc_full);
-        TL(t * 16 + 4);
         if (t > 0) {
           mbar_wait(dq_free, (t - 1) & 1, wctx, kSiteDqFree);
           tc_fence_after_sync();
         }
-        TL(t * 16 + 5);
         // dQ tile = dS K : A K-major (keys along the row), B = K tile read MN-major
         {
           uint64_t x[8], y[8];
@@ -531,7 +518,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
         }
         umma_commit_elect(dq_full);
         if (i == n_q - 1) umma_commit_elect(kv_empty + kvb);   // K and V of this item are not read again
-        TL(t * 16 + 6);
         if constexpr (!EARLY) {
           if (i + 1 < n_q) {
             mbar_wait(qdo_full + ((t + 1) % ST), ((t + 1) / ST) & 1, wctx, kSiteQdoFull);
@@ -601,16 +587,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
     // issues the reduce, so the warps never wait for one another here.
     auto dq_readout_warp = [&](int tt, int row0) {
       wait_all(dq_full, tt & 1, kSiteDqFull);
-      if (tid == 0) TL((tt + 1) * 16 + 7);
       uint32_t t16[16];
       tmem_ld16(tmem_base + lane_addr + kColdQ + cq * 16, t16);
       tmem_wait_ld();
       tc_fence_before_sync();
       mbar_arrive(dq_free);                          // the dQ columns may be overwritten
-      if (tid == 0) TL((tt + 1) * 16 + 14);
       if (lane == 0) tma_store_wait_read();          // this warp's previous reduce has read its staging tile
       __syncwarp();
-      if (tid == 0) TL((tt + 1) * 16 + 15);
       uint8_t* stage = sDQ + cw * 2048;
       const uint32_t rowaddr = smem_u32(stage) + lane * 64;
       const uint32_t sw = (lane >> 1) & 3;           // 64-byte swizzle: 16-byte chunk ^= bits 7..8 of the offset
@@ -766,9 +749,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
             kw8[d * 4 + 3] = (draw.w & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
           }
         }
-        if (tid == 0) TL(t * 16 + 8);
         wait_all(sdp_full, t & 1, kSiteSdpFull);
-        if (tid == 0) TL(t * 16 + 9);
         // The 32 columns are processed as two halves of 16: the second half of S and dP is fetched
         // from tensor memory only after the first has been turned into packed P and dS, which keeps
         // 32 fewer values live (the kernel is bound by the ALU pipe, and with all 64 values in
@@ -827,12 +808,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
           tmem_wait_ld_dep16(rs, rp);
           tc_fence_before_sync();
           mbar_arrive(sdp_free);   // the tensor core may overwrite S and dP now
-          if (tid == 0) TL(t * 16 + 10);
           if (n_cols >= kTileN) half_chunk(std::false_type{}, std::integral_constant<int, 1>{}, rs, rp);
           else half_chunk(std::true_type{}, std::integral_constant<int, 1>{}, rs, rp);
         }
 
-        if (tid == 0) TL(t * 16 + 11);
         if constexpr (EARLY) {
           // dQ of the previous tile is complete <=> the MMAs which read the single P/dS buffer have
           // completed, so it can be overwritten below (the dQ tile itself is read out afterwards).
@@ -872,7 +851,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
         }
         fence_proxy_async_smem();
         mbar_arrive(pds_full);
-        if (tid == 0) TL(t * 16 + 12);
         const int row0 = bh * a.S_q_pad + i * kTileM;
         if constexpr (EARLY) {
           if (t > 0) dq_readout_warp(t - 1, prev_row0);
@@ -880,7 +858,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
         } else {
           dq_readout_tma(t, row0);   // D = 128: dQ shares columns with dP, it must be out before dP of tile t+1
         }
-        if (tid == 0) TL(t * 16 + 13);
       }
       prev_id = cur.id;
       ++w;
@@ -900,7 +877,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
       store_dkdv(prev_id, true);
     }
     if (lane == 0) tma_store_wait_read();   // shared memory stays valid until the TMA unit has read it
-    if (tid == 0) TL(254);
   }
 
   tc_fence_before_sync();
@@ -913,7 +889,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fmha_bwd_kernel(const __grid_c
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
   }
-#undef TL
 }
 
 // ---------------------------------------------------------------------------------------
@@ -923,8 +898,8 @@ template <int D, bool BF16, bool KEYADD, bool DROP, bool PACKED = false>
 static int launch_bwd_impl(const BwdArgs& a, cudaStream_t stream) {
   using L = BwdSmem<D>;
   auto kfn = fmha_bwd_kernel<D, BF16, KEYADD, DROP, PACKED>;
-  static bool configured[64] = {};
-  static int sm_count[64] = {};
+  static std::atomic<bool> configured[64] = {};   // per device; set after the attribute call succeeded
+  static std::atomic<int> sm_count[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   int sms = 0;

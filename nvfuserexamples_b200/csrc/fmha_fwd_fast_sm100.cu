@@ -24,6 +24,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <atomic>
+
 #include "../../include/fmha_sm100.h"
 #include "fmha_device_utils.cuh"
 #include "fmha_kernel_args.h"
@@ -111,15 +113,6 @@ __device__ __forceinline__ void softmax_chunk(const uint32_t (&r)[32], int cbase
 template <int D, bool BF16, bool KEYADD, bool DROP, bool PACKED = false>
 __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_fwd_fast_kernel(const __grid_constant__ FwdArgs a) {
   griddep_wait();
-#ifdef FMHA_TIMELINE
-  // Development aid (not compiled into the library): one CTA records clock64() stamps behind its status words.
-  long long* tl_buf = reinterpret_cast<long long*>(a.status + 16);
-  const bool tl_cta = (a.status != nullptr && blockIdx.x == 1 && blockIdx.y == 3 && blockIdx.z == gridDim.z / 2);
-#define FTL(slot) do { if (tl_cta && (threadIdx.x & 31) == 0 && (slot) < 256) tl_buf[slot] = clock64(); } while (0)
-#else
-#define FTL(slot) do { } while (0)
-#endif
-  if (threadIdx.x == 64) FTL(252);
   using L = FastSmem<D>;
   constexpr int ST = L::kStages;
   constexpr int TN = L::TN;
@@ -168,7 +161,7 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
   } else if (packed) {
     const int* cu = reinterpret_cast<const int*>(a.mask);
     row_base = cu[b];
-    const int len = cu[b + 1] - row_base;
+    const int len = min(cu[b + 1] - row_base, a.S_q);   // a sequence longer than the stated maximum is cut there
     k_limit = len;
     q_limit = len;
     tb = 0;
@@ -204,7 +197,6 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_slot;
   const WaitCtx wctx{abort_flag, a.status};
-  if (threadIdx.x == 64) FTL(255);
 
   if (warp == 0) {
     // ============================ TMA producer ======================================
@@ -257,9 +249,7 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
         else umma_ss_x8(tS, aq, bk, kIdescQK, 0u);
         umma_commit_elect(k_empty + s);
         umma_commit_elect(s_full);
-        FTL(j * 16 + 0);
         mbar_wait(p_full, j & 1, wctx, kFPFull);
-        FTL(j * 16 + 1);
         mbar_wait(v_full + s, ph, wctx, kFVFull);
         tc_fence_after_sync();
         const uint32_t acc0 = (j > 0) ? 1u : 0u;
@@ -272,7 +262,6 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
           umma_ts_x4(tO, tS + 32u, 8u, b1, kIdescPV, 1u);
         }
         umma_commit_elect(v_empty + s);
-        FTL(j * 16 + 2);
       }
       umma_commit_elect(o_full);
     }
@@ -318,10 +307,8 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
           keepw[d * 4 + 3] = (draw.w & 0x7F7F7F7Fu) + (0x80u - a.philox_thr) * 0x01010101u;
         }
       }
-      if (tid == 0) FTL(j * 16 + 7);
       mbar_wait(s_full, j & 1, wctx, kFSFull, 32);
       tc_fence_after_sync();
-      if (tid == 0) FTL(j * 16 + 8);
 
       // ---- sweep 1: row maximum --------------------------------------------------------
       float tile_max = -INFINITY;
@@ -356,8 +343,6 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
         }
         if constexpr (!KEYADD) tile_max *= sl2;  // scale > 0: the maximum commutes with it
       }
-
-      if (tid == 0) FTL(j * 16 + 9);
       // ---- running reference maximum, lazy rescale of O ------------------------------------
       {
         float m_new = fmaxf(m_ref, tile_max);
@@ -379,8 +364,6 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
         sum2.y *= alpha;
         m_ref = m_new;
       }
-
-      if (tid == 0) FTL(j * 16 + 10);
       // ---- sweep 2: exponentials, dropout, P (next chunk's load in flight) ----------------------
       {
         const float neg_m = -m_ref;
@@ -406,13 +389,11 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(p_full);
-      if (tid == 0) FTL(j * 16 + 11);
     }
 
     // ---- epilogue ------------------------------------------------------------------------
     mbar_wait(o_full, 0, wctx, kFOFull, 32);
     tc_fence_after_sync();
-    if (tid == 0) FTL(250);
     const float l_sum = sum2.x + sum2.y;
     const float out_scale = (DROP ? a.dropout_scale : 1.0f) / l_sum;
     if (a.lse != nullptr && row_ok) {
@@ -454,7 +435,6 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
         tma_store_commit();
       }
       tma_store_wait_read();  // the shared-memory source must outlive the copy; the writes finish on their own
-      FTL(251);
     }
   }
 
@@ -467,7 +447,6 @@ __global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
-    FTL(253);
   }
 }
 
@@ -475,7 +454,7 @@ template <int D, bool BF16, bool KEYADD, bool DROP, bool PACKED = false>
 static int launch_fast_impl(const FwdArgs& a, cudaStream_t stream) {
   using L = FastSmem<D>;
   auto kfn = fmha_fwd_fast_kernel<D, BF16, KEYADD, DROP, PACKED>;
-  static bool configured[64] = {};
+  static std::atomic<bool> configured[64] = {};   // per device; set after the attribute call succeeded
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !configured[dev]) {

@@ -27,6 +27,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <atomic>
+
 #include "../../include/fmha_sm100.h"
 #include "fmha_device_utils.cuh"
 #include "fmha_kernel_args.h"
@@ -554,7 +556,7 @@ template <int D, bool BF16, bool LEGACY, bool PSMEM>
 static int launch_fwd_impl(const FwdArgs& a, cudaStream_t stream) {
   using L = FwdSmem<D, PSMEM>;
   auto kfn = fmha_fwd_kernel<D, BF16, LEGACY, PSMEM>;
-  static bool configured[64] = {};
+  static std::atomic<bool> configured[64] = {};   // per device; set after the attribute call succeeded
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !configured[dev]) {

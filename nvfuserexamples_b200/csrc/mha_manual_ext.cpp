@@ -22,6 +22,8 @@
 #include <torch/extension.h>
 
 #include <cmath>
+#include <ATen/cuda/CUDAGraphsUtils.cuh>
+
 #include <cstdlib>
 #include <mutex>
 #include <vector>
@@ -38,8 +40,13 @@ at::Tensor& status_block(int device) {
   static at::Tensor blocks[kMaxDevices];
   std::lock_guard<std::mutex> g(mu);
   TORCH_CHECK(device >= 0 && device < kMaxDevices, "mha_manual: device index out of range");
-  if (!blocks[device].defined())
+  if (!blocks[device].defined()) {
+    // A tensor allocated during a stream capture lives in the graph's private pool: the block must exist before.
+    TORCH_CHECK(at::cuda::currentStreamCaptureStatus() == at::cuda::CaptureStatus::None,
+                "mha_manual: the first operator call on a device allocates its status block; make one call before "
+                "capturing a CUDA graph");
     blocks[device] = at::zeros({4}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device));
+  }
   return blocks[device];
 }
 
@@ -266,6 +273,17 @@ std::tuple<at::Tensor, at::Tensor> fmha_fwd(const at::Tensor& q, const at::Tenso
   return {o, lse};
 }
 
+
+// An incoming gradient may be any view (autograd hands out expanded, i.e. stride-0, tensors for a broadcast loss):
+// what the tensor maps cannot describe - a non-contiguous last axis, a zero, negative or non-multiple-of-8 outer
+// stride, a misaligned base - is copied to a dense tensor first.
+at::Tensor dense_if_needed(const at::Tensor& t) {
+  bool ok = t.stride(-1) == 1 && (reinterpret_cast<uintptr_t>(t.data_ptr()) & 15) == 0;
+  for (int64_t d = 0; ok && d + 1 < t.dim(); ++d)
+    if (t.size(d) > 1 && (t.stride(d) <= 0 || t.stride(d) % 8 != 0)) ok = false;
+  return ok ? t : t.contiguous();
+}
+
 // Backward into caller-allocated dq, dk, dv (any strides with a contiguous last axis).
 void bwd_into(const at::Tensor& d_o, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& o,
               const at::Tensor& lse, const at::Tensor& dq, const at::Tensor& dk, const at::Tensor& dv,
@@ -273,7 +291,7 @@ void bwd_into(const at::Tensor& d_o, const at::Tensor& q, const at::Tensor& k, c
               int64_t offset, c10::optional<double> scale, int64_t bh_offset,
               const c10::optional<at::Tensor>& offset_tensor, const char* what) {
   const View4 vq = view4(q, "q"), vk = view4(k, "k"), vv = view4(v, "v"), vo = view4(o, "o");
-  at::Tensor d_o_c = d_o.stride(-1) == 1 ? d_o : d_o.contiguous();
+  at::Tensor d_o_c = dense_if_needed(d_o);
   const View4 vdo = view4(d_o_c, "d_o");
   check_same(q, k, "k"); check_same(q, v, "v"); check_same(q, o, "o"); check_same(q, d_o_c, "d_o");
   check_qkv(vq, vk, vv);
@@ -442,7 +460,8 @@ std::tuple<at::Tensor, at::Tensor> fmha_varlen_fwd(const at::Tensor& q, const at
                                                    int64_t seed, int64_t offset, c10::optional<double> scale,
                                                    const c10::optional<at::Tensor>& offset_tensor) {
   TORCH_CHECK(q.is_cuda(), "mha_manual: q must be a CUDA tensor");
-  at::Tensor o = at::empty(q.sizes(), q.options());
+  // zero-filled: rows of a sequence beyond max_seqlen (where the kernels cut it) are never written
+  at::Tensor o = at::zeros(q.sizes(), q.options());
   at::Tensor lse = varlen_fwd_into(q, k, v, o, cu_seqlens, max_seqlen, p_drop, seed, offset, scale, offset_tensor, "fmha_varlen_fwd");
   return {o, lse};
 }
@@ -453,7 +472,7 @@ void varlen_bwd_into(const at::Tensor& d_o, const at::Tensor& q, const at::Tenso
                      const at::Tensor& cu_seqlens, int64_t max_seqlen, double p_drop, int64_t seed, int64_t offset,
                      c10::optional<double> scale, const c10::optional<at::Tensor>& offset_tensor, const char* what) {
   const Packed vq = packed3(q, "q"), vk = packed3(k, "k"), vv = packed3(v, "v"), vo = packed3(o, "o");
-  at::Tensor d_o_c = d_o.stride(-1) == 1 ? d_o : d_o.contiguous();
+  at::Tensor d_o_c = dense_if_needed(d_o);
   const Packed vdo = packed3(d_o_c, "d_o");
   check_same(q, k, "k"); check_same(q, v, "v"); check_same(q, o, "o"); check_same(q, d_o_c, "d_o");
   check_packed_qkv(vq, vk, vv, max_seqlen);
@@ -499,9 +518,10 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_varlen_bwd(const at::Tensor&
                                                                int64_t seed, int64_t offset, c10::optional<double> scale,
                                                                const c10::optional<at::Tensor>& offset_tensor) {
   TORCH_CHECK(q.is_cuda() && k.is_cuda() && v.is_cuda(), "mha_manual: q, k, v must be CUDA tensors");
-  at::Tensor dq = at::empty(q.sizes(), q.options());
-  at::Tensor dk = at::empty(k.sizes(), k.options());
-  at::Tensor dv = at::empty(v.sizes(), v.options());
+  // zero-filled: rows of a sequence beyond max_seqlen (where the kernels cut it) are never written
+  at::Tensor dq = at::zeros(q.sizes(), q.options());
+  at::Tensor dk = at::zeros(k.sizes(), k.options());
+  at::Tensor dv = at::zeros(v.sizes(), v.options());
   varlen_bwd_into(d_o, q, k, v, o, lse, dq, dk, dv, cu_seqlens, max_seqlen, p_drop, seed, offset, scale, offset_tensor,
                   "fmha_varlen_bwd");
   return {dq, dk, dv};
@@ -519,7 +539,7 @@ std::tuple<at::Tensor, at::Tensor> fmha_varlen_qkvpacked_fwd(const at::Tensor& q
                                                              c10::optional<double> scale,
                                                              const c10::optional<at::Tensor>& offset_tensor) {
   check_varlen_qkvpacked(qkv);
-  at::Tensor o = at::empty({qkv.size(0), qkv.size(2), qkv.size(3)}, qkv.options());
+  at::Tensor o = at::zeros({qkv.size(0), qkv.size(2), qkv.size(3)}, qkv.options());
   at::Tensor lse = varlen_fwd_into(qkv.select(1, 0), qkv.select(1, 1), qkv.select(1, 2), o, cu_seqlens, max_seqlen, p_drop, seed,
                                    offset, scale, offset_tensor, "fmha_varlen_qkvpacked_fwd");
   return {o, lse};
@@ -529,7 +549,7 @@ at::Tensor fmha_varlen_qkvpacked_bwd(const at::Tensor& d_o, const at::Tensor& qk
                                      int64_t offset, c10::optional<double> scale,
                                      const c10::optional<at::Tensor>& offset_tensor) {
   check_varlen_qkvpacked(qkv);
-  at::Tensor dqkv = at::empty(qkv.sizes(), qkv.options());
+  at::Tensor dqkv = at::zeros(qkv.sizes(), qkv.options());
   varlen_bwd_into(d_o, qkv.select(1, 0), qkv.select(1, 1), qkv.select(1, 2), o, lse, dqkv.select(1, 0), dqkv.select(1, 1),
                   dqkv.select(1, 2), cu_seqlens, max_seqlen, p_drop, seed, offset, scale, offset_tensor,
                   "fmha_varlen_qkvpacked_bwd");
@@ -773,6 +793,45 @@ at::Tensor fmha_autograd(const at::Tensor& q, const at::Tensor& k, const at::Ten
   return FmhaFunction::apply(q, k, v, mask, seqlens, p_drop, seed, offset, scale, offset_tensor);
 }
 
+// The same four operators below the autograd keys (torch.inference_mode(), a redispatch from another autograd
+// layer): forward only, no graph is recorded.  Registered for the CUDA and Meta keys; they go through the dispatcher,
+// so a Meta call lands in the shape-only kernels.
+template <typename Ret, typename... Args>
+Ret call_op(const char* name, Args... args) {
+  return c10::Dispatcher::singleton().findSchemaOrThrow(name, "").typed<Ret(Args...)>().call(args...);
+}
+at::Tensor fmha_noautograd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const c10::optional<at::Tensor>& mask,
+                           const c10::optional<at::Tensor>& seqlens, double p_drop, int64_t seed, int64_t offset,
+                           c10::optional<double> scale, const c10::optional<at::Tensor>& offset_tensor) {
+  return std::get<0>(call_op<std::tuple<at::Tensor, at::Tensor>, const at::Tensor&, const at::Tensor&, const at::Tensor&,
+                             const c10::optional<at::Tensor>&, const c10::optional<at::Tensor>&, double, int64_t, int64_t,
+                             c10::optional<double>, int64_t, const c10::optional<at::Tensor>&>(
+      "mha_manual::fmha_fwd", q, k, v, mask, seqlens, p_drop, seed, offset, scale, 0, offset_tensor));
+}
+at::Tensor fmha_qkvpacked_noautograd(const at::Tensor& qkv, const c10::optional<at::Tensor>& mask,
+                                     const c10::optional<at::Tensor>& seqlens, double p_drop, int64_t seed, int64_t offset,
+                                     c10::optional<double> scale, const c10::optional<at::Tensor>& offset_tensor) {
+  return std::get<0>(call_op<std::tuple<at::Tensor, at::Tensor>, const at::Tensor&, const c10::optional<at::Tensor>&,
+                             const c10::optional<at::Tensor>&, double, int64_t, int64_t, c10::optional<double>, int64_t,
+                             const c10::optional<at::Tensor>&>("mha_manual::fmha_qkvpacked_fwd", qkv, mask, seqlens, p_drop, seed,
+                                                               offset, scale, 0, offset_tensor));
+}
+at::Tensor fmha_varlen_noautograd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& cu_seqlens,
+                                  int64_t max_seqlen, double p_drop, int64_t seed, int64_t offset, c10::optional<double> scale,
+                                  const c10::optional<at::Tensor>& offset_tensor) {
+  return std::get<0>(call_op<std::tuple<at::Tensor, at::Tensor>, const at::Tensor&, const at::Tensor&, const at::Tensor&,
+                             const at::Tensor&, int64_t, double, int64_t, int64_t, c10::optional<double>,
+                             const c10::optional<at::Tensor>&>("mha_manual::fmha_varlen_fwd", q, k, v, cu_seqlens, max_seqlen,
+                                                               p_drop, seed, offset, scale, offset_tensor));
+}
+at::Tensor fmha_varlen_qkvpacked_noautograd(const at::Tensor& qkv, const at::Tensor& cu_seqlens, int64_t max_seqlen, double p_drop,
+                                            int64_t seed, int64_t offset, c10::optional<double> scale,
+                                            const c10::optional<at::Tensor>& offset_tensor) {
+  return std::get<0>(call_op<std::tuple<at::Tensor, at::Tensor>, const at::Tensor&, const at::Tensor&, int64_t, double, int64_t,
+                             int64_t, c10::optional<double>, const c10::optional<at::Tensor>&>(
+      "mha_manual::fmha_varlen_qkvpacked_fwd", qkv, cu_seqlens, max_seqlen, p_drop, seed, offset, scale, offset_tensor));
+}
+
 // ---------------------------------------------------------------------------------------
 // shape-only kernels (Meta key): what fake-tensor tracing and torch.compile need.  They check the
 // same shape rules as the CUDA kernels' wrappers and allocate outputs of the same shapes.
@@ -977,6 +1036,10 @@ TORCH_LIBRARY_IMPL(mha_manual, CUDA, m) {
   m.impl("fmha_qkvpacked_bwd", fmha_qkvpacked_bwd);
   m.impl("fmha_varlen_qkvpacked_fwd", fmha_varlen_qkvpacked_fwd);
   m.impl("fmha_varlen_qkvpacked_bwd", fmha_varlen_qkvpacked_bwd);
+  m.impl("fmha", fmha_noautograd);
+  m.impl("fmha_varlen", fmha_varlen_noautograd);
+  m.impl("fmha_qkvpacked", fmha_qkvpacked_noautograd);
+  m.impl("fmha_varlen_qkvpacked", fmha_varlen_qkvpacked_noautograd);
 }
 
 TORCH_LIBRARY_IMPL(mha_manual, Meta, m) {
@@ -991,6 +1054,10 @@ TORCH_LIBRARY_IMPL(mha_manual, Meta, m) {
   m.impl("fmha_qkvpacked_bwd", fmha_qkvpacked_bwd_meta);
   m.impl("fmha_varlen_qkvpacked_fwd", fmha_varlen_qkvpacked_fwd_meta);
   m.impl("fmha_varlen_qkvpacked_bwd", fmha_varlen_qkvpacked_bwd_meta);
+  m.impl("fmha", fmha_noautograd);
+  m.impl("fmha_varlen", fmha_varlen_noautograd);
+  m.impl("fmha_qkvpacked", fmha_qkvpacked_noautograd);
+  m.impl("fmha_varlen_qkvpacked", fmha_varlen_qkvpacked_noautograd);
 }
 
 TORCH_LIBRARY_IMPL(mha_manual, Autograd, m) {

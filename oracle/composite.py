@@ -114,29 +114,7 @@ def attention_numpy(q: np.ndarray, k: np.ndarray, v: np.ndarray, add_mask=None, 
 
 
 # ----------------------------------------------------------------------------------------
-# synthetic inputs of the benchmark configurations
+# synthetic inputs of the benchmark configurations: the recipe (shapes, seeds, generators) lives with the
+# library's workload definitions, which know nothing of this oracle; re-exported here for the tests
 # ----------------------------------------------------------------------------------------
-# name: (B, H, S, D, dtype, (len_lo, len_hi), p_drop, mode)
-CONFIGS = {
-    "cpu_composite": (2, 4, 128, 64, torch.float32, (64, 128), 0.0, "fwd"),
-    "bert_base_fwd": (32, 12, 512, 64, torch.float16, (256, 512), 0.1, "fwd"),
-    "bert_large_fwd": (64, 16, 384, 64, torch.float16, (128, 384), 0.1, "fwd"),
-    "bert_large_train": (32, 16, 512, 64, torch.float16, (256, 512), 0.1, "fwd+bwd"),
-    "long_seq_train": (256, 16, 2048, 128, torch.bfloat16, (1024, 2048), 0.0, "fwd+bwd"),
-}
-CONFIG_SEEDS = {name: 1001 + i for i, name in enumerate(CONFIGS)}
-PHILOX_SEEDS = {name: 0x5EED0001 + i for i, name in enumerate(CONFIGS)}
-
-
-def make_inputs(B: int, H: int, S: int, D: int, dtype, len_range, seed: int, with_do: bool = False):
-    """Seeded N(0,1) Q/K/V (generated in fp32 on the CPU, then cast) and per-batch valid lengths
-    drawn uniformly from [len_lo, len_hi]."""
-    g = torch.Generator().manual_seed(seed)
-    q = torch.randn(B, H, S, D, generator=g).to(dtype)
-    k = torch.randn(B, H, S, D, generator=g).to(dtype)
-    v = torch.randn(B, H, S, D, generator=g).to(dtype)
-    lens = torch.randint(len_range[0], len_range[1] + 1, (B,), generator=g, dtype=torch.int32)
-    out = dict(q=q, k=k, v=v, lens=lens)
-    if with_do:
-        out["d_o"] = torch.randn(B, H, S, D, generator=g).to(dtype)
-    return out
+from nvfuserexamples_b200.workloads import CONFIG_SEEDS, CONFIGS, PHILOX_SEEDS, make_inputs  # noqa: E402,F401

@@ -190,6 +190,75 @@ def test_full_size_linearity_in_d_o(cuda_device):
     helpers.assert_close(sl(g1[2]), rdv, "dv slice")
 
 
+@pytest.mark.parametrize("seed", [1004, 1005])
+def test_bench_batch_many_slices_against_oracle(cuda_device, seed):
+    """The benchmark's own batches (bench.py: B=32, H=16, S=512, D=64 fp16, input seeds 1004 and 1005, Philox seed
+    0x5EED0004, offset = input set) through forward + backward at full size; 16 (batch, head) slices spread over the
+    batch - first and last heads of a batch element, neighbours in the order the persistent backward CTAs draw their
+    work items - are each compared with the oracle (about 0.1 s of CPU per slice)."""
+    from nvfuserexamples_b200 import workloads
+    B, H, S, D, p = 32, 16, 512, 64, 0.1
+    x = workloads.make_inputs(B, H, S, D, torch.float16, (256, 512), seed, with_do=True)
+    q, k, v, d_o, lens = (x[n].to(cuda_device) for n in ("q", "k", "v", "d_o", "lens"))
+    pseed, off = 0x5EED0004, seed - 1004
+    status = torch.zeros(4, dtype=torch.int32, device=cuda_device)
+    o, lse = api.fmha_forward(q, k, v, seqlens=lens, p_drop=p, seed=pseed, offset=off, status=status)
+    dq, dk, dv = api.fmha_backward(d_o, q, k, v, o, lse, seqlens=lens, p_drop=p, seed=pseed, offset=off, status=status)
+    assert capi.check_status(status) == [0, 0, 0, 0]
+    g = torch.Generator().manual_seed(seed)
+    picks = {(0, 0), (0, H - 1), (B - 1, H - 1), (B - 1, 0), (9, 3), (9, 4)}   # boundaries and neighbours ...
+    while len(picks) < 16:                                                      # ... and random ones
+        picks.add((int(torch.randint(0, B, (1,), generator=g)), int(torch.randint(0, H, (1,), generator=g))))
+    for b, h in sorted(picks):
+        sl = lambda t: t[b:b + 1, h:h + 1]
+        ref, add, keep, ks = helpers.oracle_forward(sl(q), sl(k), sl(v), lens=lens[b:b + 1], p_drop=p, seed=pseed, offset=off,
+                                                    bh_offset=b * H + h)
+        rdq, rdk, rdv = helpers.oracle_backward(sl(q), sl(k), sl(v), sl(d_o), add=add, keep=keep, ks=ks)
+        helpers.assert_close(sl(o), ref["o"], f"o[{b},{h}]")
+        helpers.assert_close(sl(lse), ref["lse"], f"lse[{b},{h}]", torch.float16, atol=1e-3, rtol=1e-4)
+        helpers.assert_close(sl(dq), rdq, f"dq[{b},{h}]")
+        helpers.assert_close(sl(dk), rdk, f"dk[{b},{h}]")
+        helpers.assert_close(sl(dv), rdv, f"dv[{b},{h}]")
+
+
 def test_long_sequence_head_dim_128_bf16(cuda_device):
     """The long-sequence training shape (S = 2048, D = 128, bf16, no dropout) on two heads."""
     _run(cuda_device, 1, 2, 2048, 2048, 128, torch.bfloat16, "seqlen", 0.0, seed=8)
+
+
+def test_long_sequence_many_heads_cross_work_item_boundaries(cuda_device):
+    """The long-sequence shape on 2 x 8 heads of 16 key tiles each: 256 backward work items on 148 persistent CTAs, so
+    most CTAs hand over from one item to the next (other head, other valid length) in the middle of the run.  Three
+    heads - the first, one whose items straddle the first wave, the last - are compared with the oracle."""
+    B, H, S, D, dtype = 2, 8, 2048, 128, torch.bfloat16
+    q, k, v, d_o, lens = helpers.randn_like_config(B, H, S, S, D, dtype, seed=12, device=cuda_device)
+    status = torch.zeros(4, dtype=torch.int32, device=cuda_device)
+    o, lse = api.fmha_forward(q, k, v, seqlens=lens, status=status)
+    dq, dk, dv = api.fmha_backward(d_o, q, k, v, o, lse, seqlens=lens, status=status)
+    assert capi.check_status(status) == [0, 0, 0, 0]
+    for b, h in [(0, 0), (1, 1), (1, 7)]:
+        sl = lambda t: t[b:b + 1, h:h + 1]
+        ref, add, keep, ks = helpers.oracle_forward(sl(q), sl(k), sl(v), lens=lens[b:b + 1])
+        rdq, rdk, rdv = helpers.oracle_backward(sl(q), sl(k), sl(v), sl(d_o), add=add, keep=keep, ks=ks)
+        helpers.assert_close(sl(o), ref["o"], f"o[{b},{h}]", dtype)
+        helpers.assert_close(sl(dq), rdq, f"dq[{b},{h}]", dtype)
+        helpers.assert_close(sl(dk), rdk, f"dk[{b},{h}]", dtype)
+        helpers.assert_close(sl(dv), rdv, f"dv[{b},{h}]", dtype)
+
+
+def test_backward_accepts_a_broadcast_gradient(cuda_device):
+    """A loss like (o * w).sum() with w of shape [D] makes autograd hand the operator an EXPANDED gradient (strides
+    0,0,0,1): the operator must copy it to a dense tensor, not reject it."""
+    import mha_manual  # noqa: F401
+    B, H, S, D = 2, 2, 128, 64
+    q, k, v, _, lens = helpers.randn_like_config(B, H, S, S, D, torch.float16, seed=14, device=cuda_device)
+    w = torch.linspace(-1, 1, D, device=cuda_device, dtype=torch.float16)
+    qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
+    out = torch.ops.mha_manual.fmha(qg, kg, vg, None, lens)
+    (out * w).sum().backward()
+    d_o = w.expand(B, H, S, D).contiguous()
+    ref, add, keep, ks = helpers.oracle_forward(q, k, v, lens=lens)
+    rdq, rdk, rdv = helpers.oracle_backward(q, k, v, d_o, add=add, keep=keep, ks=ks)
+    helpers.assert_close(qg.grad, rdq, "dq")
+    helpers.assert_close(kg.grad, rdk, "dk")
+    helpers.assert_close(vg.grad, rdv, "dv")

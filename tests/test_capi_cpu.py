@@ -131,3 +131,26 @@ def test_host_mask_op_matches_oracle():
     m = torch.ops.mha_manual.philox_dropout_mask(2, 3, 9, 33, 0.2, 77, 4, 1, False)
     ref = philox.dropout_keep_mask(77, 4, 1, 6, 9, 33, 0.2).reshape(2, 3, 9, 33)
     assert (m.numpy() == ref).all()
+
+
+def test_ctypes_layer_rejects_layouts_the_abi_cannot_describe():
+    """The C ABI carries no stride for the head dimension and takes lse / masks as dense arrays: the ctypes helpers
+    must raise rather than let the kernels read the wrong elements."""
+    import torch
+    x = torch.zeros(2, 2, 16, 64, dtype=torch.float16)
+    capi._t4(x)                                  # dense: fine
+    capi._t4(x[:, :, ::2])                       # strided rows: fine, the ABI has a row stride
+    with pytest.raises(ValueError):
+        capi._t4(x.transpose(-1, -2))            # head dimension not contiguous
+    with pytest.raises(ValueError):
+        capi._t4(x[..., ::2])                    # sliced inside the head dimension
+    with pytest.raises(ValueError):
+        capi._t4_packed(torch.zeros(8, 2, 64, dtype=torch.float16)[..., ::2])
+    lse = torch.zeros(2, 2, 16)
+    capi._lse_ok(lse, 64)
+    with pytest.raises(ValueError):
+        capi._lse_ok(lse.double(), 64)
+    with pytest.raises(ValueError):
+        capi._lse_ok(torch.zeros(2, 2, 32)[..., ::2], 64)
+    with pytest.raises(ValueError):
+        capi._dense_ok(torch.zeros(4, 8).t(), "mask")

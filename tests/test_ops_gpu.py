@@ -47,8 +47,12 @@ def test_reference_train_check(ops, cuda_device):
     assert torch.allclose(ctx_fused, ctx, atol=1e-2)            # test_train_mha.py:36
     assert torch.allclose(saved[0], ctx, atol=1e-2)             # test_train_mha.py:41
     r = composite.attention_fp32(q, k, v, add_mask=pad.float(), keep=dm.float(), keep_scale=2.0, scale=1 / 8)
-    helpers.assert_close(ctx_fused, r["o"], "ctx", atol=2e-3)
-    helpers.assert_close(saved[0], r["o"], "saved ctx", atol=4e-3)  # P is rounded to fp16 after normalising here
+    # These two operators round the NORMALISED, doubled probabilities (values up to 2) to 16 bits before the second
+    # GEMM, exactly as fmha/fmha_manual.cpp:478-482 and :891-897 do, so their context carries that rounding: the
+    # yardstick is the reference's own 16-bit eager composite (`ctx` above), whose error against the fp32
+    # composite the fused result may not exceed by more than a factor of two (+ the 1e-3 bar).
+    helpers.assert_no_worse_than_eager(ctx_fused, r["o"], ctx, "ctx")
+    helpers.assert_no_worse_than_eager(saved[0], r["o"], ctx, "saved ctx")
     helpers.assert_close(saved[1], r["softmax"], "softmax")
     helpers.assert_close(saved[2], r["dropout_out"], "dropout_out")
     ops.check_status()
@@ -83,10 +87,11 @@ def test_legacy_ops_accept_other_shapes(ops, cuda_device):
         helpers.assert_close(ops.fmha_nvfuser(q, k, v, amask), ref["o"], f"ctx {bh,sq,sk,d}", dt)
         r2 = composite.attention_fp32(q, k, v, add_mask=pad.float(), keep=dm.float(), keep_scale=2.0)
         out = ops.fmha_train_saveim_nvfuser(q, k, v, pad, dm)
-        helpers.assert_close(out[0], r2["o"], "saved ctx", dt, atol=6e-3)
+        eager_ctx = composite.reference_mha_train(q, k, v, pad, dm, scale=1.0 / d ** 0.5)[2]   # 16-bit eager composite
+        helpers.assert_no_worse_than_eager(out[0], r2["o"], eager_ctx, "saved ctx")
         helpers.assert_close(out[1], r2["softmax"], "softmax", dt)
         helpers.assert_close(out[2], r2["dropout_out"], "dropout", dt)
-        helpers.assert_close(ops.fmha_train_nvfuser(q, k, v, pad, dm), r2["o"], "train ctx", dt, atol=3e-3)
+        helpers.assert_no_worse_than_eager(ops.fmha_train_nvfuser(q, k, v, pad, dm), r2["o"], eager_ctx, "train ctx")
 
 
 def test_autograd_operator(ops, cuda_device):
@@ -201,3 +206,37 @@ def test_operator_errors(ops, cuda_device):
     y = torch.zeros(2, 128, 96, dtype=torch.half, device=cuda_device)
     with pytest.raises(RuntimeError):
         ops.fmha_nvfuser(y, y, y, torch.zeros(2, 128, 128, dtype=torch.half, device=cuda_device))  # head dim 96
+
+
+def test_operator_under_inference_mode(ops, cuda_device):
+    """torch.inference_mode() removes the autograd keys: the differentiable operators must still run (forward only)."""
+    B, H, S, D = 2, 2, 256, 64
+    q, k, v, _, lens = helpers.randn_like_config(B, H, S, S, D, torch.float16, seed=16, device=cuda_device)
+    with torch.inference_mode():
+        o = ops.fmha(q, k, v, None, lens)
+        qkv = torch.stack([q, k, v], 2).permute(0, 3, 2, 1, 4).contiguous()   # [B,S,3,H,D]
+        o2 = ops.fmha_qkvpacked(qkv, None, lens)
+    ref, *_ = helpers.oracle_forward(q, k, v, lens=lens)
+    helpers.assert_close(o, ref["o"], "o")
+    helpers.assert_close(o2.permute(0, 2, 1, 3), ref["o"], "o (fused projection layout)")
+
+
+def test_torch_compile_fullgraph(ops, cuda_device):
+    """A function calling torch.ops.mha_manual.fmha compiles as ONE graph (no graph break at the operator) and its
+    forward and backward results equal the eager call's."""
+    B, H, S, D = 2, 2, 256, 64
+    q, k, v, d_o, lens = helpers.randn_like_config(B, H, S, S, D, torch.float16, seed=17, device=cuda_device)
+
+    def f(q, k, v, lens):
+        return ops.fmha(q * 1.0, k, v, None, lens, 0.1, 7, 2, None) * 2.0
+
+    cf = torch.compile(f, fullgraph=True, backend="aot_eager")   # the tracing and autograd partitioning are what is under test
+    outs = []
+    for fn in (f, cf):
+        qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
+        o = fn(qg, kg, vg, lens)
+        o.backward(d_o)
+        outs.append((o.detach(), qg.grad, kg.grad, vg.grad))
+    assert torch.equal(outs[0][0], outs[1][0])
+    assert torch.equal(outs[0][2], outs[1][2]) and torch.equal(outs[0][3], outs[1][3])     # dK, dV: fixed summation order
+    assert (outs[0][1].float() - outs[1][1].float()).abs().max().item() <= 2e-3             # dQ: atomics

@@ -99,3 +99,28 @@ def test_packed_fused_projection_operators_infer_shapes(ops):
     out = ops.fmha_varlen_qkvpacked(qg, cu, 384)
     (g,) = torch.autograd.grad(out, (qg,), torch.empty_like(out))
     assert g.shape == qg.shape
+
+
+def test_differentiable_operators_run_below_the_autograd_keys(ops):
+    """torch.inference_mode() excludes the autograd keys; the four differentiable operators then reach kernels of their
+    own (forward only) instead of failing with "could not run ... with arguments from the 'Meta' backend"."""
+    q, k, v = meta(2, 3, 64, 64), meta(2, 3, 96, 64), meta(2, 3, 96, 64)
+    cu = torch.empty(5, dtype=torch.int32, device="meta")
+    with torch.inference_mode():
+        assert ops.fmha(q, k, v).shape == (2, 3, 64, 64)
+        assert ops.fmha_qkvpacked(meta(2, 96, 3, 4, 64)).shape == (2, 96, 4, 64)
+        assert ops.fmha_varlen(meta(100, 4, 64), meta(100, 4, 64), meta(100, 4, 64), cu, 64).shape == (100, 4, 64)
+        assert ops.fmha_varlen_qkvpacked(meta(100, 3, 4, 64), cu, 64).shape == (100, 4, 64)
+
+
+def test_torch_compile_traces_the_operator_as_one_graph(ops):
+    """fullgraph=True: no graph break at the operator, and the compiled backward yields the three gradients."""
+    def f(q, k, v):
+        return ops.fmha(q * 1.0, k, v, None, None, 0.1, 7, 2, None) * 2.0
+
+    cf = torch.compile(f, fullgraph=True, backend="aot_eager")
+    q, k, v = meta(2, 3, 64, 64).requires_grad_(), meta(2, 3, 96, 64).requires_grad_(), meta(2, 3, 96, 64).requires_grad_()
+    o = cf(q, k, v)
+    assert o.shape == q.shape and o.requires_grad
+    gq, gk, gv = torch.autograd.grad(o, (q, k, v), torch.empty_like(o))
+    assert gq.shape == q.shape and gk.shape == k.shape and gv.shape == v.shape

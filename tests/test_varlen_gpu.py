@@ -210,3 +210,35 @@ def test_packed_batch_on_the_fused_projection_layout(cuda_device):
     # the same bits as the three-tensor operator
     o2, _ = ops.fmha_varlen_fwd(q, k, v, cu, 384, p, 77, 4)
     assert torch.equal(o2, o.detach())
+
+
+def test_sequence_longer_than_max_seqlen_is_cut_not_spilled(cuda_device):
+    """A sequence longer than the stated max_seqlen is processed up to max_seqlen (queries and keys alike) and its
+    rows past that are left alone; above all, nothing of it lands in its neighbours' outputs or gradients (the dQ
+    accumulator and delta rows of the next head lie right behind max_seqlen)."""
+    import mha_manual  # noqa: F401
+    lens, max_len, H, D, dtype = [150, 300, 90], 256, 2, 64, torch.float16
+    q, k, v, d_o, cu = packed_batch(lens, H, D, dtype, seed=33, device=cuda_device)
+    # what it must equal: the same batch with the long sequence cut to its first max_seqlen rows
+    keep_rows = torch.cat([torch.arange(0, 150), torch.arange(150, 150 + 256), torch.arange(450, 540)]).to(cuda_device)
+    cut = [150, 256, 90]
+    qc, kc, vc, doc = (x[keep_rows].contiguous() for x in (q, k, v, d_o))
+    ref = per_sequence_oracle(qc, kc, vc, doc, cut, 0.0, 0, 0, max_len)
+    status = torch.zeros(4, dtype=torch.int32, device=cuda_device)
+    canary = 7.0
+    o = torch.full_like(q, canary)
+    res = capi.fwd_varlen(q, k, v, cu, max_len, status=status, out=o)
+    dq, dk, dv = capi.bwd_varlen(d_o, q, k, v, res["o"], res["lse"], cu, max_len, status=status)
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0, 0, 0]
+    helpers.assert_close(res["o"][keep_rows], ref["o"], "o", dtype)
+    assert (res["o"][406:450] == canary).all(), "rows past max_seqlen were written"
+    helpers.assert_close(dq[keep_rows], ref["dq"], "dq", dtype)
+    helpers.assert_close(dk[keep_rows], ref["dk"], "dk", dtype)
+    helpers.assert_close(dv[keep_rows], ref["dv"], "dv", dtype)
+    # the torch operators hand back zeros for the rows that are not computed
+    ops = torch.ops.mha_manual
+    o2, lse2 = ops.fmha_varlen_fwd(q, k, v, cu, max_len)
+    g = ops.fmha_varlen_bwd(d_o, q, k, v, o2, lse2, cu, max_len)
+    assert (o2[406:450] == 0).all() and all((t[406:450] == 0).all() for t in g)
+    helpers.assert_close(g[0][keep_rows], ref["dq"], "dq (operator)", dtype)

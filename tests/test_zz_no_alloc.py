@@ -35,6 +35,16 @@ def test_static_scratch_backward_matches_workspace_backward_twice(cuda_device):
         # order varies between any two launches: same tolerance as the parity tests.
         assert torch.equal(got[1], ref[1]) and torch.equal(got[2], ref[2])
         helpers.assert_close(got[0], ref[0].float(), "dq", dtype)
+        # ... and against the CPU oracle directly, at the parity tests' tolerance
+        d_o, q, k, v = args[:4]
+        oref, add, keep, ks = helpers.oracle_forward(q, k, v, lens=kw["mask"], p_drop=p_drop, seed=31, offset=seed)
+        rdq, rdk, rdv = helpers.oracle_backward(q, k, v, d_o, add=add, keep=keep, ks=ks)
+        for name, g, r in (("dq", got[0], rdq), ("dk", got[1], rdk), ("dv", got[2], rdv)):
+            if dtype == torch.bfloat16 and min(S_q, S_k) < 256:   # short bf16 sums: the 16-bit eager composite is the yardstick
+                eager = dict(zip(("o", "dq", "dk", "dv"), helpers.eager_16bit(q, k, v, d_o, add=add, keep=keep, ks=ks)))
+                helpers.assert_no_worse_than_eager(g, r, eager[name], name)
+            else:
+                helpers.assert_close(g, r, name, dtype)
 
 
 def test_static_scratch_rejects_sizes_beyond_the_array():
