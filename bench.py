@@ -400,6 +400,19 @@ def run_ours(args, rank, world, local_rank):
                     "dense_equiv_frac": dense_f / (fwd_ms * 1e-3) / 1e12 / pk["tflops"]}
 
     # ---- strong scaling: the FIXED B0 batch split over the ranks, and the same batch on one GPU ----------------
+    # At B0/N batch elements per GPU a step is tens of microseconds of device work, less than the host needs to
+    # issue its four launches (tensor maps + cudaLaunchKernelEx: ~30 us per step), so this leg replays a CUDA graph of
+    # the step (both input sets = two steps per replay); the directly launched figure is reported beside it.
+    def step_graph(p):
+        gs = torch.cuda.Stream(device=dev)
+        g = torch.cuda.CUDAGraph()
+        gs.wait_stream(stream)
+        with torch.cuda.graph(g, stream=gs):
+            for i in range(p.n):
+                p.step(i, torch.cuda.current_stream(dev).cuda_stream)
+        stream.wait_stream(gs)
+        return g
+
     strong = None
     if world > 1:
         sh = sharding.make_shard(B0, H, world, rank)
@@ -410,18 +423,25 @@ def run_ours(args, rank, world, local_rank):
             n_st = max(50, min(args.steps, 200))
             for i in range(5):
                 splan.step(i, sp)
-            ms_n = timed(lambda i: splan.step(i, sp), n_st, "strong")
+            torch.cuda.synchronize(dev)
+            g_n, g_1 = step_graph(splan), (step_graph(plan) if rank == 0 else None)
+            for _ in range(3):
+                g_n.replay()
+            ms_n_direct = timed(lambda i: splan.step(i, sp), n_st, "strong")
+            ms_n = timed(lambda i: g_n.replay(), n_st // 2, "strong") / splan.n
             sf, sbk, _, _ = splan.flops(64)
             exe_all = all_sum(sf + sbk)
             # the whole fixed batch on rank 0 alone (the other ranks wait at the barrier inside timed()): `plan` holds B0
-            ms_1 = timed(lambda i: plan.step(i, sp) if rank == 0 else None, n_st, "strong")
+            ms_1 = timed(lambda i: g_1.replay() if rank == 0 else None, n_st // 2, "strong") / plan.n
+            capi.check_status(status)
             n_q, n_kv = S // 128, S // 128
             strong = {"global_batch": B0, "batch_per_gpu": sb, "ms_per_step": ms_n, "value": exe_all / (ms_n * 1e-3) / 1e12,
                       "unit": "TFLOP/s", "ms_per_step_1gpu_same_run": ms_1, "efficiency": ms_1 / (world * ms_n),
-                      "steps": n_st,
+                      "launch": "CUDA graph replay, two steps per replay", "ms_per_step_direct_launch": ms_n_direct,
+                      "steps": (n_st // 2) * splan.n,
                       "work_per_gpu": {"bwd_items": sb * H * n_kv, "bwd_ctas": 148, "fwd_ctas": sb * H * n_q,
                                        "bwd_waves": round(sb * H * n_kv / 148.0, 2)}}
-            del splan
+            del splan, g_n, g_1
             torch.cuda.empty_cache()
 
     # ---- the other named configurations on this run's ranks ----------------------------------------------------
@@ -647,6 +667,37 @@ def run_configs(args):
         torch.cuda.empty_cache()
 
 
+def run_legacy_profile():
+    """The reference's three operators (fmha/fmha_manual.cpp:1218-1238 of shmsong/NvFuserExamples) at its hard-coded shape,
+    three calls each with their GPU times (CUDA events): what an ncu capture of the general forward kernel runs."""
+    import torch
+
+    import mha_manual  # noqa: F401
+    ops = torch.ops.mha_manual
+    torch.manual_seed(0)
+    bh, s, d = 32 * 16, 128, 64
+    q, k, v = (torch.randn(bh, s, d, dtype=torch.half, device="cuda") for _ in range(3))
+    amask = torch.empty(bh, s, s, device="cuda").random_(2).half()
+    pad = (1 - amask) * -1000
+    dm = torch.empty(bh, s, s, device="cuda").random_(2).half()
+    calls = {"fmha_nvfuser": lambda: ops.fmha_nvfuser(q, k, v, amask),
+             "fmha_train_nvfuser": lambda: ops.fmha_train_nvfuser(q, k, v, pad, dm),
+             "fmha_train_saveim_nvfuser": lambda: ops.fmha_train_saveim_nvfuser(q, k, v, pad, dm)}
+    out = {name: [] for name in calls}
+    for rnd in range(5):   # round-robin: launches 3, 4, 5 of the kernel are one call of each operator after a warm round
+        for name, fn in calls.items():
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            if rnd >= 2:
+                out[name].append(a.elapsed_time(b) * 1e3)
+    out = {name: {"us_per_call_incl_host": round(min(ts), 1)} for name, ts in out.items()}
+    ops.check_status()
+    print(json.dumps({"profile": "legacy", "BH": bh, "S": s, "D": d, "calls": out}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -656,8 +707,9 @@ def main():
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak",
                     help="accepted for compatibility: `value` is always the weak-scaling figure (B=32 per GPU) and the "
                          "strong split of the fixed batch is always reported as the `strong` object of the same line")
-    ap.add_argument("--profile", choices=["fwd", "bwd"], default=None,
-                    help="run three launches of one kernel path on a reduced batch and exit (for ncu)")
+    ap.add_argument("--profile", choices=["fwd", "bwd", "legacy"], default=None,
+                    help="run three launches of one kernel path on a reduced batch and exit (for ncu); `legacy`: the three "
+                         "reference operators at the reference's own shape (B*H=512, S=128, D=64)")
     ap.add_argument("--profile-batch", type=int, default=16)
     ap.add_argument("--no-other-configs", action="store_true", help="skip the `other_configs` legs")
     ap.add_argument("--configs", action="store_true",
@@ -674,6 +726,8 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if world != args.gpus and world == 1 and args.gpus > 1:
         raise SystemExit("bench.py: --gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+    if args.profile == "legacy":
+        return run_legacy_profile()
     if args.impl == "reference":
         run_reference(args, rank)
     else:

@@ -1,0 +1,52 @@
+"""The reference's documented build, `python setup.py install` (shmsong/NvFuserExamples README.md:6, setup.py:7-18),
+exercised on this repository's setup.py: `build_ext` compiles the operator layer and every kernel into ONE extension
+module (a different link layout from the in-tree build, which links libfmha_sm100.so), and the result must import and
+register the reference's three operators.  Runs without a GPU (nvcc cross-compiles).
+
+The build takes minutes, so its output is kept under build/setup_check/<hash of the sources> and reused while the
+sources are unchanged."""
+import hashlib
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _source_hash() -> str:
+    h = hashlib.sha256()
+    files = sorted((ROOT / "nvfuserexamples_b200" / "csrc").glob("*")) + sorted((ROOT / "include").glob("*.h")) + [ROOT / "setup.py"]
+    for f in files:
+        h.update(f.name.encode())
+        h.update(f.read_bytes())
+    return h.hexdigest()[:16]
+
+
+def test_setup_py_build_ext_yields_an_importable_mha_manual():
+    out = ROOT / "build" / "setup_check" / _source_hash()
+    lib, tmp, done = out / "lib", out / "tmp", out / "built.ok"
+    if not done.exists():
+        out.mkdir(parents=True, exist_ok=True)
+        env = dict(os.environ, MAX_JOBS=str(min(8, os.cpu_count() or 1)), TORCH_CUDA_ARCH_LIST="10.0a")
+        proc = subprocess.run([sys.executable, "setup.py", "build_ext", "--build-lib", str(lib), "--build-temp", str(tmp)],
+                              cwd=ROOT, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=3000)
+        assert proc.returncode == 0, proc.stdout[-4000:]
+        done.write_text("ok\n")
+    built = list(lib.glob("mha_manual*.so"))
+    assert len(built) == 1, f"expected one extension module under {lib}, found {built}"
+    # import it in a fresh interpreter whose path starts at the build output, so the in-tree module cannot shadow it
+    code = (
+        "import sys, torch\n"
+        f"sys.path.insert(0, {str(lib)!r})\n"
+        "import mha_manual\n"
+        f"assert mha_manual.__file__.startswith({str(lib)!r}), mha_manual.__file__\n"
+        "ops = torch.ops.mha_manual\n"
+        "for name in ('fmha_nvfuser', 'fmha_train_nvfuser', 'fmha_train_saveim_nvfuser', 'fmha_fwd', 'fmha_bwd', 'fmha'):\n"
+        "    assert hasattr(ops, name), name\n"
+        "q = torch.empty(4, 128, 64, dtype=torch.float16, device='meta'); m = torch.empty(4, 128, 128, dtype=torch.float16, device='meta')\n"
+        "assert ops.fmha_nvfuser(q, q, q, m).shape == (4, 128, 64)\n"
+        "assert [tuple(t.shape) for t in ops.fmha_train_saveim_nvfuser(q, q, q, m, m)] == [(4, 128, 64), (4, 128, 128), (4, 128, 128)]\n"
+        "print('ok')\n")
+    proc = subprocess.run([sys.executable, "-c", code], cwd=out, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
+    assert proc.returncode == 0 and proc.stdout.strip().endswith("ok"), proc.stdout[-4000:]
