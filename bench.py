@@ -441,7 +441,19 @@ def run_ours(args, rank, world, local_rank):
                       "steps": (n_st // 2) * splan.n,
                       "work_per_gpu": {"bwd_items": sb * H * n_kv, "bwd_ctas": 148, "fwd_ctas": sb * H * n_q,
                                        "bwd_waves": round(sb * H * n_kv / 148.0, 2)}}
-            del splan, g_n, g_1
+            # The optional output gather (outside the attention path): one NCCL all-gather of the sharded O over
+            # NVLink, checked against this rank's own slice and a checksum every rank must agree on.
+            o_shard = splan.plans[0]["keep"][0]
+            t0g = time.perf_counter()
+            full = sharding.gather_outputs(o_shard, sh, B0)
+            torch.cuda.synchronize(dev)
+            gather_ms = (time.perf_counter() - t0g) * 1e3
+            mine_ok = bool(torch.equal(sharding.shard_tensor(full, sh), o_shard))
+            csum = full.float().sum().item()
+            cmax, cmin = all_max(csum), -all_max(-csum)
+            strong["output_gather"] = {"backend": "nccl", "shape": list(full.shape), "own_slice_identical": mine_ok and bool(all_max(0.0 if mine_ok else 1.0) == 0.0),
+                                       "checksum_equal_on_all_ranks": cmax == cmin, "first_call_ms_incl_setup": gather_ms}
+            del splan, g_n, g_1, full
             torch.cuda.empty_cache()
 
     # ---- the other named configurations on this run's ranks ----------------------------------------------------
