@@ -23,7 +23,7 @@ CSRC = PKG / "csrc"
 LIBDIR = PKG / "lib"
 LIB = LIBDIR / "libfmha_sm100.so"
 
-KERNEL_SOURCES = ["fmha_capi.cu", "fmha_fwd_sm100.cu", "fmha_fwd_fast_sm100.cu", "fmha_bwd_sm100.cu"]
+KERNEL_SOURCES = ["fmha_capi.cu", "fmha_fwd_sm100.cu", "fmha_fwd_dense_sm100.cu", "fmha_fwd_fast_sm100.cu", "fmha_bwd_sm100.cu"]
 KERNEL_HEADERS = ["sm100_ptx.cuh", "philox.cuh", "fmha_device_utils.cuh", "fmha_kernel_args.h", "../../include/fmha_sm100.h"]
 GENCODE = ["-gencode", "arch=compute_100a,code=sm_100a"]
 

@@ -1,0 +1,467 @@
+// fmha_fwd_dense_sm100.cu — the forward kernel behind the reference's operators `fmha_nvfuser` and
+// `fmha_train_nvfuser` (shmsong/NvFuserExamples fmha/fmha_manual.cpp:1218-1229) at head dimension 64: a dense
+// [B*H, S_q, S_k] keep mask (1 = keep, converted as (1 - m) * -10000, fmha_manual.cpp:64-65) or additive mask
+// (:463), and optionally a dense 0/1 dropout mask whose factor is applied once to O (:478-480).
+//
+// These operators move 1.5 to 2 times more mask bytes than Q, K, V and O together and do little arithmetic per
+// byte: they are bound by HBM, and what the kernel has to do is keep loads in flight.  One persistent CTA per SM
+// walks its share of the (head, 128-row query tile) items; a producer warp streams the NEXT key step's K, V and
+// mask tiles (and the next item's Q) through TMA while the current step is worked on (two stages), sixteen softmax
+// warps (thread = query row x 32 key columns; the four parts of a row meet through shared memory) keep the
+// special-function and arithmetic units busy, the dropout mask is fetched by the softmax threads themselves a step
+// ahead of its use, and S and O are double-buffered in tensor memory, so the tensor core forms the next S while the
+// current one is exponentiated and an item's O is read out under the next item's first step.
+//
+// Numerics as in the general kernel (fmha_fwd_sm100.cu) and the reference's fused definition
+// (fmha_manual.cpp:60-97, 457-492): fp32 scores and row statistics, one rounding of P to 16 bits, the 0/1 dropout
+// mask applied to the rounded P, fp32 accumulation of O, one rounding of O.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <atomic>
+
+#include "../../include/fmha_sm100.h"
+#include "fmha_device_utils.cuh"
+#include "fmha_kernel_args.h"
+#include "sm100_ptx.cuh"
+
+namespace fmha {
+
+namespace {
+
+constexpr int kDnSoftmaxThreads = 512;              // 16 warps
+constexpr int kDnThreads = 64 + kDnSoftmaxThreads;  // + producer warp + MMA warp
+constexpr float kDnLog2e = 1.4426950408889634f;
+constexpr float kDnLn2 = 0.6931471805599453f;
+constexpr uint32_t kDnSleepNs = 32;
+
+enum DnWaitSite {
+  kDQFull = 141, kDQEmpty = 142, kDStFull = 143, kDStEmpty = 144, kDSFull = 145, kDPFull = 146, kDPvDone = 147,
+  kDOFull = 148, kDOFree = 149
+};
+
+struct DnSmem {
+  static constexpr int kTile = kTileM * 64 * 2;        // a Q, K, V or O tile: 16 KB
+  static constexpr int kMaskTile = kTileM * kTileN * 2; // a mask tile: 32 KB (two swizzled 64-column halves)
+  static constexpr int kOffQ = 0;                      // [2] by item parity
+  static constexpr int kOffK = kOffQ + 2 * kTile;      // [2] by key-step parity
+  static constexpr int kOffV = kOffK + 2 * kTile;
+  static constexpr int kOffM = kOffV + 2 * kTile;
+  static constexpr int kOffO = kOffM + 2 * kMaskTile;  // [2] output staging by item parity
+  static constexpr int kOffX = kOffO + 2 * kTile;      // [2 slots][4 column quarters][128 rows] floats
+  static constexpr int kOffBar = kOffX + 2 * 4 * kTileM * 4;
+  static constexpr int kNumBars = 18;
+  static constexpr int kOffMisc = kOffBar + kNumBars * 8;
+  static constexpr int kBytes = kOffMisc + 16;
+  static constexpr int kDynBytes = kBytes + 1024;
+  static_assert(kDynBytes <= 232448, "shared memory budget of one CTA exceeded");
+};
+
+// 32 consecutive 16-bit values of a dense row as 16 packed words; zeros where the row or the columns do not exist.
+__device__ __forceinline__ void load_row32_packed(const void* base, size_t elem_off, int n_valid, uint32_t (&out)[16]) {
+  const unsigned short* p = reinterpret_cast<const unsigned short*>(base) + elem_off;
+  if (n_valid >= 32 && ((reinterpret_cast<uintptr_t>(p) & 15) == 0)) {
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      const uint4 w = __ldg(reinterpret_cast<const uint4*>(p) + v);
+      out[v * 4 + 0] = w.x; out[v * 4 + 1] = w.y; out[v * 4 + 2] = w.z; out[v * 4 + 3] = w.w;
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      const uint32_t lo = (2 * k < n_valid) ? p[2 * k] : 0u;
+      const uint32_t hi = (2 * k + 1 < n_valid) ? p[2 * k + 1] : 0u;
+      out[k] = lo | (hi << 16);
+    }
+  }
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t mul2_16bit(uint32_t a, uint32_t b) {
+  if constexpr (BF16) {
+    const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&r);
+  } else {
+    const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&r);
+  }
+}
+
+}  // namespace
+
+// KEEP: the dense mask is a keep mask (1 = keep), else additive.  DROPMASK: a dense 0/1 dropout mask is applied.
+template <bool BF16, bool KEEP, bool DROPMASK>
+__global__ void __launch_bounds__(kDnThreads, 1) fmha_fwd_dense_kernel(const __grid_constant__ FwdArgs a) {
+  griddep_wait();
+  using L = DnSmem;
+  constexpr int D = 64;
+  constexpr int kTmemCols = 512;
+  constexpr uint32_t kColS = 0, kColO = 2 * kTileN;   // S0 S1 | O0 O1
+  constexpr int kFmt = BF16 ? 1 : 0;
+  constexpr uint32_t kIdescQK = make_idesc_f16(128, kTileN, kFmt, false, false);
+  constexpr uint32_t kIdescPV = make_idesc_f16(128, D, kFmt, false, true);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem + L::kOffQ;
+  uint8_t* sK = smem + L::kOffK;
+  uint8_t* sV = smem + L::kOffV;
+  uint8_t* sM = smem + L::kOffM;
+  uint8_t* sO = smem + L::kOffO;
+  float* sX = reinterpret_cast<float*>(smem + L::kOffX);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
+  uint64_t* q_full = bars + 0;     // [2] Q of an item has landed
+  uint64_t* q_empty = bars + 2;    // [2] ... and every Q K^T of the item has completed
+  uint64_t* st_full = bars + 4;    // [2] K, V and the mask tile of a key step have landed
+  uint64_t* st_empty = bars + 6;   // [2] ... K and V have been consumed by the MMAs, the mask by the softmax warps
+  uint64_t* s_full = bars + 8;     // [2] S of a key step is in tensor memory
+  uint64_t* p_full = bars + 10;    // [2] P of a key step is in tensor memory (over its S)
+  uint64_t* pv_done = bars + 12;   // [2] O += P V of a key step has completed
+  uint64_t* o_full = bars + 14;    // [2] the last P V of an item has completed
+  uint64_t* o_free = bars + 16;    // [2] ... and O has been read out
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(smem + L::kOffMisc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kOffMisc + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n_q = (a.S_q + kTileM - 1) / kTileM;
+  const int n_kv = (a.S_k + kTileN - 1) / kTileN;
+  const int num_items = n_q * a.H * a.B;   // item = (b*H + h) * n_q + q_tile; this CTA takes blockIdx.x, + gridDim.x, ...
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(q_full + i, 1);
+      mbar_init(q_empty + i, 1);
+      mbar_init(st_full + i, 1);
+      mbar_init(st_empty + i, 1 + kDnSoftmaxThreads / 32);
+      mbar_init(s_full + i, 1);
+      mbar_init(p_full + i, kDnSoftmaxThreads);
+      mbar_init(pv_done + i, 1);
+      mbar_init(o_full + i, 1);
+      mbar_init(o_free + i, kDnSoftmaxThreads);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&a.tm_q);
+    tma_prefetch_desc(&a.tm_k);
+    tma_prefetch_desc(&a.tm_v);
+    tma_prefetch_desc(&a.tm_o);
+    tma_prefetch_desc(&a.tm_mask);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_base_slot;
+  const WaitCtx wctx{abort_flag, a.status};
+
+  if (warp == 0) {
+    // ============================ TMA producer ======================================
+    if (lane == 0) {
+      int n = 0, g = 0;   // items and key steps loaded so far
+      for (int item = blockIdx.x; item < num_items && *abort_flag == 0; item += gridDim.x, ++n) {
+        const int bh = item / n_q, q0 = (item % n_q) * kTileM;
+        const int h = bh % a.H, b = bh / a.H;
+        const int qs = n & 1;
+        if (n >= 2) mbar_wait(q_empty + qs, ((n >> 1) - 1) & 1, wctx, kDQEmpty);
+        mbar_arrive_expect_tx(q_full + qs, L::kTile);
+        tma_load_4d(sQ + qs * L::kTile, &a.tm_q, q_full + qs, 0, q0, h, b);
+        for (int j = 0; j < n_kv; ++j, ++g) {
+          const int st = g & 1;
+          if (g >= 2) mbar_wait(st_empty + st, ((g >> 1) - 1) & 1, wctx, kDStEmpty);
+          mbar_arrive_expect_tx(st_full + st, 2 * L::kTile + L::kMaskTile);
+          tma_load_4d(sK + st * L::kTile, &a.tm_k, st_full + st, 0, j * kTileN, h, b);
+          tma_load_4d(sV + st * L::kTile, &a.tm_v, st_full + st, 0, j * kTileN, h, b);
+          // the mask tile of this step: rows of this query tile, key columns [j*128, +128) in two 64-column boxes
+          const int mrow = bh * a.S_q + q0;
+#pragma unroll
+          for (int c = 0; c < 2; ++c)
+            tma_load_2d(sM + st * L::kMaskTile + c * 16384, &a.tm_mask, st_full + st, j * kTileN + c * 64, mrow);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ============================ MMA issuer ========================================
+    // Convergent warp, bursts from one elected lane (see umma_ss_x4).  S of key step g+1 is issued before O += P V
+    // of step g, also across an item boundary, so the softmax warps find their next scores ready.
+    const uint32_t tS = tmem_base + kColS, tO = tmem_base + kColO;
+    auto issue_qk = [&](int g, int qs) {
+      const int st = g & 1;
+      mbar_wait(st_full + st, (g >> 1) & 1, wctx, kDStFull);
+      tc_fence_after_sync();
+      const uint64_t dq = make_smem_desc_sw128(smem_u32(sQ + qs * L::kTile), 16, 1024);
+      const uint64_t dk = make_smem_desc_sw128(smem_u32(sK + st * L::kTile), 16, 1024);
+      uint64_t aq[4], bk[4];
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        aq[kk] = dq + kmajor_step(kk, 16384);
+        bk[kk] = dk + kmajor_step(kk, 16384);
+      }
+      umma_ss_x4(tS + st * kTileN, aq, bk, kIdescQK, 0u);
+      umma_commit_elect(s_full + st);
+    };
+    const int my_items = (num_items - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+    int g = 0;
+    if (my_items > 0) {
+      mbar_wait(q_full + 0, 0, wctx, kDQFull);
+      issue_qk(0, 0);
+      if (n_kv == 1) umma_commit_elect(q_empty + 0);
+    }
+    for (int n = 0; n < my_items; ++n) {
+      const int qs = n & 1, ob = n & 1;
+      for (int j = 0; j < n_kv; ++j, ++g) {
+        const int st = g & 1;
+        // the next S: of this item's next step, or of the next item's first step
+        if (j + 1 < n_kv) {
+          issue_qk(g + 1, qs);
+          if (j + 2 == n_kv) umma_commit_elect(q_empty + qs);
+        } else if (n + 1 < my_items) {
+          mbar_wait(q_full + (qs ^ 1), ((n + 1) >> 1) & 1, wctx, kDQFull);
+          issue_qk(g + 1, qs ^ 1);
+          if (n_kv == 1) umma_commit_elect(q_empty + (qs ^ 1));
+        }
+        // O of this item overwrites the accumulator the item before last used: its epilogue must have read it
+        if (j == 0 && n >= 2) mbar_wait(o_free + ob, ((n >> 1) - 1) & 1, wctx, kDOFree);
+        mbar_wait(p_full + st, (g >> 1) & 1, wctx, kDPFull);
+        tc_fence_after_sync();
+        const uint64_t dv = make_smem_desc_sw128(smem_u32(sV + st * L::kTile), 16384, 1024);
+        uint64_t b0[4], b1[4];
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          b0[kk] = dv + mnmajor_step(kk);
+          b1[kk] = dv + mnmajor_step(4 + kk);
+        }
+        const uint32_t tP = tS + st * kTileN;
+        umma_ts_x4(tO + ob * D, tP, 8u, b0, kIdescPV, j > 0 ? 1u : 0u);
+        umma_ts_x4(tO + ob * D, tP + 32u, 8u, b1, kIdescPV, 1u);
+        umma_commit_elect(st_empty + st);
+        umma_commit_elect(pv_done + st);
+        if (j == n_kv - 1) umma_commit_elect(o_full + ob);
+      }
+    }
+  } else {
+    // ============================ softmax / epilogue: 16 warps ======================
+    // warp (quad, cq) owns rows [32*quad, +32) (its tensor-memory lane quarter) and the 32 key columns [32*cq, +32)
+    // of every 128-key step, and the 16 columns [16*cq, +16) of O.
+    const int quad = warp & 3;
+    const int cq = (warp - 2) >> 2;
+    const int row = quad * 32 + lane;
+    const int tid = threadIdx.x - 64;
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const float sl2 = a.scale_log2;
+
+    int g = 0, xcnt = 0;
+    int n = 0;
+    bool stop = false;   // agreed on by all softmax threads at the end of each item (named_bar_or)
+    for (int item = blockIdx.x; item < num_items && !stop; item += gridDim.x, ++n) {
+      const int bh = item / n_q, q0 = (item % n_q) * kTileM;
+      const int h = bh % a.H, b = bh / a.H;
+      const int ob = n & 1;
+      const int q_row = q0 + row;
+      const bool row_ok = q_row < a.S_q;
+      const size_t dense_row = (static_cast<size_t>(bh) * a.S_q + (row_ok ? q_row : 0)) * a.S_k;
+      float m_ref = -INFINITY;
+      float2 sum2 = make_float2(0.f, 0.f);
+
+      for (int j = 0; j < n_kv; ++j, ++g) {
+        const int st = g & 1;
+        const int col0 = j * kTileN + cq * 32;                 // first key column of this thread in this step
+        const int n_cols = min(32, a.S_k - col0);              // valid ones among its 32 (may be <= 0)
+        // the dropout mask of this thread's 32 scores, straight from global memory and before the waits below,
+        // so that its latency hides behind them
+        [[maybe_unused]] uint32_t dmw[DROPMASK ? 16 : 1];
+        if constexpr (DROPMASK) load_row32_packed(a.dropout_mask, dense_row + col0, row_ok ? max(0, n_cols) : 0, dmw);
+
+        mbar_wait(s_full + st, (g >> 1) & 1, wctx, kDSFull, kDnSleepNs);
+        mbar_wait(st_full + st, (g >> 1) & 1, wctx, kDStFull, kDnSleepNs);   // the mask tile (long there: S needed K)
+        tc_fence_after_sync();
+        uint32_t sv[32];
+        tmem_ld32(tmem_base + lane_addr + kColS + st * kTileN + cq * 32, sv);
+        // this row's 32 mask values: 64 bytes = four 16-byte chunks of one swizzled half tile
+        uint32_t mw[16];
+        {
+          const uint32_t tile = smem_u32(sM + st * L::kMaskTile + (cq >> 1) * 16384);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const uint4 w = lds128(tile + sw128_offset(row, (cq & 1) * 4 + q));
+            mw[q * 4 + 0] = w.x; mw[q * 4 + 1] = w.y; mw[q * 4 + 2] = w.z; mw[q * 4 + 3] = w.w;
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(st_empty + st);   // this warp has read its part of the mask tile
+        tmem_wait_ld_dep(sv);
+
+        // t = s * scale * log2e + additive mask * log2e ; -inf for columns past the end
+        float cmax = -INFINITY;
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+          float m0 = unpack_lo<BF16>(mw[k]), m1 = unpack_hi<BF16>(mw[k]);
+          float add0, add1;
+          if constexpr (KEEP) {
+            add0 = fmaf(m0, 10000.0f * kDnLog2e, -10000.0f * kDnLog2e);   // (1 - m) * -10000 * log2e
+            add1 = fmaf(m1, 10000.0f * kDnLog2e, -10000.0f * kDnLog2e);
+          } else {
+            add0 = m0 * kDnLog2e;
+            add1 = m1 * kDnLog2e;
+          }
+          float t0 = fmaf(__uint_as_float(sv[2 * k]), sl2, add0);
+          float t1 = fmaf(__uint_as_float(sv[2 * k + 1]), sl2, add1);
+          if (2 * k >= n_cols) t0 = -INFINITY;
+          if (2 * k + 1 >= n_cols) t1 = -INFINITY;
+          sv[2 * k] = __float_as_uint(t0);
+          sv[2 * k + 1] = __float_as_uint(t1);
+          cmax = fmax3(cmax, t0, t1);
+        }
+        // the row maximum over the four column quarters
+        const int xs = xcnt++ & 1;
+        sX[(xs * 4 + cq) * kTileM + row] = cmax;
+        named_bar_sync(1, kDnSoftmaxThreads);   // also: every thread holds its scores, P may overwrite S
+        const float* xr = sX + xs * 4 * kTileM + row;
+        const float tile_max = fmaxf(fmaxf(xr[0], xr[kTileM]), fmaxf(xr[2 * kTileM], xr[3 * kTileM]));
+
+        float m_new = fmaxf(m_ref, tile_max);
+        if (m_ref != -INFINITY && m_new - m_ref <= 8.0f) m_new = m_ref;   // exponentials stay below 2^8
+        const bool moved = (m_new != m_ref) && (m_ref != -INFINITY);
+        const float alpha = (m_ref == -INFINITY) ? 0.f : (moved ? fast_exp2(m_ref - m_new) : 1.0f);
+        if (j > 0 && __any_sync(0xffffffffu, moved)) {
+          // rescale this thread's 16 columns of O; O += P V of the previous step must be complete
+          mbar_wait(pv_done + ((g - 1) & 1), ((g - 1) >> 1) & 1, wctx, kDPvDone, kDnSleepNs);
+          tc_fence_after_sync();
+          uint32_t r[16];
+          tmem_ld16(tmem_base + lane_addr + kColO + ob * D + cq * 16, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int k = 0; k < 16; ++k) r[k] = __float_as_uint(__uint_as_float(r[k]) * alpha);
+          tmem_st16(tmem_base + lane_addr + kColO + ob * D + cq * 16, r);
+        }
+        sum2.x *= alpha;
+        sum2.y *= alpha;
+        m_ref = m_new;
+
+        uint32_t packed[16];
+        const float2 negm2 = make_float2(-m_ref, -m_ref);
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+          const float2 x = __fadd2_rn(make_float2(__uint_as_float(sv[2 * k]), __uint_as_float(sv[2 * k + 1])), negm2);
+          float2 p;
+          p.x = fast_exp2(x.x);
+          p.y = fast_exp2(x.y);
+          sum2 = __fadd2_rn(sum2, p);
+          packed[k] = pack2<BF16>(p.x, p.y);
+          if constexpr (DROPMASK) packed[k] = mul2_16bit<BF16>(packed[k], dmw[k]);
+        }
+        // P over S: 128 16-bit values in 64 columns; this thread's 32 values are columns [16*cq, +16)
+        tmem_st16(tmem_base + lane_addr + kColS + st * kTileN + cq * 16, packed);
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(p_full + st);
+      }
+
+      // ---- end of the item: row sum over the four quarters, logsumexp, this thread's 16 columns of O -------------
+      const int xs = xcnt++ & 1;
+      sX[(xs * 4 + cq) * kTileM + row] = sum2.x + sum2.y;
+      named_bar_sync(1, kDnSoftmaxThreads);
+      const float* xr = sX + xs * 4 * kTileM + row;
+      const float l_sum = (xr[0] + xr[kTileM]) + (xr[2 * kTileM] + xr[3 * kTileM]);
+      const float out_scale = (DROPMASK ? a.dropout_scale : 1.0f) / l_sum;
+      if (cq == 0 && a.lse != nullptr && row_ok) a.lse[static_cast<size_t>(bh) * a.S_q + q_row] = (m_ref + fast_log2(l_sum)) * kDnLn2;
+
+      mbar_wait(o_full + ob, (n >> 1) & 1, wctx, kDOFull, kDnSleepNs);
+      tc_fence_after_sync();
+      uint32_t r[16];
+      tmem_ld16(tmem_base + lane_addr + kColO + ob * D + cq * 16, r);
+      tmem_wait_ld();
+      tc_fence_before_sync();
+      mbar_arrive(o_free + ob);
+      // the staging tile of this parity was the source of the store two items ago: at most the previous item's
+      // store (other tile) may still be reading
+      if (tid == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+      named_bar_sync(2, kDnSoftmaxThreads);
+      uint8_t* stage = sO + ob * L::kTile;
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        uint4 w;
+        w.x = pack2<BF16>(__uint_as_float(r[q * 8 + 0]) * out_scale, __uint_as_float(r[q * 8 + 1]) * out_scale);
+        w.y = pack2<BF16>(__uint_as_float(r[q * 8 + 2]) * out_scale, __uint_as_float(r[q * 8 + 3]) * out_scale);
+        w.z = pack2<BF16>(__uint_as_float(r[q * 8 + 4]) * out_scale, __uint_as_float(r[q * 8 + 5]) * out_scale);
+        w.w = pack2<BF16>(__uint_as_float(r[q * 8 + 6]) * out_scale, __uint_as_float(r[q * 8 + 7]) * out_scale);
+        *reinterpret_cast<uint4*>(stage + sw128_offset(row, cq * 2 + q)) = w;
+      }
+      fence_proxy_async_smem();
+      stop = named_bar_or(2, kDnSoftmaxThreads, *abort_flag != 0);
+      if (tid == 0 && !stop) {
+        tma_store_4d(&a.tm_o, stage, 0, q0, h, b);
+        tma_store_commit();
+      }
+    }
+    if (tid == 0) tma_store_wait_read();   // the shared-memory sources must outlive the copies
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int k = 0; k < 20; ++k) __nanosleep(1000000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <bool BF16, bool KEEP, bool DROPMASK>
+static int launch_dense_impl(const FwdArgs& a, cudaStream_t stream) {
+  auto kfn = fmha_fwd_dense_kernel<BF16, KEEP, DROPMASK>;
+  static std::atomic<bool> configured[64] = {};   // per device; set after the attribute call succeeded
+  static std::atomic<int> sm_count[64] = {};
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, DnSmem::kDynBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (dev >= 0 && dev < 64) {
+      sm_count[dev] = sms;
+      configured[dev] = true;
+    }
+  } else {
+    sms = sm_count[dev];
+  }
+  const int64_t items = static_cast<int64_t>((a.S_q + kTileM - 1) / kTileM) * a.H * a.B;
+  const int grid = static_cast<int>(items < sms ? items : sms);   // one persistent CTA per SM
+  const cudaError_t e = launch_overlapped(kfn, dim3(grid), dim3(kDnThreads), DnSmem::kDynBytes, stream, a);
+  return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
+}
+
+// The dense-mask operators this kernel serves: head dimension 64, a dense keep or additive mask staged through TMA,
+// no dropout or a dense dropout mask, nothing saved.  Everything else stays with the general kernel.
+bool fwd_dense_applies(const FwdArgs& a, int D) {
+  const bool dense_mask = a.mask_kind == FMHA_MASK_DENSE_KEEP || a.mask_kind == FMHA_MASK_DENSE_ADDITIVE;
+  const bool drop_ok = a.dropout_kind == FMHA_DROPOUT_NONE || a.dropout_kind == FMHA_DROPOUT_DENSE;
+  return D == 64 && dense_mask && a.mask_tiles > 0 && drop_ok && a.save_softmax == nullptr && a.save_dropout == nullptr &&
+         a.keep_mask_out == nullptr && a.debug_scores == nullptr;
+}
+
+int launch_fwd_dense(const FwdArgs& a, int dtype, cudaStream_t stream) {
+  const bool bf = dtype == FMHA_DTYPE_BF16;
+  const bool keep = a.mask_kind == FMHA_MASK_DENSE_KEEP;
+  const bool dm = a.dropout_kind == FMHA_DROPOUT_DENSE;
+#define FMHA_DENSE_CASE(BF, KP, DM) \
+  if (bf == BF && keep == KP && dm == DM) return launch_dense_impl<BF, KP, DM>(a, stream);
+  FMHA_DENSE_CASE(false, false, false)
+  FMHA_DENSE_CASE(false, false, true)
+  FMHA_DENSE_CASE(false, true, false)
+  FMHA_DENSE_CASE(false, true, true)
+  FMHA_DENSE_CASE(true, false, false)
+  FMHA_DENSE_CASE(true, false, true)
+  FMHA_DENSE_CASE(true, true, false)
+  FMHA_DENSE_CASE(true, true, true)
+#undef FMHA_DENSE_CASE
+  return static_cast<int>(cudaErrorInvalidValue);
+}
+
+}  // namespace fmha

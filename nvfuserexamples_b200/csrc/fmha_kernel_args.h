@@ -88,6 +88,9 @@ struct BwdArgs {
 // Launchers (defined in the .cu files).  Return a cudaError_t as int.
 int launch_fwd(const FwdArgs& a, int D, int dtype, bool legacy, bool p_via_smem, cudaStream_t stream);
 int launch_fwd_fast(const FwdArgs& a, int D, int dtype, cudaStream_t stream);
+// the persistent kernel of the dense-mask operators at head dimension 64 (fmha_fwd_dense_sm100.cu)
+bool fwd_dense_applies(const FwdArgs& a, int D);
+int launch_fwd_dense(const FwdArgs& a, int dtype, cudaStream_t stream);
 int launch_bwd(const BwdArgs& a, int D, int dtype, cudaStream_t stream);
 int launch_bwd_prepare(const void* o, const fmha_tensor4& ot, const fmha_tensor4& dot, int B, int H, int S_q, int S_q_pad,
                        int D, int dtype, float* delta, float* dq_accum, int* work_counter, const int* cu_seqlens, cudaStream_t stream);

@@ -140,6 +140,23 @@ __device__ __forceinline__ void tc_fence_after_sync() {
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
+// Barrier that also ORs a predicate over its participants: every one of them gets the same answer, which a
+// flag read by each thread on its own cannot promise (used for "has any wait of this CTA been given up?",
+// where threads that disagree would leave each other alone at the next barrier).
+__device__ __forceinline__ bool named_bar_or(int id, int nthreads, bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      "setp.ne.u32 p, %3, 0;\n\t"
+      "bar.red.or.pred q, %1, %2, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t"
+      "}\n"
+      : "=r"(r)
+      : "r"(id), "r"(nthreads), "r"(static_cast<uint32_t>(pred))
+      : "memory");
+  return r != 0;
+}
 
 // ------------------------------------------------------------------------------------
 // TMA: 4-D tiled loads and stores. coordinates are (c0 innermost .. c3 outermost)

@@ -18,7 +18,7 @@ setup(
         CUDAExtension(
             name="mha_manual",
             sources=[os.path.join(csrc, f) for f in
-                     ("mha_manual_ext.cpp", "fmha_capi.cu", "fmha_fwd_sm100.cu", "fmha_fwd_fast_sm100.cu", "fmha_bwd_sm100.cu")],
+                     ("mha_manual_ext.cpp", "fmha_capi.cu", "fmha_fwd_sm100.cu", "fmha_fwd_dense_sm100.cu", "fmha_fwd_fast_sm100.cu", "fmha_bwd_sm100.cu")],
             include_dirs=[os.path.join(this_dir, "include")],
             extra_compile_args={
                 "cxx": ["-O2", "-std=c++17"],
