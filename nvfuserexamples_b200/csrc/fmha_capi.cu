@@ -210,8 +210,11 @@ int fmha_sm100_fwd(const fmha_fwd_params* p, void* stream) {
   if ((rc = make_tmap(&a.tm_o, sanitized(p->o, mB, p->H, mSq, p->D), p->dtype, mB, p->H, mSq, p->D, kTileM))) return rc;
   a.total_rows = p->total_rows;
   a.o_ptr = p->o.ptr; a.o_ss = p->o.stride_s; a.o_sh = p->o.stride_h;
+  a.o_sb = sanitized(p->o, mB, p->H, mSq, p->D).stride_b;
+  a.o_sh = sanitized(p->o, mB, p->H, mSq, p->D).stride_h;
   a.B = p->B; a.H = p->H; a.S_q = p->S_q; a.S_k = p->S_k;
   a.scale_log2 = p->scale * 1.4426950408889634f;
+  a.scale = p->scale;
   a.lse = p->lse;
   a.mask_kind = p->mask_kind;
   a.mask = p->mask;
@@ -244,6 +247,12 @@ int fmha_sm100_fwd(const fmha_fwd_params* p, void* stream) {
   if (dense_mask && (p->S_k % 8) == 0 && (reinterpret_cast<uintptr_t>(p->mask) & 15) == 0) {
     if ((rc = make_tmap_dense(&a.tm_mask, p->mask, p->dtype, static_cast<uint64_t>(p->B) * p->H * p->S_q, p->S_k))) return rc;
     a.mask_tiles = 1;
+  }
+  a.dmask_tiles = 0;
+  if (p->dropout_kind == FMHA_DROPOUT_DENSE && p->dropout_mask != nullptr && (p->S_k % 8) == 0 &&
+      (reinterpret_cast<uintptr_t>(p->dropout_mask) & 15) == 0) {
+    if ((rc = make_tmap_dense(&a.tm_dmask, p->dropout_mask, p->dtype, static_cast<uint64_t>(p->B) * p->H * p->S_q, p->S_k))) return rc;
+    a.dmask_tiles = 1;
   }
 
   const int e = launch_fwd(a, p->D, p->dtype, legacy, p_via_smem, static_cast<cudaStream_t>(stream));

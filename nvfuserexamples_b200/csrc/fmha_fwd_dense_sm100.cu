@@ -4,13 +4,17 @@
 // (:463), and optionally a dense 0/1 dropout mask whose factor is applied once to O (:478-480).
 //
 // These operators move 1.5 to 2 times more mask bytes than Q, K, V and O together and do little arithmetic per
-// byte: they are bound by HBM, and what the kernel has to do is keep loads in flight.  One persistent CTA per SM
-// walks its share of the (head, 128-row query tile) items; a producer warp streams the NEXT key step's K, V and
-// mask tiles (and the next item's Q) through TMA while the current step is worked on (two stages), sixteen softmax
-// warps (thread = query row x 32 key columns; the four parts of a row meet through shared memory) keep the
-// special-function and arithmetic units busy, the dropout mask is fetched by the softmax threads themselves a step
-// ahead of its use, and S and O are double-buffered in tensor memory, so the tensor core forms the next S while the
-// current one is exponentiated and an item's O is read out under the next item's first step.
+// byte: they are bound by HBM, and what the kernel has to do is keep loads in flight and keep the per-item chain of
+// dependent phases short.  One persistent CTA per SM walks its share of the (head, 128-row query tile) items:
+//   * a producer thread streams Q, K, V and the mask tiles through TMA, every operand in its own ring with its own
+//     barriers, so that each load goes out as soon as ITS buffer is free and runs one to two key steps ahead;
+//   * sixteen softmax warps (thread = query row x 32 key columns; the four parts of a row meet through shared
+//     memory) do the exponentials; the dense masks reach them through shared memory, never by row-wise global
+//     loads: a warp instruction that touches 32 different rows costs 32 cycles of the load/store unit, which
+//     measured as 1.3 us per item when the dropout mask and O went that way;
+//   * S and O are double-buffered in tensor memory: the tensor core forms the next S while the current one is
+//     exponentiated (also across an item boundary), and an item's O is read out after the NEXT item's softmax,
+//     when its last P V has long completed.
 //
 // Numerics as in the general kernel (fmha_fwd_sm100.cu) and the reference's fused definition
 // (fmha_manual.cpp:60-97, 457-492): fp32 scores and row statistics, one rounding of P to 16 bits, the 0/1 dropout
@@ -30,7 +34,7 @@ namespace fmha {
 namespace {
 
 constexpr int kDnSoftmaxThreads = 512;              // 16 warps
-constexpr int kDnThreads = 64 + kDnSoftmaxThreads;  // + producer warp + MMA warp
+constexpr int kDnThreads = 64 + kDnSoftmaxThreads + 32;  // + producer warp + MMA warp + store warp
 constexpr float kDnLog2e = 1.4426950408889634f;
 constexpr float kDnLn2 = 0.6931471805599453f;
 constexpr uint32_t kDnSleepNs = 32;
@@ -40,40 +44,35 @@ enum DnWaitSite {
   kDOFull = 148, kDOFree = 149
 };
 
+// Shared memory of one CTA.  With a dropout mask every key step stages two 32 KB mask tiles, and Q, V and the output
+// staging tile give up their second (third) buffer for it: their loads then start one step later, which the
+// larger step (twice the mask bytes) covers.
+template <bool DROPMASK>
 struct DnSmem {
-  static constexpr int kTile = kTileM * 64 * 2;        // a Q, K, V or O tile: 16 KB
-  static constexpr int kMaskTile = kTileM * kTileN * 2; // a mask tile: 32 KB (two swizzled 64-column halves)
-  static constexpr int kOffQ = 0;                      // [2] by item parity
-  static constexpr int kOffK = kOffQ + 2 * kTile;      // [2] by key-step parity
+  static constexpr int kTile = kTileM * 64 * 2;          // a Q, K, V or O tile: 16 KB
+  static constexpr int kMaskTile = kTileM * kTileN * 2;  // a mask tile: 32 KB (two swizzled 64-column halves)
+  static constexpr int kQSlots = DROPMASK ? 1 : 2;
+  static constexpr int kVSlots = DROPMASK ? 1 : 3;
+  static constexpr int kOSlots = DROPMASK ? 1 : 2;
+  static constexpr int kOffQ = 0;
+  static constexpr int kOffK = kOffQ + kQSlots * kTile;  // [2] by key-step parity
   static constexpr int kOffV = kOffK + 2 * kTile;
-  static constexpr int kOffM = kOffV + 2 * kTile;
-  static constexpr int kOffO = kOffM + 2 * kMaskTile;  // [2] output staging by item parity
-  static constexpr int kOffX = kOffO + 2 * kTile;      // [2 slots][4 column quarters][128 rows] floats
+  static constexpr int kOffM = kOffV + kVSlots * kTile;  // [2] by key-step parity
+  static constexpr int kOffDM = kOffM + 2 * kMaskTile;   // [2] dropout mask tiles
+  static constexpr int kOffO = kOffDM + (DROPMASK ? 2 * kMaskTile : 0);
+  static constexpr int kOffX = kOffO + kOSlots * kTile;  // [2 slots][4 column quarters][128 rows] floats
   static constexpr int kOffBar = kOffX + 2 * 4 * kTileM * 4;
-  static constexpr int kNumBars = 18;
+  static constexpr int kNumBars = 32;
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;
   static constexpr int kBytes = kOffMisc + 16;
   static constexpr int kDynBytes = kBytes + 1024;
   static_assert(kDynBytes <= 232448, "shared memory budget of one CTA exceeded");
 };
 
-// 32 consecutive 16-bit values of a dense row as 16 packed words; zeros where the row or the columns do not exist.
-__device__ __forceinline__ void load_row32_packed(const void* base, size_t elem_off, int n_valid, uint32_t (&out)[16]) {
-  const unsigned short* p = reinterpret_cast<const unsigned short*>(base) + elem_off;
-  if (n_valid >= 32 && ((reinterpret_cast<uintptr_t>(p) & 15) == 0)) {
-#pragma unroll
-    for (int v = 0; v < 4; ++v) {
-      const uint4 w = __ldg(reinterpret_cast<const uint4*>(p) + v);
-      out[v * 4 + 0] = w.x; out[v * 4 + 1] = w.y; out[v * 4 + 2] = w.z; out[v * 4 + 3] = w.w;
-    }
-  } else {
-#pragma unroll
-    for (int k = 0; k < 16; ++k) {
-      const uint32_t lo = (2 * k < n_valid) ? p[2 * k] : 0u;
-      const uint32_t hi = (2 * k + 1 < n_valid) ? p[2 * k + 1] : 0u;
-      out[k] = lo | (hi << 16);
-    }
-  }
+template <bool BF16>
+__device__ __forceinline__ float2 unpack2(uint32_t w) {
+  if constexpr (BF16) return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
+  else return __half22float2(*reinterpret_cast<const __half2*>(&w));
 }
 
 template <bool BF16>
@@ -87,14 +86,21 @@ __device__ __forceinline__ uint32_t mul2_16bit(uint32_t a, uint32_t b) {
   }
 }
 
+// The bounded wait, inlined: an out-of-line slow path would make the code a fifth smaller, but its call made the
+// compiler spill loop-carried values to local memory, and each reload sat on the per-item critical path.
+__device__ __forceinline__ bool dn_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, int where, uint32_t sleep_ns = 0) {
+  return mbar_wait(bar, parity, ctx, where, sleep_ns);
+}
+
 }  // namespace
 
 // KEEP: the dense mask is a keep mask (1 = keep), else additive.  DROPMASK: a dense 0/1 dropout mask is applied.
 template <bool BF16, bool KEEP, bool DROPMASK>
 __global__ void __launch_bounds__(kDnThreads, 1) fmha_fwd_dense_kernel(const __grid_constant__ FwdArgs a) {
   griddep_wait();
-  using L = DnSmem;
+  using L = DnSmem<DROPMASK>;
   constexpr int D = 64;
+  constexpr int QS = L::kQSlots, VS = L::kVSlots, OS = L::kOSlots;
   constexpr int kTmemCols = 512;
   constexpr uint32_t kColS = 0, kColO = 2 * kTileN;   // S0 S1 | O0 O1
   constexpr int kFmt = BF16 ? 1 : 0;
@@ -107,18 +113,25 @@ __global__ void __launch_bounds__(kDnThreads, 1) fmha_fwd_dense_kernel(const __g
   uint8_t* sK = smem + L::kOffK;
   uint8_t* sV = smem + L::kOffV;
   uint8_t* sM = smem + L::kOffM;
+  [[maybe_unused]] uint8_t* sDM = smem + L::kOffDM;
   uint8_t* sO = smem + L::kOffO;
   float* sX = reinterpret_cast<float*>(smem + L::kOffX);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
-  uint64_t* q_full = bars + 0;     // [2] Q of an item has landed
-  uint64_t* q_empty = bars + 2;    // [2] ... and every Q K^T of the item has completed
-  uint64_t* st_full = bars + 4;    // [2] K, V and the mask tile of a key step have landed
-  uint64_t* st_empty = bars + 6;   // [2] ... K and V have been consumed by the MMAs, the mask by the softmax warps
-  uint64_t* s_full = bars + 8;     // [2] S of a key step is in tensor memory
-  uint64_t* p_full = bars + 10;    // [2] P of a key step is in tensor memory (over its S)
-  uint64_t* pv_done = bars + 12;   // [2] O += P V of a key step has completed
-  uint64_t* o_full = bars + 14;    // [2] the last P V of an item has completed
-  uint64_t* o_free = bars + 16;    // [2] ... and O has been read out
+  uint64_t* q_full = bars + 0;     // [QS] Q of an item has landed
+  uint64_t* q_empty = bars + 2;    // [QS] ... and every Q K^T of the item has completed
+  uint64_t* k_full = bars + 4;     // [2] K of a key step has landed
+  uint64_t* k_empty = bars + 6;    // [2] ... and its Q K^T has completed
+  uint64_t* m_full = bars + 8;     // [2] the mask tile(s) of a key step have landed
+  uint64_t* m_empty = bars + 10;   // [2] ... and the 16 softmax warps have taken them into registers
+  uint64_t* s_full = bars + 12;    // [2] S of a key step is in tensor memory
+  uint64_t* p_full = bars + 14;    // [2] P of a key step is in tensor memory (over its S)
+  uint64_t* pv_done = bars + 16;   // [2] O += P V of a key step has completed
+  uint64_t* o_full = bars + 18;    // [2] the last P V of an item has completed
+  uint64_t* o_free = bars + 20;    // [2] ... and O has been read out
+  uint64_t* v_full = bars + 22;    // [VS] V of a key step has landed
+  uint64_t* v_empty = bars + 25;   // [VS] ... and its P V has completed
+  uint64_t* o_staged = bars + 28;  // [OS] the rounded O tile of an item is in its staging tile
+  uint64_t* o_stage_free = bars + 30;  // [OS] ... and the TMA store has read it
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(smem + L::kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kOffMisc + 4);
 
@@ -127,26 +140,73 @@ __global__ void __launch_bounds__(kDnThreads, 1) fmha_fwd_dense_kernel(const __g
   const int n_q = (a.S_q + kTileM - 1) / kTileM;
   const int n_kv = (a.S_k + kTileN - 1) / kTileN;
   const int num_items = n_q * a.H * a.B;   // item = (b*H + h) * n_q + q_tile; this CTA takes blockIdx.x, + gridDim.x, ...
+  const WaitCtx wctx{abort_flag, a.status};
+
+  // Loads of one item (Q) and of one key step (K, the mask tiles, V), by the producer thread.
+  auto load_q = [&](int n, int q0, int h, int b) {
+    const int qs = n % QS;
+    if (n >= QS) dn_wait(q_empty + qs, ((n / QS) - 1) & 1, wctx, kDQEmpty);
+    mbar_arrive_expect_tx(q_full + qs, L::kTile);
+    tma_load_4d(sQ + qs * L::kTile, &a.tm_q, q_full + qs, 0, q0, h, b);
+  };
+  auto load_km = [&](int g, int j, int bh, int q0, int h, int b) {
+    const int st = g & 1;
+    if (g >= 2) dn_wait(k_empty + st, ((g >> 1) - 1) & 1, wctx, kDStEmpty);
+    mbar_arrive_expect_tx(k_full + st, L::kTile);
+    tma_load_4d(sK + st * L::kTile, &a.tm_k, k_full + st, 0, j * kTileN, h, b);
+    // the mask tiles of this step: rows of this query tile, key columns [j*128, +128) in two 64-column boxes each
+    if (g >= 2) dn_wait(m_empty + st, ((g >> 1) - 1) & 1, wctx, kDStEmpty);
+    mbar_arrive_expect_tx(m_full + st, (DROPMASK ? 2 : 1) * L::kMaskTile);
+    const int mrow = bh * a.S_q + q0;
+#pragma unroll
+    for (int c = 0; c < 2; ++c)
+      tma_load_2d(sM + st * L::kMaskTile + c * 16384, &a.tm_mask, m_full + st, j * kTileN + c * 64, mrow);
+    if constexpr (DROPMASK) {
+#pragma unroll
+      for (int c = 0; c < 2; ++c)
+        tma_load_2d(sDM + st * L::kMaskTile + c * 16384, &a.tm_dmask, m_full + st, j * kTileN + c * 64, mrow);
+    }
+  };
+  auto load_v = [&](int g, int j, int h, int b) {
+    const int vs = g % VS;
+    if (g >= VS) dn_wait(v_empty + vs, ((g / VS) - 1) & 1, wctx, kDStEmpty);
+    mbar_arrive_expect_tx(v_full + vs, L::kTile);
+    tma_load_4d(sV + vs * L::kTile, &a.tm_v, v_full + vs, 0, j * kTileN, h, b);
+  };
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int i = 0; i < 2; ++i) {
       mbar_init(q_full + i, 1);
       mbar_init(q_empty + i, 1);
-      mbar_init(st_full + i, 1);
-      mbar_init(st_empty + i, 1 + kDnSoftmaxThreads / 32);
+      mbar_init(k_full + i, 1);
+      mbar_init(k_empty + i, 1);
+      mbar_init(m_full + i, 1);
+      mbar_init(m_empty + i, kDnSoftmaxThreads / 32);
       mbar_init(s_full + i, 1);
       mbar_init(p_full + i, kDnSoftmaxThreads);
       mbar_init(pv_done + i, 1);
       mbar_init(o_full + i, 1);
       mbar_init(o_free + i, kDnSoftmaxThreads);
     }
+    for (int i = 0; i < 3; ++i) {
+      mbar_init(v_full + i, 1);
+      mbar_init(v_empty + i, 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(o_staged + i, kDnSoftmaxThreads / 32);
+      mbar_init(o_stage_free + i, 1);
+    }
     mbar_fence_init();
-    tma_prefetch_desc(&a.tm_q);
-    tma_prefetch_desc(&a.tm_k);
-    tma_prefetch_desc(&a.tm_v);
+    // The first item's loads go out at once: the rest of the set-up (tensor-memory allocation, the CTA-wide
+    // synchronisation) runs under their latency.
+    if (static_cast<int>(blockIdx.x) < num_items) {
+      const int bh = blockIdx.x / n_q, q0 = (blockIdx.x % n_q) * kTileM;
+      load_q(0, q0, bh % a.H, bh / a.H);
+      load_km(0, 0, bh, q0, bh % a.H, bh / a.H);
+      load_v(0, 0, bh % a.H, bh / a.H);
+    }
     tma_prefetch_desc(&a.tm_o);
-    tma_prefetch_desc(&a.tm_mask);
   }
   if (warp == 1) {
     tmem_alloc(tmem_base_slot, kTmemCols);
@@ -156,32 +216,27 @@ __global__ void __launch_bounds__(kDnThreads, 1) fmha_fwd_dense_kernel(const __g
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_slot;
-  const WaitCtx wctx{abort_flag, a.status};
 
   if (warp == 0) {
     // ============================ TMA producer ======================================
     if (lane == 0) {
+      // Order: K and the masks of step g, then V of step g-1.  V's buffer is the last of a step to come free (after
+      // P V), and waiting for it first would hold back the K and mask loads of the next step, which can go earlier.
       int n = 0, g = 0;   // items and key steps loaded so far
+      int pj = 0, ph = 0, pb = 0;   // the step whose V is still to be loaded
       for (int item = blockIdx.x; item < num_items && *abort_flag == 0; item += gridDim.x, ++n) {
         const int bh = item / n_q, q0 = (item % n_q) * kTileM;
         const int h = bh % a.H, b = bh / a.H;
-        const int qs = n & 1;
-        if (n >= 2) mbar_wait(q_empty + qs, ((n >> 1) - 1) & 1, wctx, kDQEmpty);
-        mbar_arrive_expect_tx(q_full + qs, L::kTile);
-        tma_load_4d(sQ + qs * L::kTile, &a.tm_q, q_full + qs, 0, q0, h, b);
+        if (n > 0) load_q(n, q0, h, b);
         for (int j = 0; j < n_kv; ++j, ++g) {
-          const int st = g & 1;
-          if (g >= 2) mbar_wait(st_empty + st, ((g >> 1) - 1) & 1, wctx, kDStEmpty);
-          mbar_arrive_expect_tx(st_full + st, 2 * L::kTile + L::kMaskTile);
-          tma_load_4d(sK + st * L::kTile, &a.tm_k, st_full + st, 0, j * kTileN, h, b);
-          tma_load_4d(sV + st * L::kTile, &a.tm_v, st_full + st, 0, j * kTileN, h, b);
-          // the mask tile of this step: rows of this query tile, key columns [j*128, +128) in two 64-column boxes
-          const int mrow = bh * a.S_q + q0;
-#pragma unroll
-          for (int c = 0; c < 2; ++c)
-            tma_load_2d(sM + st * L::kMaskTile + c * 16384, &a.tm_mask, st_full + st, j * kTileN + c * 64, mrow);
+          if (g > 0) {   // step 0 went out before the set-up
+            load_km(g, j, bh, q0, h, b);
+            if (g > 1) load_v(g - 1, pj, ph, pb);
+          }
+          pj = j; ph = h; pb = b;
         }
       }
+      if (g > 1 && *abort_flag == 0) load_v(g - 1, pj, ph, pb);
     }
   } else if (warp == 1) {
     // ============================ MMA issuer ========================================
@@ -190,7 +245,7 @@ __global__ void __launch_bounds__(kDnThreads, 1) fmha_fwd_dense_kernel(const __g
     const uint32_t tS = tmem_base + kColS, tO = tmem_base + kColO;
     auto issue_qk = [&](int g, int qs) {
       const int st = g & 1;
-      mbar_wait(st_full + st, (g >> 1) & 1, wctx, kDStFull);
+      dn_wait(k_full + st, (g >> 1) & 1, wctx, kDStFull);
       tc_fence_after_sync();
       const uint64_t dq = make_smem_desc_sw128(smem_u32(sQ + qs * L::kTile), 16, 1024);
       const uint64_t dk = make_smem_desc_sw128(smem_u32(sK + st * L::kTile), 16, 1024);
@@ -202,32 +257,35 @@ __global__ void __launch_bounds__(kDnThreads, 1) fmha_fwd_dense_kernel(const __g
       }
       umma_ss_x4(tS + st * kTileN, aq, bk, kIdescQK, 0u);
       umma_commit_elect(s_full + st);
+      umma_commit_elect(k_empty + st);
     };
     const int my_items = (num_items - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
     int g = 0;
     if (my_items > 0) {
-      mbar_wait(q_full + 0, 0, wctx, kDQFull);
+      dn_wait(q_full + 0, 0, wctx, kDQFull);
       issue_qk(0, 0);
       if (n_kv == 1) umma_commit_elect(q_empty + 0);
     }
     for (int n = 0; n < my_items; ++n) {
-      const int qs = n & 1, ob = n & 1;
+      const int qs = n % QS, ob = n & 1;
       for (int j = 0; j < n_kv; ++j, ++g) {
-        const int st = g & 1;
+        const int st = g & 1, vs = g % VS;
         // the next S: of this item's next step, or of the next item's first step
         if (j + 1 < n_kv) {
           issue_qk(g + 1, qs);
           if (j + 2 == n_kv) umma_commit_elect(q_empty + qs);
         } else if (n + 1 < my_items) {
-          mbar_wait(q_full + (qs ^ 1), ((n + 1) >> 1) & 1, wctx, kDQFull);
-          issue_qk(g + 1, qs ^ 1);
-          if (n_kv == 1) umma_commit_elect(q_empty + (qs ^ 1));
+          const int qn = (n + 1) % QS;
+          dn_wait(q_full + qn, ((n + 1) / QS) & 1, wctx, kDQFull);
+          issue_qk(g + 1, qn);
+          if (n_kv == 1) umma_commit_elect(q_empty + qn);
         }
         // O of this item overwrites the accumulator the item before last used: its epilogue must have read it
-        if (j == 0 && n >= 2) mbar_wait(o_free + ob, ((n >> 1) - 1) & 1, wctx, kDOFree);
-        mbar_wait(p_full + st, (g >> 1) & 1, wctx, kDPFull);
+        if (j == 0 && n >= 2) dn_wait(o_free + ob, ((n >> 1) - 1) & 1, wctx, kDOFree);
+        dn_wait(v_full + vs, (g / VS) & 1, wctx, kDStFull);
+        dn_wait(p_full + st, (g >> 1) & 1, wctx, kDPFull);
         tc_fence_after_sync();
-        const uint64_t dv = make_smem_desc_sw128(smem_u32(sV + st * L::kTile), 16384, 1024);
+        const uint64_t dv = make_smem_desc_sw128(smem_u32(sV + vs * L::kTile), 16384, 1024);
         uint64_t b0[4], b1[4];
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
@@ -237,10 +295,27 @@ __global__ void __launch_bounds__(kDnThreads, 1) fmha_fwd_dense_kernel(const __g
         const uint32_t tP = tS + st * kTileN;
         umma_ts_x4(tO + ob * D, tP, 8u, b0, kIdescPV, j > 0 ? 1u : 0u);
         umma_ts_x4(tO + ob * D, tP + 32u, 8u, b1, kIdescPV, 1u);
-        umma_commit_elect(st_empty + st);
+        umma_commit_elect(v_empty + vs);
         umma_commit_elect(pv_done + st);
         if (j == n_kv - 1) umma_commit_elect(o_full + ob);
       }
+    }
+  } else if (warp == 18) {
+    // ============================ store warp =========================================
+    // One thread: as each item's O tile is staged, hands it to TMA and releases the staging tile once it is read.
+    if (lane == 0) {
+      const int my_items = (num_items - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+      int item = blockIdx.x;
+      for (int n = 0; n < my_items && *abort_flag == 0; ++n, item += gridDim.x) {
+        const int os = n % OS;
+        if (!dn_wait(o_staged + os, (n / OS) & 1, wctx, kDOFull, kDnSleepNs)) break;
+        const int bh = item / n_q, q0 = (item % n_q) * kTileM;
+        tma_store_4d(&a.tm_o, sO + os * L::kTile, 0, q0, bh % a.H, bh / a.H);
+        tma_store_commit();
+        tma_store_wait_read();
+        mbar_arrive(o_stage_free + os);
+      }
+      tma_store_wait_read();   // the shared-memory sources must outlive the copies
     }
   } else {
     // ============================ softmax / epilogue: 16 warps ======================
@@ -249,138 +324,27 @@ __global__ void __launch_bounds__(kDnThreads, 1) fmha_fwd_dense_kernel(const __g
     const int quad = warp & 3;
     const int cq = (warp - 2) >> 2;
     const int row = quad * 32 + lane;
-    const int tid = threadIdx.x - 64;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    const float sl2 = a.scale_log2;
+    const float2 sc2 = make_float2(a.scale, a.scale);
 
-    int g = 0, xcnt = 0;
+    int g = 0;
     int n = 0;
-    bool stop = false;   // agreed on by all softmax threads at the end of each item (named_bar_or)
-    for (int item = blockIdx.x; item < num_items && !stop; item += gridDim.x, ++n) {
-      const int bh = item / n_q, q0 = (item % n_q) * kTileM;
-      const int h = bh % a.H, b = bh / a.H;
-      const int ob = n & 1;
-      const int q_row = q0 + row;
-      const bool row_ok = q_row < a.S_q;
-      const size_t dense_row = (static_cast<size_t>(bh) * a.S_q + (row_ok ? q_row : 0)) * a.S_k;
-      float m_ref = -INFINITY;
-      float2 sum2 = make_float2(0.f, 0.f);
-
-      for (int j = 0; j < n_kv; ++j, ++g) {
-        const int st = g & 1;
-        const int col0 = j * kTileN + cq * 32;                 // first key column of this thread in this step
-        const int n_cols = min(32, a.S_k - col0);              // valid ones among its 32 (may be <= 0)
-        // the dropout mask of this thread's 32 scores, straight from global memory and before the waits below,
-        // so that its latency hides behind them
-        [[maybe_unused]] uint32_t dmw[DROPMASK ? 16 : 1];
-        if constexpr (DROPMASK) load_row32_packed(a.dropout_mask, dense_row + col0, row_ok ? max(0, n_cols) : 0, dmw);
-
-        mbar_wait(s_full + st, (g >> 1) & 1, wctx, kDSFull, kDnSleepNs);
-        mbar_wait(st_full + st, (g >> 1) & 1, wctx, kDStFull, kDnSleepNs);   // the mask tile (long there: S needed K)
-        tc_fence_after_sync();
-        uint32_t sv[32];
-        tmem_ld32(tmem_base + lane_addr + kColS + st * kTileN + cq * 32, sv);
-        // this row's 32 mask values: 64 bytes = four 16-byte chunks of one swizzled half tile
-        uint32_t mw[16];
-        {
-          const uint32_t tile = smem_u32(sM + st * L::kMaskTile + (cq >> 1) * 16384);
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const uint4 w = lds128(tile + sw128_offset(row, (cq & 1) * 4 + q));
-            mw[q * 4 + 0] = w.x; mw[q * 4 + 1] = w.y; mw[q * 4 + 2] = w.z; mw[q * 4 + 3] = w.w;
-          }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(st_empty + st);   // this warp has read its part of the mask tile
-        tmem_wait_ld_dep(sv);
-
-        // t = s * scale * log2e + additive mask * log2e ; -inf for columns past the end
-        float cmax = -INFINITY;
-#pragma unroll
-        for (int k = 0; k < 16; ++k) {
-          float m0 = unpack_lo<BF16>(mw[k]), m1 = unpack_hi<BF16>(mw[k]);
-          float add0, add1;
-          if constexpr (KEEP) {
-            add0 = fmaf(m0, 10000.0f * kDnLog2e, -10000.0f * kDnLog2e);   // (1 - m) * -10000 * log2e
-            add1 = fmaf(m1, 10000.0f * kDnLog2e, -10000.0f * kDnLog2e);
-          } else {
-            add0 = m0 * kDnLog2e;
-            add1 = m1 * kDnLog2e;
-          }
-          float t0 = fmaf(__uint_as_float(sv[2 * k]), sl2, add0);
-          float t1 = fmaf(__uint_as_float(sv[2 * k + 1]), sl2, add1);
-          if (2 * k >= n_cols) t0 = -INFINITY;
-          if (2 * k + 1 >= n_cols) t1 = -INFINITY;
-          sv[2 * k] = __float_as_uint(t0);
-          sv[2 * k + 1] = __float_as_uint(t1);
-          cmax = fmax3(cmax, t0, t1);
-        }
-        // the row maximum over the four column quarters
-        const int xs = xcnt++ & 1;
-        sX[(xs * 4 + cq) * kTileM + row] = cmax;
-        named_bar_sync(1, kDnSoftmaxThreads);   // also: every thread holds its scores, P may overwrite S
-        const float* xr = sX + xs * 4 * kTileM + row;
-        const float tile_max = fmaxf(fmaxf(xr[0], xr[kTileM]), fmaxf(xr[2 * kTileM], xr[3 * kTileM]));
-
-        float m_new = fmaxf(m_ref, tile_max);
-        if (m_ref != -INFINITY && m_new - m_ref <= 8.0f) m_new = m_ref;   // exponentials stay below 2^8
-        const bool moved = (m_new != m_ref) && (m_ref != -INFINITY);
-        const float alpha = (m_ref == -INFINITY) ? 0.f : (moved ? fast_exp2(m_ref - m_new) : 1.0f);
-        if (j > 0 && __any_sync(0xffffffffu, moved)) {
-          // rescale this thread's 16 columns of O; O += P V of the previous step must be complete
-          mbar_wait(pv_done + ((g - 1) & 1), ((g - 1) >> 1) & 1, wctx, kDPvDone, kDnSleepNs);
-          tc_fence_after_sync();
-          uint32_t r[16];
-          tmem_ld16(tmem_base + lane_addr + kColO + ob * D + cq * 16, r);
-          tmem_wait_ld();
-#pragma unroll
-          for (int k = 0; k < 16; ++k) r[k] = __float_as_uint(__uint_as_float(r[k]) * alpha);
-          tmem_st16(tmem_base + lane_addr + kColO + ob * D + cq * 16, r);
-        }
-        sum2.x *= alpha;
-        sum2.y *= alpha;
-        m_ref = m_new;
-
-        uint32_t packed[16];
-        const float2 negm2 = make_float2(-m_ref, -m_ref);
-#pragma unroll
-        for (int k = 0; k < 16; ++k) {
-          const float2 x = __fadd2_rn(make_float2(__uint_as_float(sv[2 * k]), __uint_as_float(sv[2 * k + 1])), negm2);
-          float2 p;
-          p.x = fast_exp2(x.x);
-          p.y = fast_exp2(x.y);
-          sum2 = __fadd2_rn(sum2, p);
-          packed[k] = pack2<BF16>(p.x, p.y);
-          if constexpr (DROPMASK) packed[k] = mul2_16bit<BF16>(packed[k], dmw[k]);
-        }
-        // P over S: 128 16-bit values in 64 columns; this thread's 32 values are columns [16*cq, +16)
-        tmem_st16(tmem_base + lane_addr + kColS + st * kTileN + cq * 16, packed);
-        tmem_wait_st();
-        tc_fence_before_sync();
-        mbar_arrive(p_full + st);
-      }
-
-      // ---- end of the item: row sum over the four quarters, logsumexp, this thread's 16 columns of O -------------
-      const int xs = xcnt++ & 1;
-      sX[(xs * 4 + cq) * kTileM + row] = sum2.x + sum2.y;
-      named_bar_sync(1, kDnSoftmaxThreads);
-      const float* xr = sX + xs * 4 * kTileM + row;
-      const float l_sum = (xr[0] + xr[kTileM]) + (xr[2 * kTileM] + xr[3 * kTileM]);
-      const float out_scale = (DROPMASK ? a.dropout_scale : 1.0f) / l_sum;
-      if (cq == 0 && a.lse != nullptr && row_ok) a.lse[static_cast<size_t>(bh) * a.S_q + q_row] = (m_ref + fast_log2(l_sum)) * kDnLn2;
-
-      mbar_wait(o_full + ob, (n >> 1) & 1, wctx, kDOFull, kDnSleepNs);
+    bool stop = false;   // "a wait of this CTA was given up": agreed on by all softmax threads at the end of each item
+    // O of item number n_ep of this CTA (accumulator n_ep & 1): scale, round, stage in shared memory for the store
+    // warp.  No CTA-wide barrier and no TMA instruction here: issuing a TMA store behind the producer's queued loads
+    // took the issuing thread some 600 cycles, with every other softmax warp waiting for it at the next barrier.
+    auto epilogue = [&](int n_ep, float out_scale) {
+      const int ob = n_ep & 1;
+      dn_wait(o_full + ob, (n_ep >> 1) & 1, wctx, kDOFull, kDnSleepNs);
       tc_fence_after_sync();
       uint32_t r[16];
       tmem_ld16(tmem_base + lane_addr + kColO + ob * D + cq * 16, r);
       tmem_wait_ld();
       tc_fence_before_sync();
       mbar_arrive(o_free + ob);
-      // the staging tile of this parity was the source of the store two items ago: at most the previous item's
-      // store (other tile) may still be reading
-      if (tid == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-      named_bar_sync(2, kDnSoftmaxThreads);
-      uint8_t* stage = sO + ob * L::kTile;
+      const int os = n_ep % OS;
+      if (n_ep >= OS) dn_wait(o_stage_free + os, ((n_ep / OS) - 1) & 1, wctx, kDOFree, kDnSleepNs);   // long free, as a rule
+      uint8_t* stage = sO + os * L::kTile;
 #pragma unroll
       for (int q = 0; q < 2; ++q) {
         uint4 w;
@@ -391,13 +355,151 @@ __global__ void __launch_bounds__(kDnThreads, 1) fmha_fwd_dense_kernel(const __g
         *reinterpret_cast<uint4*>(stage + sw128_offset(row, cq * 2 + q)) = w;
       }
       fence_proxy_async_smem();
-      stop = named_bar_or(2, kDnSoftmaxThreads, *abort_flag != 0);
-      if (tid == 0 && !stop) {
-        tma_store_4d(&a.tm_o, stage, 0, q0, h, b);
-        tma_store_commit();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(o_staged + os);   // the store warp takes it from here
+    };
+    // (head, query tile) of the current item, advanced without divisions: the item number grows by gridDim.x
+    int bh = blockIdx.x / n_q, qt = blockIdx.x % n_q;
+    const int d_bh = gridDim.x / n_q, d_qt = gridDim.x % n_q;
+    float pend_scale = 0.f;
+    for (int item = blockIdx.x;; item += gridDim.x, ++n) {
+      const bool have = item < num_items && !stop;   // the same for all softmax threads
+      float out_scale_item = 0.f;
+      const int q0 = qt * kTileM;
+      if (have) {
+        const int ob = n & 1;
+        const int q_row = q0 + row;
+        const bool row_ok = q_row < a.S_q;
+        float m_ref = -INFINITY;
+        float2 sum2 = make_float2(0.f, 0.f);
+
+        for (int j = 0; j < n_kv; ++j, ++g) {
+          const int st = g & 1;
+          const int col0 = j * kTileN + cq * 32;                 // first key column of this thread in this step
+          const int n_cols = min(32, a.S_k - col0);              // valid ones among its 32 (may be <= 0)
+
+          // S and the mask tile(s): both polls are issued before either answer is looked at, their latencies overlap.
+          // (Nothing but straight-line code may stand between a tensor-memory load and its wait: the destination
+          // registers are written until then, and a wait loop in between lets the compiler move them.)
+          const bool s_ok = mbar_try_wait(s_full + st, (g >> 1) & 1);
+          const bool m_ok = mbar_try_wait(m_full + st, (g >> 1) & 1);
+          if (!s_ok) dn_wait(s_full + st, (g >> 1) & 1, wctx, kDSFull, kDnSleepNs);
+          if (!m_ok) dn_wait(m_full + st, (g >> 1) & 1, wctx, kDStFull, kDnSleepNs);
+          tc_fence_after_sync();
+          uint32_t sv[32];
+          tmem_ld32(tmem_base + lane_addr + kColS + st * kTileN + cq * 32, sv);
+          tmem_wait_ld_dep(sv);
+          // this row's 32 mask values: 64 bytes = four 16-byte chunks of one swizzled half tile; and
+          // t = s * scale + additive mask (natural-log domain, two scores per packed instruction)
+          {
+            const uint32_t tile = smem_u32(sM + st * L::kMaskTile + (cq >> 1) * 16384);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint4 w = lds128(tile + sw128_offset(row, (cq & 1) * 4 + q));
+              const uint32_t mw[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int k = q * 4 + e;
+                float2 add = unpack2<BF16>(mw[e]);
+                if constexpr (KEEP) {   // (1 - m) * -10000, the constants as immediates
+                  add.x = fmaf(add.x, 10000.0f, -10000.0f);
+                  add.y = fmaf(add.y, 10000.0f, -10000.0f);
+                }
+                const float2 t = __ffma2_rn(make_float2(__uint_as_float(sv[2 * k]), __uint_as_float(sv[2 * k + 1])), sc2, add);
+                sv[2 * k] = __float_as_uint(t.x);
+                sv[2 * k + 1] = __float_as_uint(t.y);
+              }
+            }
+          }
+          if constexpr (!DROPMASK) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(m_empty + st);   // this warp has read its part of the mask tile
+          }
+          if (n_cols < 32) {   // the same for the whole warp
+#pragma unroll
+            for (int k = 0; k < 32; ++k)
+              if (k >= n_cols) sv[k] = __float_as_uint(-INFINITY);
+          }
+          float cmax = -INFINITY;
+#pragma unroll
+          for (int k = 0; k < 16; ++k) cmax = fmax3(cmax, __uint_as_float(sv[2 * k]), __uint_as_float(sv[2 * k + 1]));
+          // the row maximum over the four column quarters
+          const int xs = (g + n) & 1;   // exchanges so far: one per key step and one per finished item
+          sX[(xs * 4 + cq) * kTileM + row] = cmax;
+          named_bar_sync(1, kDnSoftmaxThreads);   // also: every thread holds its scores, P may overwrite S
+          const float* xr = sX + xs * 4 * kTileM + row;
+          const float tile_max = fmaxf(fmaxf(xr[0], xr[kTileM]), fmaxf(xr[2 * kTileM], xr[3 * kTileM]));
+
+          float m_new = fmaxf(m_ref, tile_max);
+          if (m_ref != -INFINITY && m_new - m_ref <= 5.5f) m_new = m_ref;   // exponentials stay below e^5.5 < 2^8
+          const bool moved = (m_new != m_ref) && (m_ref != -INFINITY);
+          const float alpha = (m_ref == -INFINITY) ? 0.f : (moved ? fast_exp2((m_ref - m_new) * kDnLog2e) : 1.0f);
+          if (j > 0 && __any_sync(0xffffffffu, moved)) {
+            // rescale this thread's 16 columns of O; O += P V of the previous step must be complete
+            dn_wait(pv_done + ((g - 1) & 1), ((g - 1) >> 1) & 1, wctx, kDPvDone, kDnSleepNs);
+            tc_fence_after_sync();
+            uint32_t r[16];
+            tmem_ld16(tmem_base + lane_addr + kColO + ob * D + cq * 16, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int k = 0; k < 16; ++k) r[k] = __float_as_uint(__uint_as_float(r[k]) * alpha);
+            tmem_st16(tmem_base + lane_addr + kColO + ob * D + cq * 16, r);
+          }
+          sum2.x *= alpha;
+          sum2.y *= alpha;
+          m_ref = m_new;
+
+          // the dropout mask of this thread's 32 scores, taken from its tile only now: sixteen registers less while the
+          // scores and the padding mask are live (columns past the end of a mask row arrive as zeros, like P there)
+          [[maybe_unused]] uint32_t dmw[DROPMASK ? 16 : 1];
+          if constexpr (DROPMASK) {
+            const uint32_t dtile = smem_u32(sDM + st * L::kMaskTile + (cq >> 1) * 16384);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint4 w = lds128(dtile + sw128_offset(row, (cq & 1) * 4 + q));
+              dmw[q * 4 + 0] = w.x; dmw[q * 4 + 1] = w.y; dmw[q * 4 + 2] = w.z; dmw[q * 4 + 3] = w.w;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(m_empty + st);   // this warp has read its part of both mask tiles
+          }
+          uint32_t packed[16];
+          const float2 negm2 = make_float2(-m_ref * kDnLog2e, -m_ref * kDnLog2e);
+          const float2 l2e2 = make_float2(kDnLog2e, kDnLog2e);
+#pragma unroll
+          for (int k = 0; k < 16; ++k) {
+            const float2 x = __ffma2_rn(make_float2(__uint_as_float(sv[2 * k]), __uint_as_float(sv[2 * k + 1])), l2e2, negm2);
+            float2 p;
+            p.x = fast_exp2(x.x);
+            p.y = fast_exp2(x.y);
+            sum2 = __fadd2_rn(sum2, p);
+            packed[k] = pack2<BF16>(p.x, p.y);
+            if constexpr (DROPMASK) packed[k] = mul2_16bit<BF16>(packed[k], dmw[k]);
+          }
+          // P over S: 128 16-bit values in 64 columns; this thread's 32 values are columns [16*cq, +16)
+          tmem_st16(tmem_base + lane_addr + kColS + st * kTileN + cq * 16, packed);
+          tmem_wait_st();
+          tc_fence_before_sync();
+          mbar_arrive(p_full + st);
+        }
+
+        // ---- end of the item: row sum over the four quarters, logsumexp -----------------------------------------
+        const int xs = (g + n) & 1;   // exchanges so far: one per key step and one per finished item
+        sX[(xs * 4 + cq) * kTileM + row] = sum2.x + sum2.y;
+        stop = named_bar_or(1, kDnSoftmaxThreads, *abort_flag != 0);
+        const float* xr = sX + xs * 4 * kTileM + row;
+        const float l_sum = (xr[0] + xr[kTileM]) + (xr[2 * kTileM] + xr[3 * kTileM]);
+        out_scale_item = __fdividef(DROPMASK ? a.dropout_scale : 1.0f, l_sum);
+        if (cq == 0 && a.lse != nullptr && row_ok) a.lse[static_cast<size_t>(bh) * a.S_q + q_row] = m_ref + fast_log2(l_sum) * kDnLn2;
+        bh += d_bh;
+        qt += d_qt;
+        if (qt >= n_q) { qt -= n_q; ++bh; }
       }
+      // The read-out of an item's O waits for its last P V, which has only just been handed to the tensor core: it is
+      // done after the softmax of the NEXT item (whose S is ready already), when that wait costs nothing.
+      if (n > 0) epilogue(n - 1, pend_scale);
+      if (!have) break;
+      pend_scale = out_scale_item;
     }
-    if (tid == 0) tma_store_wait_read();   // the shared-memory sources must outlive the copies
   }
 
   tc_fence_before_sync();
@@ -420,7 +522,7 @@ static int launch_dense_impl(const FwdArgs& a, cudaStream_t stream) {
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, DnSmem::kDynBytes);
+    cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, DnSmem<DROPMASK>::kDynBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
     e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return static_cast<int>(e);
@@ -433,18 +535,20 @@ static int launch_dense_impl(const FwdArgs& a, cudaStream_t stream) {
   }
   const int64_t items = static_cast<int64_t>((a.S_q + kTileM - 1) / kTileM) * a.H * a.B;
   const int grid = static_cast<int>(items < sms ? items : sms);   // one persistent CTA per SM
-  const cudaError_t e = launch_overlapped(kfn, dim3(grid), dim3(kDnThreads), DnSmem::kDynBytes, stream, a);
+  const cudaError_t e = launch_overlapped(kfn, dim3(grid), dim3(kDnThreads), DnSmem<DROPMASK>::kDynBytes, stream, a);
   return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
 }
 
-// The dense-mask operators this kernel serves: head dimension 64, a dense keep or additive mask staged through TMA,
-// no dropout or a dense dropout mask, nothing saved.  Everything else stays with the general kernel.
+// The dense-mask operators this kernel serves: head dimension 64, a dense keep or additive mask and (if any) a dense
+// dropout mask that TMA can address (rows of 16-byte multiples), nothing saved.  Everything else stays with the
+// general kernel.
 bool fwd_dense_applies(const FwdArgs& a, int D) {
   const bool dense_mask = a.mask_kind == FMHA_MASK_DENSE_KEEP || a.mask_kind == FMHA_MASK_DENSE_ADDITIVE;
-  const bool drop_ok = a.dropout_kind == FMHA_DROPOUT_NONE || a.dropout_kind == FMHA_DROPOUT_DENSE;
+  const bool drop_ok = a.dropout_kind == FMHA_DROPOUT_NONE || (a.dropout_kind == FMHA_DROPOUT_DENSE && a.dmask_tiles > 0);
   return D == 64 && dense_mask && a.mask_tiles > 0 && drop_ok && a.save_softmax == nullptr && a.save_dropout == nullptr &&
          a.keep_mask_out == nullptr && a.debug_scores == nullptr;
 }
+
 
 int launch_fwd_dense(const FwdArgs& a, int dtype, cudaStream_t stream) {
   const bool bf = dtype == FMHA_DTYPE_BF16;

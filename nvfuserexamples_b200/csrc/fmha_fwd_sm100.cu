@@ -571,6 +571,8 @@ static int launch_fwd_impl(const FwdArgs& a, cudaStream_t stream) {
 
 int launch_fwd(const FwdArgs& a, int D, int dtype, bool legacy, bool p_via_smem, cudaStream_t stream) {
   if (!legacy) return launch_fwd_fast(a, D, dtype, stream);  // compact masks, Philox dropout: the production kernel
+  // the reference's dense-mask operators with nothing saved: the persistent, double-buffered kernel
+  if (!p_via_smem && fwd_dense_applies(a, D)) return launch_fwd_dense(a, dtype, stream);
 #define FMHA_FWD_CASE(DD, BF, LG, PS) \
   if (D == DD && (dtype == FMHA_DTYPE_BF16) == BF && legacy == LG && p_via_smem == PS) \
     return launch_fwd_impl<DD, BF, LG, PS>(a, stream);

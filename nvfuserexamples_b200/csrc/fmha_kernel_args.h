@@ -23,14 +23,18 @@ struct FwdArgs {
   alignas(64) CUtensorMap tm_o;
   // general kernel only: the dense [B*H*S_q, S_k] 16-bit padding mask as a 2-D map with {64 x 128} boxes
   alignas(64) CUtensorMap tm_mask;
+  // dense-mask kernel only: the dense dropout mask, same shape and boxes as tm_mask (valid when dmask_tiles is 1)
+  alignas(64) CUtensorMap tm_dmask;
+  int dmask_tiles;
   int mask_tiles;   // 0: the mask is read with plain loads; 1: staged tile by tile through TMA
   // FMHA_MASK_CU_SEQLENS (production kernel): mask = int32 [B+1] row offsets into the packed [total_rows, H, D]
   // tensors; o_ptr / strides serve the row-wise stores of a sequence's last, partial query tile
   int total_rows;
   void* o_ptr;
-  int64_t o_ss, o_sh;
+  int64_t o_ss, o_sh, o_sb;   // strides in elements (o_sb: dense-mask kernel, which stores O row by row)
   int B, H, S_q, S_k;
   float scale_log2;  // softmax scale * log2(e)
+  float scale;       // softmax scale
   float* lse;
   int mask_kind;
   const void* mask;
