@@ -7,6 +7,7 @@ Layout of the package:
   capi.py      ctypes binding of the C ABI
   api.py       Python mirror of the reference's operator interface plus the new entry points
   sharding.py  batch x heads partitioning across the GPUs of one box (no collective)
+  workloads.py the named benchmark configurations and their seeded synthetic inputs (bench.py, tests)
 """
 from . import capi, sharding  # noqa: F401
 from .api import (fmha_backward, fmha_forward, fmha_nvfuser, fmha_train_nvfuser,  # noqa: F401
