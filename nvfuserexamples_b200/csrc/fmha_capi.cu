@@ -101,6 +101,25 @@ static int make_tmap_dense(CUtensorMap* out, const void* ptr, int dtype, uint64_
   return FMHA_OK;
 }
 
+// Tensor map of a dense 16-bit [heads, rows, cols] output with {64 x 128 x 1} boxes and 128-byte swizzle (stores of a
+// tile that reaches past a head's last row are clipped at that row).
+static int make_tmap_dense3(CUtensorMap* out, void* ptr, int dtype, uint64_t heads, uint64_t rows, uint64_t cols) {
+  auto enc = get_encode_fn();
+  if (enc == nullptr) return FMHA_ERR_LAUNCH;
+  const cuuint64_t dims[3] = {cols, rows, heads};
+  const cuuint64_t strides[2] = {cols * 2, rows * cols * 2};
+  const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(kTileM), 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUtensorMapDataType dt = (dtype == FMHA_DTYPE_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = enc(out, dt, 3, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_cuda_error = static_cast<int>(r);
+    return FMHA_ERR_LAUNCH;
+  }
+  return FMHA_OK;
+}
+
 static bool tensor_ok(const fmha_tensor4& t, int B, int H) {
   if (t.ptr == nullptr) return false;
   if (reinterpret_cast<uintptr_t>(t.ptr) & 15) return false;
@@ -247,6 +266,14 @@ int fmha_sm100_fwd(const fmha_fwd_params* p, void* stream) {
   if (dense_mask && (p->S_k % 8) == 0 && (reinterpret_cast<uintptr_t>(p->mask) & 15) == 0) {
     if ((rc = make_tmap_dense(&a.tm_mask, p->mask, p->dtype, static_cast<uint64_t>(p->B) * p->H * p->S_q, p->S_k))) return rc;
     a.mask_tiles = 1;
+  }
+  a.save_tiles = 0;
+  if (p->save_softmax != nullptr && p->save_dropout != nullptr && (p->S_k % 8) == 0 &&
+      (reinterpret_cast<uintptr_t>(p->save_softmax) & 15) == 0 && (reinterpret_cast<uintptr_t>(p->save_dropout) & 15) == 0) {
+    const uint64_t heads = static_cast<uint64_t>(p->B) * p->H;
+    if ((rc = make_tmap_dense3(&a.tm_save_sm, p->save_softmax, p->dtype, heads, p->S_q, p->S_k))) return rc;
+    if ((rc = make_tmap_dense3(&a.tm_save_dr, p->save_dropout, p->dtype, heads, p->S_q, p->S_k))) return rc;
+    a.save_tiles = 1;
   }
   a.dmask_tiles = 0;
   if (p->dropout_kind == FMHA_DROPOUT_DENSE && p->dropout_mask != nullptr && (p->S_k % 8) == 0 &&

@@ -62,7 +62,7 @@ struct DnSmem {
   static constexpr int kOffO = kOffDM + (DROPMASK ? 2 * kMaskTile : 0);
   static constexpr int kOffX = kOffO + kOSlots * kTile;  // [2 slots][4 column quarters][128 rows] floats
   static constexpr int kOffBar = kOffX + 2 * 4 * kTileM * 4;
-  static constexpr int kNumBars = 32;
+  static constexpr int kNumBars = 34;
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;
   static constexpr int kBytes = kOffMisc + 16;
   static constexpr int kDynBytes = kBytes + 1024;
@@ -95,9 +95,16 @@ __device__ __forceinline__ bool dn_wait(uint64_t* bar, uint32_t parity, const Wa
 }  // namespace
 
 // KEEP: the dense mask is a keep mask (1 = keep), else additive.  DROPMASK: a dense 0/1 dropout mask is applied.
-template <bool BF16, bool KEEP, bool DROPMASK>
+// SAVE (`fmha_train_saveim_nvfuser`, fmha_manual.cpp:1231-1238; one key step, i.e. S_k <= 128): the normalised softmax
+// and softmax * mask * scale are also written as 16-bit [B*H, S_q, S_k] tensors, and the ROUNDED second tensor is what
+// the second GEMM consumes (fmha_manual.cpp:891-897).  Both tiles are staged in the shared-memory slots their mask
+// tiles came in (every thread overwrites exactly the 64 bytes it read) and leave through the store warp.
+template <bool BF16, bool KEEP, bool DROPMASK, bool SAVE>
 __global__ void __launch_bounds__(kDnThreads, 1) fmha_fwd_dense_kernel(const __grid_constant__ FwdArgs a) {
-  griddep_wait();
+  static_assert(!SAVE || DROPMASK, "the save mode is the train operator's: it has a dropout mask");
+  // The kernel is launched with programmatic stream serialization: everything up to the first access to global
+  // memory (barrier set-up, tensor-memory allocation) may run while the previous kernel of the stream drains; each
+  // thread calls griddep_wait() before its own first access.
   using L = DnSmem<DROPMASK>;
   constexpr int D = 64;
   constexpr int QS = L::kQSlots, VS = L::kVSlots, OS = L::kOSlots;
@@ -132,6 +139,7 @@ __global__ void __launch_bounds__(kDnThreads, 1) fmha_fwd_dense_kernel(const __g
   uint64_t* v_empty = bars + 25;   // [VS] ... and its P V has completed
   uint64_t* o_staged = bars + 28;  // [OS] the rounded O tile of an item is in its staging tile
   uint64_t* o_stage_free = bars + 30;  // [OS] ... and the TMA store has read it
+  [[maybe_unused]] uint64_t* save_staged = bars + 32;  // [2] SAVE: the two saved tiles of a key step are in their mask slots
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(smem + L::kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kOffMisc + 4);
 
@@ -182,7 +190,8 @@ __global__ void __launch_bounds__(kDnThreads, 1) fmha_fwd_dense_kernel(const __g
       mbar_init(k_full + i, 1);
       mbar_init(k_empty + i, 1);
       mbar_init(m_full + i, 1);
-      mbar_init(m_empty + i, kDnSoftmaxThreads / 32);
+      mbar_init(m_empty + i, SAVE ? 1 : kDnSoftmaxThreads / 32);   // SAVE: released by the store warp
+      mbar_init(save_staged + i, kDnSoftmaxThreads / 32);
       mbar_init(s_full + i, 1);
       mbar_init(p_full + i, kDnSoftmaxThreads);
       mbar_init(pv_done + i, 1);
@@ -198,6 +207,7 @@ __global__ void __launch_bounds__(kDnThreads, 1) fmha_fwd_dense_kernel(const __g
       mbar_init(o_stage_free + i, 1);
     }
     mbar_fence_init();
+    griddep_wait();
     // The first item's loads go out at once: the rest of the set-up (tensor-memory allocation, the CTA-wide
     // synchronisation) runs under their latency.
     if (static_cast<int>(blockIdx.x) < num_items) {
@@ -216,6 +226,7 @@ __global__ void __launch_bounds__(kDnThreads, 1) fmha_fwd_dense_kernel(const __g
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_slot;
+  griddep_wait();
 
   if (warp == 0) {
     // ============================ TMA producer ======================================
@@ -305,16 +316,37 @@ __global__ void __launch_bounds__(kDnThreads, 1) fmha_fwd_dense_kernel(const __g
     // One thread: as each item's O tile is staged, hands it to TMA and releases the staging tile once it is read.
     if (lane == 0) {
       const int my_items = (num_items - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
-      int item = blockIdx.x;
-      for (int n = 0; n < my_items && *abort_flag == 0; ++n, item += gridDim.x) {
+      auto store_o = [&](int n) {   // O of this CTA's item number n
         const int os = n % OS;
-        if (!dn_wait(o_staged + os, (n / OS) & 1, wctx, kDOFull, kDnSleepNs)) break;
+        if (!dn_wait(o_staged + os, (n / OS) & 1, wctx, kDOFull, kDnSleepNs)) return;
+        const int item = blockIdx.x + n * gridDim.x;
         const int bh = item / n_q, q0 = (item % n_q) * kTileM;
         tma_store_4d(&a.tm_o, sO + os * L::kTile, 0, q0, bh % a.H, bh / a.H);
         tma_store_commit();
         tma_store_wait_read();
         mbar_arrive(o_stage_free + os);
+      };
+      for (int n = 0; n < my_items && *abort_flag == 0; ++n) {
+        if constexpr (SAVE) {
+          // the saved tiles of item n are staged right after its softmax, O of item n-1 right after that
+          const int st = n & 1;   // one key step per item
+          if (!dn_wait(save_staged + st, (n >> 1) & 1, wctx, kDOFull, kDnSleepNs)) break;
+          const int item = blockIdx.x + n * gridDim.x;
+          const int bh = item / n_q, q0 = (item % n_q) * kTileM;
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            tma_store_3d(&a.tm_save_sm, sM + st * L::kMaskTile + c * 16384, c * 64, q0, bh);
+            tma_store_3d(&a.tm_save_dr, sDM + st * L::kMaskTile + c * 16384, c * 64, q0, bh);
+          }
+          tma_store_commit();
+          tma_store_wait_read();
+          mbar_arrive(m_empty + st);   // the slots may take the masks of the step after next
+          if (n > 0) store_o(n - 1);
+        } else {
+          store_o(n);
+        }
       }
+      if (SAVE && my_items > 0 && *abort_flag == 0) store_o(my_items - 1);
       tma_store_wait_read();   // the shared-memory sources must outlive the copies
     }
   } else {
@@ -372,6 +404,7 @@ __global__ void __launch_bounds__(kDnThreads, 1) fmha_fwd_dense_kernel(const __g
         const bool row_ok = q_row < a.S_q;
         float m_ref = -INFINITY;
         float2 sum2 = make_float2(0.f, 0.f);
+        [[maybe_unused]] float l_row = 1.0f;
 
         for (int j = 0; j < n_kv; ++j, ++g) {
           const int st = g & 1;
@@ -415,6 +448,7 @@ __global__ void __launch_bounds__(kDnThreads, 1) fmha_fwd_dense_kernel(const __g
             __syncwarp();
             if (lane == 0) mbar_arrive(m_empty + st);   // this warp has read its part of the mask tile
           }
+          [[maybe_unused]] const uint32_t mtile = smem_u32(sM + st * L::kMaskTile + (cq >> 1) * 16384);
           if (n_cols < 32) {   // the same for the whole warp
 #pragma unroll
             for (int k = 0; k < 32; ++k)
@@ -459,8 +493,10 @@ __global__ void __launch_bounds__(kDnThreads, 1) fmha_fwd_dense_kernel(const __g
               const uint4 w = lds128(dtile + sw128_offset(row, (cq & 1) * 4 + q));
               dmw[q * 4 + 0] = w.x; dmw[q * 4 + 1] = w.y; dmw[q * 4 + 2] = w.z; dmw[q * 4 + 3] = w.w;
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(m_empty + st);   // this warp has read its part of both mask tiles
+            if constexpr (!SAVE) {
+              __syncwarp();
+              if (lane == 0) mbar_arrive(m_empty + st);   // this warp has read its part of both mask tiles
+            }
           }
           uint32_t packed[16];
           const float2 negm2 = make_float2(-m_ref * kDnLog2e, -m_ref * kDnLog2e);
@@ -472,8 +508,45 @@ __global__ void __launch_bounds__(kDnThreads, 1) fmha_fwd_dense_kernel(const __g
             p.x = fast_exp2(x.x);
             p.y = fast_exp2(x.y);
             sum2 = __fadd2_rn(sum2, p);
-            packed[k] = pack2<BF16>(p.x, p.y);
-            if constexpr (DROPMASK) packed[k] = mul2_16bit<BF16>(packed[k], dmw[k]);
+            if constexpr (SAVE) {
+              sv[2 * k] = __float_as_uint(p.x);
+              sv[2 * k + 1] = __float_as_uint(p.y);
+            } else {
+              packed[k] = pack2<BF16>(p.x, p.y);
+              if constexpr (DROPMASK) packed[k] = mul2_16bit<BF16>(packed[k], dmw[k]);
+            }
+          }
+          if constexpr (SAVE) {
+            // One key step per item: the row sum is final.  Normalise, write the softmax tile and the dropout tile
+            // (fp32 product, one rounding each, as fmha_manual.cpp:880-897) over the mask tiles, and hand the rounded
+            // dropout tile to the second GEMM.
+            const int xs2 = (g + n + 1) & 1;
+            sX[(xs2 * 4 + cq) * kTileM + row] = sum2.x + sum2.y;
+            stop = named_bar_or(1, kDnSoftmaxThreads, *abort_flag != 0);
+            const float* xr2 = sX + xs2 * 4 * kTileM + row;
+            l_row = (xr2[0] + xr2[kTileM]) + (xr2[2 * kTileM] + xr2[3 * kTileM]);
+            const float inv_l = __fdividef(1.0f, l_row);
+            const float2 il2 = make_float2(inv_l, inv_l);
+            const float2 ds2 = make_float2(a.dropout_scale, a.dropout_scale);
+            const uint32_t dtile = smem_u32(sDM + st * L::kMaskTile + (cq >> 1) * 16384);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint32_t smw[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int k = q * 4 + e;
+                const float2 sm = __fmul2_rn(make_float2(__uint_as_float(sv[2 * k]), __uint_as_float(sv[2 * k + 1])), il2);
+                smw[e] = pack2<BF16>(sm.x, sm.y);
+                const float2 dr = __fmul2_rn(sm, __fmul2_rn(unpack2<BF16>(dmw[k]), ds2));
+                packed[k] = pack2<BF16>(dr.x, dr.y);
+              }
+              const uint32_t off = sw128_offset(row, (cq & 1) * 4 + q);
+              sts128(mtile + off, smw[0], smw[1], smw[2], smw[3]);
+              sts128(dtile + off, packed[q * 4 + 0], packed[q * 4 + 1], packed[q * 4 + 2], packed[q * 4 + 3]);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(save_staged + st);
           }
           // P over S: 128 16-bit values in 64 columns; this thread's 32 values are columns [16*cq, +16)
           tmem_st16(tmem_base + lane_addr + kColS + st * kTileN + cq * 16, packed);
@@ -483,12 +556,18 @@ __global__ void __launch_bounds__(kDnThreads, 1) fmha_fwd_dense_kernel(const __g
         }
 
         // ---- end of the item: row sum over the four quarters, logsumexp -----------------------------------------
-        const int xs = (g + n) & 1;   // exchanges so far: one per key step and one per finished item
-        sX[(xs * 4 + cq) * kTileM + row] = sum2.x + sum2.y;
-        stop = named_bar_or(1, kDnSoftmaxThreads, *abort_flag != 0);
-        const float* xr = sX + xs * 4 * kTileM + row;
-        const float l_sum = (xr[0] + xr[kTileM]) + (xr[2 * kTileM] + xr[3 * kTileM]);
-        out_scale_item = __fdividef(DROPMASK ? a.dropout_scale : 1.0f, l_sum);
+        float l_sum;
+        if constexpr (SAVE) {
+          l_sum = l_row;              // exchanged inside the (only) key step; P is normalised already
+          out_scale_item = 1.0f;
+        } else {
+          const int xs = (g + n) & 1;   // exchanges so far: one per key step and one per finished item
+          sX[(xs * 4 + cq) * kTileM + row] = sum2.x + sum2.y;
+          stop = named_bar_or(1, kDnSoftmaxThreads, *abort_flag != 0);
+          const float* xr = sX + xs * 4 * kTileM + row;
+          l_sum = (xr[0] + xr[kTileM]) + (xr[2 * kTileM] + xr[3 * kTileM]);
+          out_scale_item = __fdividef(DROPMASK ? a.dropout_scale : 1.0f, l_sum);
+        }
         if (cq == 0 && a.lse != nullptr && row_ok) a.lse[static_cast<size_t>(bh) * a.S_q + q_row] = m_ref + fast_log2(l_sum) * kDnLn2;
         bh += d_bh;
         qt += d_qt;
@@ -514,9 +593,9 @@ __global__ void __launch_bounds__(kDnThreads, 1) fmha_fwd_dense_kernel(const __g
   }
 }
 
-template <bool BF16, bool KEEP, bool DROPMASK>
+template <bool BF16, bool KEEP, bool DROPMASK, bool SAVE>
 static int launch_dense_impl(const FwdArgs& a, cudaStream_t stream) {
-  auto kfn = fmha_fwd_dense_kernel<BF16, KEEP, DROPMASK>;
+  auto kfn = fmha_fwd_dense_kernel<BF16, KEEP, DROPMASK, SAVE>;
   static std::atomic<bool> configured[64] = {};   // per device; set after the attribute call succeeded
   static std::atomic<int> sm_count[64] = {};
   int dev = 0, sms = 0;
@@ -544,18 +623,21 @@ static int launch_dense_impl(const FwdArgs& a, cudaStream_t stream) {
 // general kernel.
 bool fwd_dense_applies(const FwdArgs& a, int D) {
   const bool dense_mask = a.mask_kind == FMHA_MASK_DENSE_KEEP || a.mask_kind == FMHA_MASK_DENSE_ADDITIVE;
-  const bool drop_ok = a.dropout_kind == FMHA_DROPOUT_NONE || (a.dropout_kind == FMHA_DROPOUT_DENSE && a.dmask_tiles > 0);
-  return D == 64 && dense_mask && a.mask_tiles > 0 && drop_ok && a.save_softmax == nullptr && a.save_dropout == nullptr &&
-         a.keep_mask_out == nullptr && a.debug_scores == nullptr;
+  const bool drop_dense = a.dropout_kind == FMHA_DROPOUT_DENSE && a.dmask_tiles > 0;
+  if (D != 64 || !dense_mask || a.mask_tiles <= 0 || a.keep_mask_out != nullptr || a.debug_scores != nullptr) return false;
+  if (a.save_softmax == nullptr && a.save_dropout == nullptr) return a.dropout_kind == FMHA_DROPOUT_NONE || drop_dense;
+  // the save-intermediates operator: both tensors, an additive mask, a dropout mask, one key step
+  return a.save_tiles > 0 && a.mask_kind == FMHA_MASK_DENSE_ADDITIVE && drop_dense && a.S_k <= kTileN;
 }
-
 
 int launch_fwd_dense(const FwdArgs& a, int dtype, cudaStream_t stream) {
   const bool bf = dtype == FMHA_DTYPE_BF16;
   const bool keep = a.mask_kind == FMHA_MASK_DENSE_KEEP;
   const bool dm = a.dropout_kind == FMHA_DROPOUT_DENSE;
+  if (a.save_softmax != nullptr)
+    return bf ? launch_dense_impl<true, false, true, true>(a, stream) : launch_dense_impl<false, false, true, true>(a, stream);
 #define FMHA_DENSE_CASE(BF, KP, DM) \
-  if (bf == BF && keep == KP && dm == DM) return launch_dense_impl<BF, KP, DM>(a, stream);
+  if (bf == BF && keep == KP && dm == DM) return launch_dense_impl<BF, KP, DM, false>(a, stream);
   FMHA_DENSE_CASE(false, false, false)
   FMHA_DENSE_CASE(false, false, true)
   FMHA_DENSE_CASE(false, true, false)

@@ -26,6 +26,11 @@ struct FwdArgs {
   // dense-mask kernel only: the dense dropout mask, same shape and boxes as tm_mask (valid when dmask_tiles is 1)
   alignas(64) CUtensorMap tm_dmask;
   int dmask_tiles;
+  // dense-mask kernel only: the two saved [B*H, S_q, S_k] tensors as 3-D maps {S_k, S_q, B*H} with {64 x 128 x 1}
+  // boxes, so that a tile stored at the end of a head's rows is clipped there (valid when save_tiles is 1)
+  alignas(64) CUtensorMap tm_save_sm;
+  alignas(64) CUtensorMap tm_save_dr;
+  int save_tiles;
   int mask_tiles;   // 0: the mask is read with plain loads; 1: staged tile by tile through TMA
   // FMHA_MASK_CU_SEQLENS (production kernel): mask = int32 [B+1] row offsets into the packed [total_rows, H, D]
   // tensors; o_ptr / strides serve the row-wise stores of a sequence's last, partial query tile

@@ -35,11 +35,13 @@ def _inputs(bh, sq, sk, dt, dev):
     return q, k, v, am, dm
 
 
-def _run(q, k, v, am, dm, keep, drop, general):
+def _run(q, k, v, am, dm, keep, drop, general, save=False):
     mask = am if keep else ((1 - am) * -1000).to(am.dtype)
     kw = dict(mask_kind=capi.MASK_DENSE_KEEP if keep else capi.MASK_DENSE_ADDITIVE, mask=mask, scale=0.125)
     if drop:
         kw.update(dropout_kind=capi.DROPOUT_DENSE, dropout_mask=dm, dropout_scale=2.0)
+    if save:
+        kw.update(save_softmax=True, save_dropout=True)
     if general:
         kw["flags"] = capi.FLAG_P_VIA_SMEM
     st = torch.zeros(4, dtype=torch.int32, device=q.device)
@@ -91,3 +93,30 @@ def test_reference_shape_many_calls_are_deterministic(cuda_device):
     for _ in range(10):
         again, _ = _run(q, k, v, am, dm, False, True, general=False)
         assert torch.equal(first["o"], again["o"]) and torch.equal(first["lse"], again["lse"])
+
+
+@pytest.mark.parametrize("bh,sq,sk", [(4, 128, 128), (700, 128, 128), (3, 200, 120), (5, 77, 64), (150, 300, 128)])
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+def test_save_intermediates_mode(cuda_device, bh, sq, sk, dt):
+    """`fmha_train_saveim_nvfuser` (fmha/fmha_manual.cpp:1231-1238) with one key step: the softmax and dropout tensors
+    and the context computed from the ROUNDED dropout tensor (:891-897), against the fp32 composite and the general
+    kernel, on shapes whose last query tile and only key step are ragged (the tile stores are clipped per head)."""
+    q, k, v, am, dm = _inputs(bh, sq, sk, dt, cuda_device)
+    res, add = _run(q, k, v, am, dm, False, True, general=False, save=True)
+    gen, _ = _run(q, k, v, am, dm, False, True, general=True, save=True)
+    ref = composite.attention_fp32(q[0], k[0], v[0], add_mask=add, keep=dm.float(), keep_scale=2.0, scale=0.125)
+    what = f"save bh={bh} sq={sq} sk={sk} {dt}"
+    ulp = 2.0 ** -10 if dt == torch.float16 else 2.0 ** -7   # one rounding of values up to 1 (softmax) or 2 (dropout)
+    for name, key, top in (("softmax", "softmax", 1.0), ("dropout_out", "dropout_out", 2.0)):
+        got, want = res[name].float(), ref[key]
+        assert got.shape == want.shape, what
+        assert (got - want).abs().max().item() <= 1.5 * top * ulp + 1e-5, f"{what}: {name}"
+        assert (got - gen[name].float()).abs().max().item() <= 2 * top * ulp, f"{what}: {name} against the general kernel"
+    lse = res["lse"].reshape(bh, sq)
+    assert torch.allclose(lse, ref["lse"], atol=1e-3, rtol=1e-4), what
+    # the context: the second GEMM consumed the rounded dropout tensor, so compare with that product in fp32
+    o_from_saved = torch.matmul(res["dropout_out"].float(), v[0].float())
+    assert (res["o"][0].float() - o_from_saved).abs().max().item() <= (4e-3 if dt == torch.float16 else 3e-2), what
+    e_dense = (res["o"][0].float() - ref["o"]).abs().max().item()
+    e_general = (gen["o"][0].float() - ref["o"]).abs().max().item()
+    assert e_dense <= max(1.5 * e_general, 1e-3), f"{what}: {e_dense:.3e} against {e_general:.3e}"
