@@ -7,6 +7,7 @@ The build takes minutes, so its output is kept under build/setup_check/<hash of 
 sources are unchanged."""
 import hashlib
 import os
+import shutil
 import subprocess
 import sys
 from pathlib import Path
@@ -33,6 +34,9 @@ def test_setup_py_build_ext_yields_an_importable_mha_manual():
                               cwd=ROOT, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=3000)
         assert proc.returncode == 0, proc.stdout[-4000:]
         done.write_text("ok\n")
+        for other in out.parent.iterdir():   # outputs of earlier source states are of no further use
+            if other != out and other.is_dir():
+                shutil.rmtree(other, ignore_errors=True)
     built = list(lib.glob("mha_manual*.so"))
     assert len(built) == 1, f"expected one extension module under {lib}, found {built}"
     # import it in a fresh interpreter whose path starts at the build output, so the in-tree module cannot shadow it
