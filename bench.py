@@ -309,7 +309,8 @@ def run_ours(args, rank, world, local_rank):
         raise SystemExit("bench.py: no CUDA device (the kernels have no CPU fallback)")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    numa = pin_to_gpu_cpus(local_rank) if world > 1 else None   # before any pinned host buffer is touched
+    # before any pinned host buffer is touched; BENCH_NO_PIN=1 leaves the affinity alone (for comparison runs)
+    numa = None if os.environ.get("BENCH_NO_PIN") == "1" else pin_to_gpu_cpus(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     sampler = ClockSampler(local_rank)   # NVML is up before anything is timed
