@@ -52,6 +52,8 @@ template <int D, bool DROP = false>
 struct FastSmem {
   static constexpr int TN = (D == 64) ? 64 : 128;
   // With dropout the Philox state needs registers: three CTAs (112 registers per thread) instead of four (80).
+  // The additive key mask needs them too (at 80 registers its kernel spilled 244 bytes per thread and ran the
+  // BERT-large batch in 134 us; at three CTAs per SM, 101 us): see the launch bounds of the kernel.
   static constexpr int kCtasPerSm = (D == 64) ? (DROP ? 3 : 4) : 2;
   static constexpr int kStages = (D == 64) ? 2 : 1;
   static constexpr int kQBytes = kTileM * D * 2;
@@ -111,7 +113,7 @@ __device__ __forceinline__ void softmax_chunk(const uint32_t (&r)[32], int cbase
 // PACKED: the batch is one [total_rows, H, D] tensor per operand with row offsets (FMHA_MASK_CU_SEQLENS); a
 // template parameter so that the padded kernels carry none of its bookkeeping in registers.
 template <int D, bool BF16, bool KEYADD, bool DROP, bool PACKED = false>
-__global__ void __launch_bounds__(kThreads, FastSmem<D, DROP>::kCtasPerSm) fmha_fwd_fast_kernel(const __grid_constant__ FwdArgs a) {
+__global__ void __launch_bounds__(kThreads, (D == 64 && KEYADD) ? 3 : FastSmem<D, DROP>::kCtasPerSm) fmha_fwd_fast_kernel(const __grid_constant__ FwdArgs a) {
   griddep_wait();
   using L = FastSmem<D>;
   constexpr int ST = L::kStages;
