@@ -36,7 +36,12 @@ namespace fmha {
 
 namespace {
 
-constexpr int kThreads = 192;
+// D = 128: 192 threads (TMA producer warp, MMA warp, four softmax warps).  D = 64: 160 threads, one warp issues both
+// the TMA loads and the MMAs.  Registers are allocated per SM sub-partition (16 384 each, warps dealt round-robin):
+// four CTAs of six warps put six warps on a sub-partition (80 registers per thread), four CTAs of five warps put
+// five (96), which is what the dropout and additive-mask variants need to stay out of local memory.
+constexpr int kThreadsSplit = 192, kThreadsMerged = 160;
+template <int D> constexpr int fast_threads() { return D == 64 ? kThreadsMerged : kThreadsSplit; }
 constexpr float kLog2eF = 1.4426950408889634f;
 constexpr float kLn2F = 0.6931471805599453f;
 
@@ -51,10 +56,8 @@ enum FastWaitSite {
 template <int D, bool DROP = false>
 struct FastSmem {
   static constexpr int TN = (D == 64) ? 64 : 128;
-  // With dropout the Philox state needs registers: three CTAs (112 registers per thread) instead of four (80).
-  // The additive key mask needs them too (at 80 registers its kernel spilled 244 bytes per thread and ran the
-  // BERT-large batch in 134 us; at three CTAs per SM, 101 us): see the launch bounds of the kernel.
-  static constexpr int kCtasPerSm = (D == 64) ? (DROP ? 3 : 4) : 2;
+  // Four CTAs per SM at D = 64 (five warps each: 96 registers per thread), two at D = 128.
+  static constexpr int kCtasPerSm = (D == 64) ? 4 : 2;
   static constexpr int kStages = (D == 64) ? 2 : 1;
   static constexpr int kQBytes = kTileM * D * 2;
   static constexpr int kTileBytes = TN * D * 2;    // one K or V tile
@@ -113,8 +116,11 @@ __device__ __forceinline__ void softmax_chunk(const uint32_t (&r)[32], int cbase
 // PACKED: the batch is one [total_rows, H, D] tensor per operand with row offsets (FMHA_MASK_CU_SEQLENS); a
 // template parameter so that the padded kernels carry none of its bookkeeping in registers.
 template <int D, bool BF16, bool KEYADD, bool DROP, bool PACKED = false>
-__global__ void __launch_bounds__(kThreads, (D == 64 && KEYADD) ? 3 : FastSmem<D, DROP>::kCtasPerSm) fmha_fwd_fast_kernel(const __grid_constant__ FwdArgs a) {
+__global__ void __launch_bounds__(fast_threads<D>(), FastSmem<D, DROP>::kCtasPerSm) fmha_fwd_fast_kernel(const __grid_constant__ FwdArgs a) {
   griddep_wait();
+  constexpr bool MERGED = (D == 64);          // one warp issues the loads and the MMAs
+  constexpr int kMmaWarp = MERGED ? 0 : 1;    // it also owns the tensor-memory allocation
+  constexpr int kFirstSoftmaxThread = MERGED ? 32 : 64;
   using L = FastSmem<D>;
   constexpr int ST = L::kStages;
   constexpr int TN = L::TN;
@@ -190,7 +196,7 @@ __global__ void __launch_bounds__(kThreads, (D == 64 && KEYADD) ? 3 : FastSmem<D
     tma_prefetch_desc(&a.tm_v);
     tma_prefetch_desc(&a.tm_o);
   }
-  if (warp == 1) {
+  if (warp == kMmaWarp) {
     tmem_alloc(tmem_base_slot, kTmemCols);
     tmem_relinquish();
   }
@@ -200,7 +206,7 @@ __global__ void __launch_bounds__(kThreads, (D == 64 && KEYADD) ? 3 : FastSmem<D
   const uint32_t tmem_base = *tmem_base_slot;
   const WaitCtx wctx{abort_flag, a.status};
 
-  if (warp == 0) {
+  if (warp == 0 && !MERGED) {
     // ============================ TMA producer ======================================
     if (lane == 0) {
       mbar_arrive_expect_tx(q_full, L::kQBytes);
@@ -220,7 +226,79 @@ __global__ void __launch_bounds__(kThreads, (D == 64 && KEYADD) ? 3 : FastSmem<D
           tma_load_4d(sV + s * L::kTileBytes + c * L::kSubTile, &a.tm_v, v_full + s, c * 64, row_base + j * TN, h, tb);
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 0 && MERGED) {
+    // ============================ TMA producer + MMA issuer in one warp (D = 64) =====
+    // The warp runs convergently; one elected lane issues the loads, MMA bursts go out as in the split version.
+    // Order per key step j: Q K^T(j); then, while the softmax warps work on S(j), wait for that MMA to complete
+    // (a few hundred cycles) and refill what it and the previous P V have released: K of step j+ST and V of step
+    // j-1+ST (the tensor core works in order, so P V(j-1), issued before Q K^T(j), has completed too); then wait
+    // for P(j) and issue P V(j).  No refill ever stands between P V(j) and Q K^T(j+1), the chain the step time
+    // hangs on.
+    if constexpr (MERGED) {
+      constexpr int KQ = D / 16;     // k-steps of S = Q K^T
+      constexpr int KP = TN / 16;    // k-steps of O += P V
+      static_assert(KQ == 4 && KP == 4, "merged warp: D = 64 with 64-key steps");
+      const uint32_t tS = tmem_base + kColS;
+      const uint32_t tO = tmem_base + kColO;
+      auto load_k = [&](int j) {
+        const int s = j % ST;
+        mbar_arrive_expect_tx(k_full + s, L::kTileBytes);
+        tma_load_4d(sK + s * L::kTileBytes, &a.tm_k, k_full + s, 0, row_base + j * TN, h, tb);
+      };
+      auto load_v = [&](int j) {
+        const int s = j % ST;
+        mbar_arrive_expect_tx(v_full + s, L::kTileBytes);
+        tma_load_4d(sV + s * L::kTileBytes, &a.tm_v, v_full + s, 0, row_base + j * TN, h, tb);
+      };
+      if (elect_one()) {
+        mbar_arrive_expect_tx(q_full, L::kQBytes);
+        tma_load_4d(sQ, &a.tm_q, q_full, 0, row_base + q0, h, tb);
+        for (int j = 0; j < ST && j < n_kv; ++j) {
+          load_k(j);
+          load_v(j);
+        }
+      }
+      __syncwarp();
+      const uint64_t dq = make_smem_desc_sw128(smem_u32(sQ), 16, 1024);
+      uint64_t aq[KQ];
+#pragma unroll
+      for (int kk = 0; kk < KQ; ++kk) aq[kk] = dq + kmajor_step(kk, 16384);
+      mbar_wait(q_full, 0, wctx, kFQFull);
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j % ST;
+        const uint32_t ph = (j / ST) & 1;
+        const uint64_t dk = make_smem_desc_sw128(smem_u32(sK + s * L::kTileBytes), 16, 1024);
+        const uint64_t dv = make_smem_desc_sw128(smem_u32(sV + s * L::kTileBytes), L::kSubTile, 1024);
+        uint64_t bk[KQ], bv[KP];
+#pragma unroll
+        for (int kk = 0; kk < KQ; ++kk) bk[kk] = dk + kmajor_step(kk, L::kSubTile);
+#pragma unroll
+        for (int kk = 0; kk < KP; ++kk) bv[kk] = dv + mnmajor_step(kk);
+        mbar_wait(k_full + s, ph, wctx, kFKFull);
+        tc_fence_after_sync();
+        umma_ss_x4(tS, aq, bk, kIdescQK, 0u);
+        umma_commit_elect(k_empty + s);
+        umma_commit_elect(s_full);
+        // refills, under the softmax of this step
+        const bool more_k = j + ST < n_kv, more_v = j >= 1 && j - 1 + ST < n_kv;
+        if (more_k || more_v) {
+          mbar_wait(k_empty + s, ph, wctx, kFKEmpty);       // Q K^T(j) has completed, and P V(j-1) before it
+          if (more_v) mbar_wait(v_empty + ((j - 1) % ST), ((j - 1) / ST) & 1, wctx, kFVEmpty);
+          if (elect_one()) {
+            if (more_k) load_k(j + ST);
+            if (more_v) load_v(j - 1 + ST);
+          }
+          __syncwarp();
+        }
+        mbar_wait(p_full, j & 1, wctx, kFPFull);
+        mbar_wait(v_full + s, ph, wctx, kFVFull);
+        tc_fence_after_sync();
+        umma_ts_x4(tO, tS, 8u, bv, kIdescPV, (j > 0) ? 1u : 0u);
+        umma_commit_elect(v_empty + s);
+      }
+      umma_commit_elect(o_full);
+    }
+  } else if (warp == 1 && !MERGED) {
     // ============================ MMA issuer ========================================
     // The warp runs the loop convergently and issues the MMAs in bursts from one elected lane
     // with descriptors prepared beforehand (see umma_ss_x4): a single lane that computes each
@@ -271,7 +349,7 @@ __global__ void __launch_bounds__(kThreads, (D == 64 && KEYADD) ? 3 : FastSmem<D
     // ============================ softmax / epilogue ================================
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
-    const int tid = threadIdx.x - 64;
+    const int tid = threadIdx.x - kFirstSoftmaxThread;
     const int q_row = q0 + row;
     const bool row_ok = q_row < q_limit;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
@@ -446,7 +524,7 @@ __global__ void __launch_bounds__(kThreads, (D == 64 && KEYADD) ? 3 : FastSmem<D
     for (int k = 0; k < 20; ++k) __nanosleep(1000000);
     __syncthreads();
   }
-  if (warp == 1) {
+  if (warp == kMmaWarp) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
   }
@@ -465,7 +543,7 @@ static int launch_fast_impl(const FwdArgs& a, cudaStream_t stream) {
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   dim3 grid((a.S_q + kTileM - 1) / kTileM, a.H, a.B);
-  const cudaError_t e = launch_overlapped(kfn, grid, dim3(kThreads), L::kDynBytes, stream, a);
+  const cudaError_t e = launch_overlapped(kfn, grid, dim3(fast_threads<D>()), L::kDynBytes, stream, a);
   return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
 }
 
