@@ -2,11 +2,12 @@
 // lengths, additive [B,S_k] row, or a packed variable-length batch), optional Philox dropout,
 // writes O and the row logsumexp.
 //
-// Same CTA organisation as the general kernel in fmha_fwd_sm100.cu (TMA producer warp,
-// tcgen05.mma issuer warp, four softmax warps with one thread per query row; S in tensor
-// memory, P written back over it, O beside it).  Head dimension 64 walks the keys in 64-key
-// steps (S 64 + O 64 = 128 tensor-memory columns, three or four CTAs per SM), head dimension
-// 128 in 128-key steps (two CTAs per SM).  The softmax is written for instruction count and
+// CTA organisation as in the general kernel in fmha_fwd_sm100.cu (TMA producer, tcgen05.mma
+// issuer, four softmax warps with one thread per query row; S in tensor memory, P written back
+// over it, O beside it).  Head dimension 64 walks the keys in 64-key steps (S 64 + O 64 = 128
+// tensor-memory columns); there the producer and the MMA issuer are ONE warp, so a CTA has five
+// warps and four CTAs share an SM at 96 registers per thread.  Head dimension 128 uses 128-key
+// steps, separate producer and MMA warps and two CTAs per SM.  The softmax is written for instruction count and
 // latency, because at head dimension 64 the softmax warps, not the tensor core, set the pace:
 //   * mask kind, dropout and the packed-batch bookkeeping are template parameters: no
 //     per-chunk branches and no registers spent on modes that are off;
