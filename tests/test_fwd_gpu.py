@@ -137,6 +137,20 @@ def test_sharded_equals_unsharded_bitwise(cuda_device):
         assert torch.equal(torch.cat(parts), full.reshape(B * H, S, D))
 
 
+@pytest.mark.parametrize("D,dtype", [(64, torch.float16), (128, torch.bfloat16)])
+def test_forward_is_bit_reproducible_across_calls(cuda_device, D, dtype):
+    """More CTAs than resident slots, valid lengths and an additive key mask, with dropout: 40 calls give the same bits
+    (nothing in the forward depends on the order in which CTAs, loads or MMAs complete)."""
+    B, H, S = 8, 16, 512
+    q, k, v, _, lens = helpers.randn_like_config(B, H, S, S, D, dtype, seed=12, device=cuda_device)
+    add = composite.padding_add_mask(lens, S).reshape(B, S).contiguous()
+    for kw in (dict(seqlens=lens), dict(mask=add)):
+        first_o, first_lse = api.fmha_forward(q, k, v, p_drop=0.1, seed=4, offset=2, **kw)
+        for _ in range(40):
+            o, lse = api.fmha_forward(q, k, v, p_drop=0.1, seed=4, offset=2, **kw)
+        assert torch.equal(o, first_o) and torch.equal(lse, first_lse)
+
+
 @pytest.mark.parametrize("name", ["bert_base_fwd", "bert_large_fwd"])
 def test_full_size_properties(cuda_device, name):
     """At the benchmark sizes the CPU oracle is too slow, so check size-independent properties:
