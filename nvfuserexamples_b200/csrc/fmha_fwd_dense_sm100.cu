@@ -367,15 +367,19 @@ __global__ void __launch_bounds__(kDnThreads, 1) fmha_fwd_dense_kernel(const __g
     // took the issuing thread some 600 cycles, with every other softmax warp waiting for it at the next barrier.
     auto epilogue = [&](int n_ep, float out_scale) {
       const int ob = n_ep & 1;
-      dn_wait(o_full + ob, (n_ep >> 1) & 1, wctx, kDOFull, kDnSleepNs);
+      const int os = n_ep % OS;
+      // both polls go out before either answer is looked at (each is a round trip of about a hundred cycles, and both
+      // barriers have completed long ago as a rule)
+      const bool o_ok = mbar_try_wait(o_full + ob, (n_ep >> 1) & 1);
+      const bool st_ok = n_ep < OS || mbar_try_wait(o_stage_free + os, ((n_ep / OS) - 1) & 1);
+      if (!o_ok) dn_wait(o_full + ob, (n_ep >> 1) & 1, wctx, kDOFull, kDnSleepNs);
+      if (!st_ok) dn_wait(o_stage_free + os, ((n_ep / OS) - 1) & 1, wctx, kDOFree, kDnSleepNs);
       tc_fence_after_sync();
       uint32_t r[16];
       tmem_ld16(tmem_base + lane_addr + kColO + ob * D + cq * 16, r);
       tmem_wait_ld();
       tc_fence_before_sync();
       mbar_arrive(o_free + ob);
-      const int os = n_ep % OS;
-      if (n_ep >= OS) dn_wait(o_stage_free + os, ((n_ep / OS) - 1) & 1, wctx, kDOFree, kDnSleepNs);   // long free, as a rule
       uint8_t* stage = sO + os * L::kTile;
 #pragma unroll
       for (int q = 0; q < 2; ++q) {
